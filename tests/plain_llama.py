@@ -1,0 +1,195 @@
+"""A plain, slow implementation of the Llama-3 dense decoder: the oracle of the tests.
+
+Whole sequences, no cache, no batching, one function per part, float32 unless
+told otherwise.  It is written from the reference's formulas (each function
+cites torchllms file:line) and shares no code with ``torchllms_b200``: it reads
+``config.json`` with ``json`` and ``model.safetensors`` with the ``safetensors``
+package.  ``tests/golden/make_golden.py`` compared it once with the reference's
+own ``Transformer`` on CPU; ``tests/golden/*.json`` holds that run's outputs.
+"""
+
+from __future__ import annotations
+
+import json
+import math
+import re
+from pathlib import Path
+from typing import Dict, List, Optional, Sequence
+
+import torch
+from safetensors import safe_open
+
+
+# ----------------------------------------------------------------------------- parts
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """torchllms/models/networks.py:195-200: normalise in float32, cast back, times weight."""
+    xf = x.float()
+    normed = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).type_as(x)
+    return normed * weight
+
+
+def rope_frequencies(head_dim: int, theta: float, scaling: Optional[dict]) -> torch.Tensor:
+    """torchllms/models/networks.py:253-279: base frequencies and the llama3 three-band rescaling."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2)[: head_dim // 2].float() / head_dim))
+    kind = (scaling or {}).get("rope_type", (scaling or {}).get("type", "default"))
+    if kind == "llama3":
+        factor = scaling["factor"]
+        low = scaling["low_freq_factor"]
+        high = scaling["high_freq_factor"]
+        old_len = scaling["original_max_position_embeddings"]
+        wavelen = 2 * math.pi / inv                      # of the unscaled frequencies (:263)
+        low_band = wavelen > old_len / low               # long waves: divided by factor (:266)
+        high_band = wavelen < old_len / high             # short waves: untouched (:264)
+        smooth = (old_len / wavelen - low) / (high - low)
+        blended = (1 - smooth) * inv / factor + smooth * inv
+        inv = torch.where(low_band, inv / factor, torch.where(high_band, inv, blended))
+    elif kind != "default":
+        raise ValueError(kind)
+    return inv
+
+
+def rope_angles(inv_freq: torch.Tensor, positions: torch.Tensor):
+    """torchllms/models/networks.py:284-297: cos and sin of position * frequency, in float32."""
+    ang = positions.float()[:, None] * inv_freq[None, :].float()
+    return torch.cos(ang), torch.sin(ang)
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """torchllms/models/networks.py:332-352: rotate adjacent lanes (2i, 2i+1) in float32.
+    x: [S, heads, head_dim]; cos, sin: [S, head_dim / 2]."""
+    xf = x.float()
+    even, odd = xf[..., 0::2], xf[..., 1::2]
+    c, s = cos[:, None, :], sin[:, None, :]
+    out = torch.empty_like(xf)
+    out[..., 0::2] = even * c - odd * s
+    out[..., 1::2] = odd * c + even * s
+    return out.type_as(x)
+
+
+def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: Optional[int] = None) -> torch.Tensor:
+    """torchllms/models/networks.py:355-397 (eager form): query head h uses kv head h // (H / KV)
+    (repeat_interleave :371-374), scores / sqrt(head_dim) (:386), causal mask, softmax, times v.
+    q: [S, H, hd]; k, v: [S, KV, hd] -> [S, H * hd].  ``window`` (not in the reference) keeps only
+    the last ``window`` keys of each query, itself included."""
+    S, H, hd = q.shape
+    KV = k.shape[1]
+    rep = H // KV
+    out = torch.zeros(S, H, hd, dtype=torch.float32)
+    for h in range(H):
+        kh, vh = k[:, h // rep, :].float(), v[:, h // rep, :].float()
+        scores = (q[:, h, :].float() @ kh.T) / math.sqrt(hd)
+        i = torch.arange(S)[:, None]
+        j = torch.arange(S)[None, :]
+        hidden = j > i
+        if window is not None:
+            hidden = hidden | (j <= i - window)
+        scores = scores.masked_fill(hidden, float("-inf"))
+        out[:, h, :] = torch.softmax(scores, dim=-1) @ vh
+    return out.reshape(S, H * hd).type_as(q)
+
+
+def swiglu_ffn(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, w3: torch.Tensor) -> torch.Tensor:
+    """torchllms/models/networks.py:604-605: w2(silu(w1 x) * w3 x)."""
+    return (torch.nn.functional.silu(x @ w1.T) * (x @ w3.T)) @ w2.T
+
+
+def attention_layer(x, wq, wk, wv, wo, cfg, cos, sin):
+    """torchllms/models/networks.py:513-558: project, view as heads, rope q and k, attend, project."""
+    S = x.shape[0]
+    q = (x @ wq.T).view(S, cfg["n_heads"], cfg["head_dim"])
+    k = (x @ wk.T).view(S, cfg["n_kv_heads"], cfg["head_dim"])
+    v = (x @ wv.T).view(S, cfg["n_kv_heads"], cfg["head_dim"])
+    q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+    return causal_attention(q, k, v) @ wo.T
+
+
+def block(x, w: Dict[str, torch.Tensor], prefix: str, cfg, cos, sin):
+    """torchllms/models/networks.py:635-644: pre-norm residual block."""
+    g = lambda n: w[f"{prefix}.{n}"]
+    h = x + attention_layer(rms_norm(x, g("attention_norm.weight"), cfg["eps"]),
+                            g("attention.wq.weight"), g("attention.wk.weight"),
+                            g("attention.wv.weight"), g("attention.wo.weight"), cfg, cos, sin)
+    return h + swiglu_ffn(rms_norm(h, g("ffn_norm.weight"), cfg["eps"]),
+                          g("feed_forward.w1.weight"), g("feed_forward.w2.weight"), g("feed_forward.w3.weight"))
+
+
+def forward_logits(w: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int]) -> torch.Tensor:
+    """torchllms/models/networks.py:1017-1047: embed, blocks, final norm, head (tied :806-809).
+    Returns [len(tokens), vocab] logits for the whole sequence."""
+    ids = torch.as_tensor(list(tokens), dtype=torch.long)
+    x = w["tok_embeddings.weight"][ids]
+    inv = rope_frequencies(cfg["head_dim"], cfg["rope_theta"], cfg["rope_scaling"])
+    cos, sin = rope_angles(inv, torch.arange(len(ids)))
+    for i in range(cfg["n_layers"]):
+        x = block(x, w, f"layers.{i}", cfg, cos, sin)
+    x = rms_norm(x, w["norm.weight"], cfg["eps"])
+    head = w["tok_embeddings.weight"] if cfg["tie"] else w["output.weight"]
+    return x @ head.T
+
+
+# ------------------------------------------------------------------ reading a model folder
+
+_HF_LAYER = {
+    "self_attn.q_proj.weight": "attention.wq.weight", "self_attn.k_proj.weight": "attention.wk.weight",
+    "self_attn.v_proj.weight": "attention.wv.weight", "self_attn.o_proj.weight": "attention.wo.weight",
+    "mlp.gate_proj.weight": "feed_forward.w1.weight", "mlp.up_proj.weight": "feed_forward.w3.weight",
+    "mlp.down_proj.weight": "feed_forward.w2.weight", "input_layernorm.weight": "attention_norm.weight",
+    "post_attention_layernorm.weight": "ffn_norm.weight",
+}
+
+
+def read_config(folder) -> dict:
+    """Hugging Face keys -> the numbers above (torchllms/models/checkpoint_converter.py:359-397)."""
+    raw = json.loads((Path(folder) / "config.json").read_text())
+    heads = raw["num_attention_heads"]
+    return {
+        "n_layers": raw["num_hidden_layers"], "dim": raw["hidden_size"], "n_heads": heads,
+        "n_kv_heads": raw.get("num_key_value_heads", heads),
+        "head_dim": raw.get("head_dim") or raw["hidden_size"] // heads,
+        "vocab": raw["vocab_size"], "eps": raw["rms_norm_eps"], "rope_theta": raw["rope_theta"],
+        "rope_scaling": raw.get("rope_scaling"), "tie": raw.get("tie_word_embeddings", False),
+    }
+
+
+def read_weights(folder, cfg: dict, dtype=torch.float32) -> Dict[str, torch.Tensor]:
+    """Tensors by torchllms name; Hugging Face names are mapped and their q/k rows permuted to the
+    adjacent-lane order (torchllms/models/checkpoint_converter.py:96-108, :124-141, :172-178)."""
+    out: Dict[str, torch.Tensor] = {}
+    with safe_open(str(Path(folder) / "model.safetensors"), framework="pt") as f:
+        for name in f.keys():
+            t = f.get_tensor(name).to(dtype)
+            m = re.match(r"^model\.layers\.(\d+)\.(.+)$", name)
+            if m and m.group(2) in _HF_LAYER:
+                new = f"layers.{m.group(1)}.{_HF_LAYER[m.group(2)]}"
+                if m.group(2).startswith("self_attn.q_proj") or m.group(2).startswith("self_attn.k_proj"):
+                    hd = cfg["head_dim"]
+                    n = t.shape[0] // hd
+                    t = t.view(n, 2, hd // 2, t.shape[1]).transpose(1, 2).reshape(n * hd, t.shape[1])
+                out[new] = t
+            elif name == "model.embed_tokens.weight":
+                out["tok_embeddings.weight"] = t
+            elif name == "model.norm.weight":
+                out["norm.weight"] = t
+            elif name == "lm_head.weight":
+                out["output.weight"] = t
+            else:
+                out[name] = t
+    return out
+
+
+class PlainModel:
+    def __init__(self, folder, dtype=torch.float32):
+        self.cfg = read_config(folder)
+        self.weights = read_weights(folder, self.cfg, dtype)
+
+    @torch.no_grad()
+    def logits(self, tokens: Sequence[int]) -> torch.Tensor:
+        return forward_logits(self.weights, self.cfg, tokens).float()
+
+    @torch.no_grad()
+    def greedy(self, prompt: Sequence[int], n_new: int) -> List[int]:
+        seq = list(prompt)
+        for _ in range(n_new):
+            seq.append(int(torch.argmax(self.logits(seq)[-1])))
+        return seq[len(prompt):]

@@ -1,0 +1,71 @@
+// Shared helpers of the sm_100a kernels: element conversion, launch checks, the C ABI convention.
+//
+// Every exported function is `extern "C" int tl_<name>(..., void* stream)`.  It
+// validates what only the host can see cheaply, launches on `stream`, and returns 0
+// or a negative code from the enum below (positive values are cudaError_t).  The
+// Python side turns a non-zero return into an exception; nothing here allocates
+// memory, synchronises a stream or keeps state between calls.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+enum TlStatus : int {
+    TL_OK = 0,
+    TL_BAD_DTYPE = -1,      // dtype code is not one of TL_F32 / TL_BF16
+    TL_BAD_SIZE = -2,       // a size the kernel refuses (see the message of the Python wrapper)
+    TL_BAD_ALIGN = -3,      // a pointer or row pitch is not aligned as the kernel needs
+    TL_TOO_LARGE = -4,      // needs more shared memory or scratch than there is
+};
+
+enum TlDtype : int { TL_F32 = 0, TL_BF16 = 1 };
+
+#define TL_LAUNCH_CHECK()                                  \
+    do {                                                   \
+        cudaError_t e__ = cudaGetLastError();              \
+        if (e__ != cudaSuccess) return (int)e__;           \
+    } while (0)
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// 16-byte vector of elements: 4 floats or 8 bfloat16.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    float4 v;
+    __device__ __forceinline__ void load(const float* p) { v = *reinterpret_cast<const float4*>(p); }
+    __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = v; }
+    __device__ __forceinline__ float get(int i) const { return reinterpret_cast<const float*>(&v)[i]; }
+    __device__ __forceinline__ void set(int i, float x) { reinterpret_cast<float*>(&v)[i] = x; }
+};
+template <> struct Vec16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    uint4 v;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void store(__nv_bfloat16* p) const { *reinterpret_cast<uint4*>(p) = v; }
+    __device__ __forceinline__ float get(int i) const {
+        return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(&v)[i]);
+    }
+    __device__ __forceinline__ void set(int i, float x) {
+        reinterpret_cast<__nv_bfloat16*>(&v)[i] = __float2bfloat16_rn(x);
+    }
+};
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    return x;
+}
+__device__ __forceinline__ float warp_max(float x) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+    return x;
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

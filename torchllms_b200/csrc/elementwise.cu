@@ -1,0 +1,136 @@
+// Embedding gather, residual sum + RMS norm, and the SwiGLU gate.
+//
+// embed:    h[t, :] = float(table[ids[t], :])                 (the residual stream is float32)
+// rmsnorm:  x = h[row] (+ delta[row]);  y = x * rsqrt(mean(x^2) + eps) * w   -- all in float32,
+//           rounded once to the output dtype; with `write_back` the sum x replaces h[row].
+//           The reference normalises in float32 too (torchllms/models/networks.py:195-200).
+// swiglu:   out[t, f] = silu(in[t, f]) * in[t, F + f],  silu(g) = g / (1 + exp(-g)), in float32
+//           (torchllms/models/networks.py:604-605).
+#include "common.cuh"
+
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                             float* __restrict__ out, int dim, int vocab) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // the host rejects such ids; stay in bounds anyway
+    const T* src = table + (size_t)id * dim;
+    float* dst = out + (size_t)t * dim;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = to_float(src[d]);
+}
+
+template <typename TD, typename TO>
+__global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                               const float* __restrict__ weight, TO* __restrict__ out,
+                               const int* __restrict__ rows, int dim, float eps, int write_back) {
+    extern __shared__ float row_buf[];  // the summed row, kept for the second pass
+    __shared__ float warp_part[32];
+    const int o = blockIdx.x;
+    const int r = rows ? rows[o] : o;
+    float* hr = h + (size_t)r * dim;
+    const TD* dr = delta ? delta + (size_t)r * dim : nullptr;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float x = hr[d];
+        if (dr) x += to_float(dr[d]);
+        row_buf[d] = x;
+        ss += x * x;
+    }
+    ss = warp_sum(ss);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    if (lane == 0) warp_part[warp] = ss;
+    __syncthreads();
+    if (warp == 0) {
+        float v = lane < n_warps ? warp_part[lane] : 0.f;
+        v = warp_sum(v);
+        if (lane == 0) warp_part[0] = v;
+    }
+    __syncthreads();
+    const float rstd = rsqrtf(warp_part[0] / (float)dim + eps);
+    TO* orow = out + (size_t)o * dim;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        const float x = row_buf[d];
+        if (write_back) hr[d] = x;
+        orow[d] = from_float<TO>(x * rstd * weight[d]);
+    }
+}
+
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int hidden, long long total) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const long long t = i / hidden;
+        const int f = (int)(i - t * hidden);
+        const float g = to_float(in[t * 2 * hidden + f]);
+        const float u = to_float(in[t * 2 * hidden + hidden + f]);
+        out[i] = from_float<T>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+extern "C" int tl_embed(const int* ids, const void* table, int table_dtype, float* out,
+                        int n_tokens, int dim, int vocab, void* stream) {
+    if (n_tokens <= 0) return TL_OK;
+    if (dim <= 0 || vocab <= 0) return TL_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = dim >= 1024 ? 256 : 128;
+    if (table_dtype == TL_F32)
+        embed_kernel<float><<<n_tokens, threads, 0, s>>>(ids, (const float*)table, out, dim, vocab);
+    else if (table_dtype == TL_BF16)
+        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(ids, (const __nv_bfloat16*)table, out, dim, vocab);
+    else
+        return TL_BAD_DTYPE;
+    TL_LAUNCH_CHECK();
+    return TL_OK;
+}
+
+template <typename TD, typename TO>
+static int launch_rmsnorm(float* h, const void* delta, const float* w, void* out, const int* rows,
+                          int n_out, int dim, float eps, int write_back, cudaStream_t s) {
+    const size_t smem = (size_t)dim * sizeof(float);
+    if (smem > 200 * 1024) return TL_TOO_LARGE;
+    auto kern = rmsnorm_kernel<TD, TO>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+    kern<<<n_out, threads, smem, s>>>(h, (const TD*)delta, w, (TO*)out, rows, dim, eps, write_back);
+    TL_LAUNCH_CHECK();
+    return TL_OK;
+}
+
+// delta may be null (then nothing is added); rows may be null (then row o is row o of h).
+extern "C" int tl_rmsnorm(float* h, const void* delta, int delta_dtype, const float* weight, void* out,
+                          int out_dtype, const int* rows, int n_out, int dim, float eps, int write_back,
+                          void* stream) {
+    if (n_out <= 0) return TL_OK;
+    if (dim <= 0) return TL_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (delta_dtype == TL_F32 && out_dtype == TL_F32)
+        return launch_rmsnorm<float, float>(h, delta, weight, out, rows, n_out, dim, eps, write_back, s);
+    if (delta_dtype == TL_BF16 && out_dtype == TL_BF16)
+        return launch_rmsnorm<__nv_bfloat16, __nv_bfloat16>(h, delta, weight, out, rows, n_out, dim, eps, write_back, s);
+    if (delta_dtype == TL_F32 && out_dtype == TL_BF16)
+        return launch_rmsnorm<float, __nv_bfloat16>(h, delta, weight, out, rows, n_out, dim, eps, write_back, s);
+    if (delta_dtype == TL_BF16 && out_dtype == TL_F32)
+        return launch_rmsnorm<__nv_bfloat16, float>(h, delta, weight, out, rows, n_out, dim, eps, write_back, s);
+    return TL_BAD_DTYPE;
+}
+
+extern "C" int tl_swiglu(const void* in, void* out, int dtype, int n_tokens, int hidden, void* stream) {
+    const long long total = (long long)n_tokens * hidden;
+    if (total <= 0) return TL_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 256;
+    long long blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (dtype == TL_F32)
+        swiglu_kernel<float><<<(int)blocks, threads, 0, s>>>((const float*)in, (float*)out, hidden, total);
+    else if (dtype == TL_BF16)
+        swiglu_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, hidden, total);
+    else
+        return TL_BAD_DTYPE;
+    TL_LAUNCH_CHECK();
+    return TL_OK;
+}

@@ -1,0 +1,231 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+Reference: ``Transformer.forward`` with a paged pool
+(torchllms/models/networks.py:909-1049) builds per-forward index tensors
+(``PagedBatchLayout``, torchllms/models/paged_kv.py:74-111, :486-617), derives
+positions from the pool's lengths (:992-1015), runs the layers and keeps the
+last row of each request (:1030-1045).  Its driver only ever builds whole-prompt
+batches or one-token-per-request batches and requires every live request in
+every forward (:984-990).  Here a step takes any subset of the live requests,
+each with any number of next tokens (a portion of a prompt, or one decoded
+token), runs exactly those tokens as one flat batch against the cache earlier
+steps left, and returns float32 logits at the places asked for.
+
+All index data of a step is packed on the host into one pinned int32 buffer
+with a fixed layout and uploaded with a single copy; the device-side views
+have fixed addresses, which is what CUDA-graph replay of decode steps needs.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, OutOfPages
+from .model import Model
+
+
+class StepError(ValueError):
+    """A step was asked for that cannot run (bad token id, too many tokens, ...)."""
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and which of them want logits.
+
+    ``want`` holds indices into ``tokens``; ``None`` means the last token only."""
+
+    handle: int
+    tokens: Sequence[int]
+    want: Optional[Sequence[int]] = None
+
+
+@dataclass
+class StepContext:
+    """What the parts see of a step (device tensors are views of one uploaded buffer)."""
+
+    n_tokens: int
+    n_seqs: int
+    n_want: int
+    max_q_len: int
+    max_kv_len: int
+    token_ids: torch.Tensor      # [T] int32
+    positions: torch.Tensor      # [T] int32, absolute position of each token in its request
+    seq_of_token: torch.Tensor   # [T] int32, index into the step's requests
+    q_start: torch.Tensor        # [B + 1] int32, first token of each request in the flat batch
+    kv_len: torch.Tensor         # [B] int32, request length after this step
+    state_slot: torch.Tensor     # [B] int32, the request's slot (row of per-request state)
+    fresh: torch.Tensor          # [B] int32, 1 where the portion starts at position 0
+    want_rows: torch.Tensor      # [n_want] int32, flat indices of the tokens whose logits are wanted
+    # host copies, for parts that plan on the host
+    q_lens: List[int] = field(default_factory=list)
+    kv_lens: List[int] = field(default_factory=list)
+    slots: List[int] = field(default_factory=list)
+
+
+class _StepBuffers:
+    """Fixed-layout pinned host buffer and its device twin."""
+
+    def __init__(self, cache: CacheManager, max_tokens: int, device: torch.device):
+        B, T, NB, G = cache.max_num_seqs, max_tokens, cache.max_blocks, len(cache.groups)
+        self.T, self.B, self.NB, self.G = T, B, NB, G
+        off = 0
+        self.sections = {}
+        for name, n in (("token_ids", T), ("positions", T), ("seq_of_token", T), ("want_rows", T),
+                        ("q_start", B + 1), ("kv_len", B), ("state_slot", B), ("fresh", B)):
+            self.sections[name] = (off, n)
+            off += n
+        for g in range(G):
+            self.sections[f"slot_mapping{g}"] = (off, T)
+            off += T
+        for g in range(G):
+            self.sections[f"block_table{g}"] = (off, B * NB)
+            off += B * NB
+        self.total = off
+        pin = device.type == "cuda"
+        self.host = torch.zeros(self.total, dtype=torch.int32, pin_memory=pin)
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(self.total, dtype=torch.int32, device=device)
+        self.copied = torch.cuda.Event() if pin else None
+        self._pending = False
+
+    def host_view(self, name: str) -> np.ndarray:
+        off, n = self.sections[name]
+        return self.host_np[off:off + n]
+
+    def dev_view(self, name: str, n: Optional[int] = None) -> torch.Tensor:
+        off, full = self.sections[name]
+        return self.dev[off:off + (full if n is None else n)]
+
+    def wait_host_free(self) -> None:
+        if self._pending and self.copied is not None:
+            self.copied.synchronize()
+        self._pending = False
+
+    def upload(self, n_seqs: int) -> None:
+        # everything up to the last block-table row in use, in one copy
+        if self.G:
+            off, _ = self.sections[f"block_table{self.G - 1}"]
+            end = off + n_seqs * self.NB
+        else:
+            end = self.sections["fresh"][0] + self.B
+        self.dev[:end].copy_(self.host[:end], non_blocking=True)
+        if self.copied is not None:
+            self.copied.record()
+            self._pending = True
+
+
+class Engine:
+    """A model, its cache, and the step function over them."""
+
+    def __init__(self, model: Model, *, page_size: int = 16, pool_tokens: int, max_num_seqs: int = 64,
+                 max_len: Optional[int] = None, max_step_tokens: int = 8192):
+        self.model = model
+        self.device = model.device
+        self.max_len = int(max_len or model.max_positions)
+        if self.max_len > model.max_positions:
+            raise StepError(f"max_len {self.max_len} exceeds the model's position table ({model.max_positions})")
+        self.max_step_tokens = int(max_step_tokens)
+        self.cache = CacheManager(model.run_needs(), page_size=page_size, pool_tokens=pool_tokens,
+                                  max_num_seqs=max_num_seqs, max_len=self.max_len, dtype=model.dtype,
+                                  device=self.device, max_step_tokens=self.max_step_tokens)
+        self._buf = _StepBuffers(self.cache, self.max_step_tokens, self.device)
+        self.vocab_size = model.spec.vocab_size
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    # ----------------------------------------------------------------- requests
+    def claim(self) -> int:
+        return self.cache.claim()
+
+    def release(self, handle: int) -> None:
+        self.cache.release(handle)
+
+    def can_run(self, wants: Sequence[Tuple[int, int]]) -> bool:
+        return self.cache.can_extend(wants)
+
+    # --------------------------------------------------------------------- step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run the entries' tokens as one batch.  Returns float32 logits
+        ``[n_wanted, vocab]`` on the device, rows in the order of the entries and
+        of each entry's ``want``; ``None`` when nothing was wanted.
+
+        Raises :class:`~torchllms_b200.cache.manager.OutOfPages` (nothing changed)
+        when the pool cannot hold the new tokens."""
+        if not entries:
+            return None
+        q_lens = [len(e.tokens) for e in entries]
+        T, B = sum(q_lens), len(entries)
+        if min(q_lens) <= 0:
+            raise StepError("every entry of a step must bring at least one token")
+        if T > self.max_step_tokens:
+            raise StepError(f"a step may bring at most {self.max_step_tokens} tokens, got {T}")
+        if B > self.cache.max_num_seqs:
+            raise StepError(f"a step may hold at most {self.cache.max_num_seqs} requests, got {B}")
+        flat = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=T)
+        if flat.min() < 0 or flat.max() >= self.vocab_size:
+            bad = int(flat[(flat < 0) | (flat >= self.vocab_size)][0])
+            raise StepError(f"token id {bad} is outside the vocabulary (0..{self.vocab_size - 1})")
+        want_rows: List[int] = []
+        base = 0
+        for e, n in zip(entries, q_lens):
+            want = [n - 1] if e.want is None else list(e.want)
+            for w in want:
+                if not 0 <= w < n:
+                    raise StepError(f"request {e.handle}: wanted place {w} is outside its {n} tokens")
+                want_rows.append(base + w)
+            base += n
+
+        cache = self.cache
+        starts = cache.extend_many([(e.handle, n) for e, n in zip(entries, q_lens)])  # may raise OutOfPages
+        buf = self._buf
+        buf.wait_host_free()
+        q_start = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(q_lens, out=q_start[1:])
+        kv_lens = [s + n for s, n in zip(starts, q_lens)]
+        slots = [cache.slot(e.handle) for e in entries]
+        buf.host_view("token_ids")[:T] = flat
+        pos = buf.host_view("positions")
+        sot = buf.host_view("seq_of_token")
+        for i, (s, n) in enumerate(zip(starts, q_lens)):
+            a = q_start[i]
+            pos[a:a + n] = np.arange(s, s + n)
+            sot[a:a + n] = i
+        buf.host_view("q_start")[:B + 1] = q_start
+        buf.host_view("kv_len")[:B] = kv_lens
+        buf.host_view("state_slot")[:B] = slots
+        buf.host_view("fresh")[:B] = [1 if s == 0 else 0 for s in starts]
+        buf.host_view("want_rows")[:len(want_rows)] = want_rows
+        for g in range(len(cache.groups)):
+            sm = buf.host_view(f"slot_mapping{g}")
+            for i, (e, s, n) in enumerate(zip(entries, starts, q_lens)):
+                a = q_start[i]
+                sm[a:a + n] = cache.slot_mapping(g, e.handle, s, n)
+            bt = buf.host_view(f"block_table{g}")[:B * buf.NB].reshape(B, buf.NB)
+            bt[:] = cache.block_table_rows(g, slots)
+        buf.upload(B)
+
+        ctx = StepContext(
+            n_tokens=T, n_seqs=B, n_want=len(want_rows), max_q_len=max(q_lens), max_kv_len=max(kv_lens),
+            token_ids=buf.dev_view("token_ids", T), positions=buf.dev_view("positions", T),
+            seq_of_token=buf.dev_view("seq_of_token", T), q_start=buf.dev_view("q_start", B + 1),
+            kv_len=buf.dev_view("kv_len", B), state_slot=buf.dev_view("state_slot", B),
+            fresh=buf.dev_view("fresh", B), want_rows=buf.dev_view("want_rows", len(want_rows)),
+            q_lens=q_lens, kv_lens=kv_lens, slots=slots)
+        block_tables = [buf.dev_view(f"block_table{g}", B * buf.NB).view(B, buf.NB) for g in range(len(cache.groups))]
+        slot_maps = [buf.dev_view(f"slot_mapping{g}", T) for g in range(len(cache.groups))]
+        views = [cache.run_view(i, block_tables, slot_maps) for i in range(cache.n_runs)]
+        try:
+            logits = self.model.forward(ctx, views)
+        except BaseException:
+            for e, s in zip(entries, starts):  # leave the cache as the step found it
+                cache.truncate(e.handle, s)
+            raise
+        for e in entries:
+            cache.pass_window(e.handle)
+        self.steps_run += 1
+        self.tokens_run += T
+        return logits

@@ -1,0 +1,277 @@
+"""ctypes front end of the CUDA kernels: argument checks, output allocation, launches.
+
+Every method checks dtype, device, contiguity and the sizes its kernel supports
+and raises :class:`KernelError` with the reason; a size a kernel cannot handle
+is refused, never computed wrongly.  Launches go to PyTorch's current stream,
+so they order with PyTorch's own work and can be captured into CUDA graphs.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .build import ALL_LIBRARIES, build_libraries, load_library
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+_STATUS = {
+    -1: "unsupported dtype",
+    -2: "unsupported size",
+    -3: "misaligned pointer",
+    -4: "needs more shared memory or scratch than available",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc < 0:
+        raise KernelError(f"{what}: {_STATUS.get(rc, 'error ' + str(rc))}")
+    raise KernelError(f"{what}: CUDA error {rc} ({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no GPU'})")
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _cuda_contig(t: torch.Tensor, name: str, dtype=None) -> None:
+    _need(t.is_cuda, f"{name} must live on the GPU (there is no CPU implementation)")
+    _need(t.is_contiguous(), f"{name} must be contiguous")
+    if dtype is not None:
+        _need(t.dtype == dtype, f"{name} must be {dtype}, got {t.dtype}")
+
+
+class NativeOps:
+    """The kernels as methods.  Libraries are compiled and loaded on first use."""
+
+    name = "native-sm100a"
+
+    def __init__(self):
+        if not torch.cuda.is_available():
+            raise KernelError(
+                "torchllms_b200 runs on a CUDA GPU (sm_100a) only: torch.cuda.is_available() is False "
+                "and there is no CPU implementation")
+        self._workspace: Dict[Tuple[int, str], torch.Tensor] = {}
+        self._mm_out_dtype: Optional[bool] = None
+
+    # ------------------------------------------------------------ libraries
+    def prepare(self, dtype: torch.dtype, sampling: bool = True) -> None:
+        """Compile, side by side, what a model of this dtype will call."""
+        names = ["elementwise", "rope", "attention", "gemm_simt"]
+        if sampling:
+            names.append("sampling")
+        build_libraries(names)
+
+    def _lib(self, name: str):
+        return load_library(name)
+
+    # ------------------------------------------------------------- checks
+    def check_attention_sizes(self, n_heads: int, n_kv_heads: int, head_dim: int, dtype: torch.dtype) -> None:
+        _need(dtype in _DT, f"attention supports float32 and bfloat16, not {dtype}")
+        _need(n_heads > 0 and n_kv_heads > 0 and n_heads % n_kv_heads == 0,
+              f"n_heads ({n_heads}) must be a positive multiple of n_kv_heads ({n_kv_heads})")
+        _need(head_dim % 16 == 0 and 16 <= head_dim <= 256,
+              f"head_dim must be a multiple of 16 between 16 and 256, got {head_dim}")
+
+    # ------------------------------------------------------------ elementwise
+    def embed(self, token_ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+        _cuda_contig(token_ids, "token_ids", torch.int32)
+        _cuda_contig(table, "embedding table")
+        _need(table.dtype in _DT and table.dim() == 2, "embedding table must be a float32/bfloat16 matrix")
+        n, (vocab, dim) = token_ids.numel(), table.shape
+        out = torch.empty((n, dim), dtype=torch.float32, device=table.device)
+        rc = self._lib("elementwise").tl_embed(_ptr(token_ids), _ptr(table), _DT[table.dtype], _ptr(out),
+                                              n, dim, vocab, _stream())
+        _check(rc, "embed")
+        return out
+
+    def rmsnorm(self, h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _cuda_contig(h, "residual stream", torch.float32)
+        _cuda_contig(weight, "norm weight", torch.float32)
+        _need(h.dim() == 2 and weight.numel() == h.shape[1], "norm weight must match the stream's width")
+        _need(out_dtype in _DT, f"norm output dtype {out_dtype} unsupported")
+        dim = h.shape[1]
+        _need(dim * 4 <= 200 * 1024, f"rmsnorm keeps a row in shared memory: width {dim} exceeds 51200")
+        if delta is not None:
+            _cuda_contig(delta, "delta")
+            _need(delta.shape == h.shape and delta.dtype in _DT, "delta must have the stream's shape")
+        if rows is not None:
+            _cuda_contig(rows, "rows", torch.int32)
+        n_out = h.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n_out, dim), dtype=out_dtype, device=h.device)
+        write_back = 1 if (delta is not None and rows is None) else 0
+        rc = self._lib("elementwise").tl_rmsnorm(
+            _ptr(h), _ptr(delta), _DT[delta.dtype] if delta is not None else 0, _ptr(weight), _ptr(out),
+            _DT[out_dtype], _ptr(rows), n_out, dim, ctypes.c_float(eps), write_back, _stream())
+        _check(rc, "rmsnorm")
+        return out
+
+    def swiglu(self, gate_up: torch.Tensor) -> torch.Tensor:
+        _cuda_contig(gate_up, "gate_up")
+        _need(gate_up.dim() == 2 and gate_up.shape[1] % 2 == 0 and gate_up.dtype in _DT,
+              "swiglu input must be [tokens, 2 * hidden] in float32/bfloat16")
+        n, hidden = gate_up.shape[0], gate_up.shape[1] // 2
+        out = torch.empty((n, hidden), dtype=gate_up.dtype, device=gate_up.device)
+        rc = self._lib("elementwise").tl_swiglu(_ptr(gate_up), _ptr(out), _DT[gate_up.dtype], n, hidden, _stream())
+        _check(rc, "swiglu")
+        return out
+
+    # ------------------------------------------------------------------ linear
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``x [M, K] @ w[N, K]^T``.  float32 runs on the CUDA cores (true 32-bit);
+        bfloat16 uses the library product, as the reference's ``nn.Linear`` does."""
+        _cuda_contig(x, "linear input")
+        _cuda_contig(w, "linear weight")
+        _need(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], "linear: inner sizes differ")
+        _need(x.dtype == w.dtype and x.dtype in _DT, f"linear: dtypes {x.dtype} / {w.dtype} unsupported")
+        out_dtype = out_dtype or x.dtype
+        M, K = x.shape
+        N = w.shape[0]
+        if x.dtype == torch.float32:
+            _need(out_dtype == torch.float32, "a float32 product has float32 output")
+            return self.gemm_simt(x, w, torch.float32)
+        if out_dtype == torch.bfloat16:
+            return torch.mm(x, w.t())
+        _need(out_dtype == torch.float32, f"linear: output dtype {out_dtype} unsupported")
+        if self._mm_out_dtype is None:
+            try:
+                torch.mm(x[:1], w[:8].t(), out_dtype=torch.float32)
+                self._mm_out_dtype = True
+            except (TypeError, RuntimeError):
+                self._mm_out_dtype = False
+        if self._mm_out_dtype:
+            return torch.mm(x, w.t(), out_dtype=torch.float32)
+        return self.gemm_simt(x, w, torch.float32)
+
+    def gemm_simt(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        _cuda_contig(x, "gemm input")
+        _cuda_contig(w, "gemm weight")
+        _need(x.shape[1] == w.shape[1] and x.dtype == w.dtype and x.dtype in _DT, "gemm_simt: operands disagree")
+        M, K = x.shape
+        N = w.shape[0]
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        rc = self._lib("gemm_simt").tl_gemm_simt(_ptr(x), _ptr(w), _ptr(out), _DT[x.dtype], _DT[out_dtype],
+                                                M, N, K, _stream())
+        _check(rc, "gemm_simt")
+        return out
+
+    # -------------------------------------------------------------------- rope
+    def rope_kv_write(self, qkv: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, *,
+                      n_heads: int, n_kv_heads: int, head_dim: int, interleaved: bool,
+                      k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                      slot_mapping: Optional[torch.Tensor], page_size: int) -> torch.Tensor:
+        _cuda_contig(qkv, "qkv")
+        _cuda_contig(positions, "positions", torch.int32)
+        _cuda_contig(table, "rotary table", torch.float32)
+        T = qkv.shape[0]
+        _need(qkv.dim() == 2 and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim and qkv.dtype in _DT,
+              "qkv must be [tokens, (n_heads + 2 n_kv_heads) * head_dim]")
+        _need(table.dim() == 3 and table.shape[1] == head_dim // 2 and table.shape[2] == 2,
+              "rotary table must be [positions, head_dim / 2, 2]")
+        _need(positions.numel() == T, "one position per token")
+        if k_pages is not None:
+            _cuda_contig(k_pages, "k_pages", qkv.dtype)
+            _cuda_contig(v_pages, "v_pages", qkv.dtype)
+            _cuda_contig(slot_mapping, "slot_mapping", torch.int32)
+            _need(k_pages.shape[1:] == (n_kv_heads, page_size, head_dim) and v_pages.shape == k_pages.shape,
+                  "pages must be [pages, n_kv_heads, page_size, head_dim]")
+            _need(slot_mapping.numel() == T, "one cache slot per token")
+        q = torch.empty((T, n_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+        rc = self._lib("rope").tl_rope_kv_write(
+            _ptr(qkv), _ptr(positions), _ptr(table), _ptr(slot_mapping if k_pages is not None else None),
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _DT[qkv.dtype], T, n_heads, n_kv_heads, head_dim,
+            page_size, table.shape[0], 1 if interleaved else 0, _stream())
+        _check(rc, "rope_kv_write")
+        return q
+
+    # --------------------------------------------------------------- attention
+    def _scratch(self, device: torch.device, floats: int, tag: str = "attention") -> Optional[torch.Tensor]:
+        if floats <= 0:
+            return None
+        key = (device.index or 0, tag)
+        buf = self._workspace.get(key)
+        if buf is None or buf.numel() < floats:
+            buf = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+            self._workspace[key] = buf
+        return buf
+
+    def paged_attention(self, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                        block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor, *,
+                        n_seqs: int, max_q_len: int, max_kv_len: int, scale: float,
+                        window: Optional[int], page_size: int, allow_split: bool = True) -> torch.Tensor:
+        _cuda_contig(q, "q")
+        _cuda_contig(k_pages, "k_pages", q.dtype)
+        _cuda_contig(v_pages, "v_pages", q.dtype)
+        _cuda_contig(q_start, "q_start", torch.int32)
+        _cuda_contig(kv_len, "kv_len", torch.int32)
+        _need(block_table.is_cuda and block_table.dtype == torch.int32 and block_table.dim() == 2
+              and block_table.stride(1) == 1, "block_table must be an int32 matrix with unit column stride")
+        T, n_heads, head_dim = q.shape
+        n_kv_heads = k_pages.shape[1]
+        self.check_attention_sizes(n_heads, n_kv_heads, head_dim, q.dtype)
+        _need(k_pages.shape[2] == page_size and k_pages.shape[3] == head_dim and v_pages.shape == k_pages.shape,
+              "pages must be [pages, n_kv_heads, page_size, head_dim]")
+        _need(block_table.shape[0] >= n_seqs and q_start.numel() >= n_seqs + 1 and kv_len.numel() >= n_seqs,
+              "block_table, q_start and kv_len must cover every request of the step")
+        _need(block_table.shape[1] * page_size >= max_kv_len, "block_table is too narrow for max_kv_len")
+        lib = self._lib("attention")
+        n_splits = ctypes.c_int(0)
+        floats = ctypes.c_longlong(0)
+        rc = lib.tl_attention_plan(T, n_seqs, n_heads, n_kv_heads, head_dim, max_q_len, max_kv_len,
+                                   1 if allow_split else 0, ctypes.byref(n_splits), ctypes.byref(floats))
+        _check(rc, "attention_plan")
+        ws = self._scratch(q.device, floats.value)
+        out = torch.empty_like(q)
+        rc = lib.tl_paged_attention(
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
+            _ptr(q_start), _ptr(kv_len), _ptr(ws), _DT[q.dtype], T, n_seqs, n_heads, n_kv_heads, head_dim,
+            page_size, max_q_len, max_kv_len, int(window or 0), ctypes.c_float(scale),
+            1 if allow_split else 0, _stream())
+        _check(rc, "paged_attention")
+        return out
+
+    # ---------------------------------------------------------------- sampling
+    def sample(self, logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+               top_k: Optional[torch.Tensor] = None, row_keys: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Next token of every row.  ``temperature`` (float32), ``top_k`` (int32) and
+        ``row_keys`` (int64 holding the 64-bit key) are per row; without a temperature
+        every row is greedy."""
+        _need(logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1,
+              "logits must be a float32 matrix on the GPU with unit column stride")
+        n, vocab = logits.shape
+        if temperature is not None:
+            _cuda_contig(temperature, "temperature", torch.float32)
+            _need(row_keys is not None, "sampling with a temperature needs row keys")
+            _cuda_contig(row_keys, "row_keys", torch.int64)
+            _need(temperature.numel() == n and row_keys.numel() == n, "one temperature and key per row")
+        if top_k is not None:
+            _cuda_contig(top_k, "top_k", torch.int32)
+            _need(top_k.numel() == n, "one top_k per row")
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+        rc = self._lib("sampling").tl_sample(
+            _ptr(logits), ctypes.c_longlong(logits.stride(0)), n, vocab, _ptr(temperature), _ptr(top_k),
+            _ptr(row_keys), _ptr(out), _stream())
+        _check(rc, "sample")
+        return out
+
+
+def build_all() -> None:
+    """Compile every kernel library (what ``__graft_entry__.build`` calls)."""
+    build_libraries(ALL_LIBRARIES)
