@@ -1,0 +1,72 @@
+"""The engine's host side (cache, step function, replay) on the CPU over the plain PyTorch twins
+of the kernels: every way of cutting and batching must reproduce the plain implementation."""
+
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import traces
+from helpers import TINY, tiny_folder
+from plain_llama import PlainModel
+from torch_ops import TorchOps
+from torchllms_b200.engine.replay import Replayer
+
+LENGTHS = {"A": [1, 7, 33, 64, 97, 50, 120, 20, 3, 70], "B": [2, 5, 17, 40, 100, 65, 129, 30, 90]}
+# The plain implementation itself sits about 1.3e-5 from a float64 evaluation of these
+# (deliberately peaked) models, so float32 paths that sum in another order differ by a few 1e-5.
+ATOL = 1e-4
+
+
+@pytest.fixture(scope="module")
+def setups(tmp_path_factory):
+    out = {}
+    for name, (cfg, seed, page) in TINY.items():
+        folder = tiny_folder(tmp_path_factory.mktemp(name), name)
+        rng = random.Random(seed)
+        reqs = {f"r{i}": [rng.randrange(cfg["vocab_size"]) for _ in range(n)] for i, n in enumerate(LENGTHS[name])}
+        plain = PlainModel(folder)
+        out[name] = (folder, page, reqs, {rid: plain.logits(t).numpy() for rid, t in reqs.items()})
+    return out
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("mode", ["whole", "tail_one_by_one", "portions", "mixed"])
+def test_cuts_agree_with_plain(setups, name, mode):
+    folder, page, reqs, ref = setups[name]
+    steps, places, peak = getattr(traces, mode)(reqs)
+    rp = Replayer(folder, "float32", peak, page_size=page, device="cpu", ops=TorchOps())
+    for s in steps:
+        got = rp.run_step(s)
+        rp.engine.cache.check_invariants()
+        if s["step"] in places:
+            want = np.stack([ref[rid][pos] for rid, pos in places[s["step"]]])
+            assert np.abs(got - want).max() < ATOL, (mode, s["step"])
+        else:
+            assert got is None
+    assert rp.engine.cache.n_live() == 0
+    assert rp.engine.cache.free_pages() == rp.engine.cache.groups[0].allocator.n_pages
+    if mode == "mixed":
+        # the pool was sized to the peak, so pages must have been used again
+        assert sum(-(-len(t) // page) for t in reqs.values()) > rp.engine.cache.groups[0].allocator.n_pages
+
+
+def test_step_rejects_bad_input(setups):
+    from torchllms_b200.engine.step import StepEntry, StepError
+    from torchllms_b200.cache.manager import OutOfPages
+    folder, page, reqs, _ = setups["A"]
+    rp = Replayer(folder, "float32", 64, page_size=page, device="cpu", ops=TorchOps())
+    eng = rp.engine
+    h = eng.claim()
+    with pytest.raises(StepError):
+        eng.step([StepEntry(h, [512])])                  # outside the vocabulary
+    with pytest.raises(StepError):
+        eng.step([StepEntry(h, [])])
+    with pytest.raises(StepError):
+        eng.step([StepEntry(h, [1, 2], want=[2])])
+    eng.step([StepEntry(h, list(range(60)))])
+    with pytest.raises(OutOfPages):
+        eng.step([StepEntry(h, list(range(10)))])        # 70 tokens do not fit 64
+    assert eng.cache.length(h) == 60                     # nothing changed
+    eng.cache.check_invariants()

@@ -1,0 +1,310 @@
+"""Each CUDA kernel alone against its plain PyTorch twin, at sizes other than the engine's."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from torch_ops import TorchOps, mix64, noise_row
+
+pytestmark = pytest.mark.gpu
+
+TWIN = TorchOps()
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from torchllms_b200.kernels import get_ops
+    return get_ops()
+
+
+def tol(dtype, f32=1e-5, bf16=2e-2):
+    return f32 if dtype == torch.float32 else bf16
+
+
+def rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).cuda()
+
+
+# ------------------------------------------------------------------------------ elementwise
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,dim,n", [(37, 24, 5), (1000, 96, 64), (50, 4100, 3)])
+def test_embed(ops, dtype, vocab, dim, n):
+    table = rand((vocab, dim), dtype, 1)
+    ids = torch.randint(0, vocab, (n,), dtype=torch.int32).cuda()
+    ids[0], ids[-1] = vocab - 1, 0
+    out = ops.embed(ids, table)
+    assert out.dtype == torch.float32
+    assert torch.equal(out, TWIN.embed(ids, table))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,dim", [(1, 16), (7, 96), (33, 4096), (3, 5000), (2, 20000)])
+@pytest.mark.parametrize("eps", [1e-5, 1e-2])
+def test_rmsnorm_with_and_without_delta(ops, dtype, n, dim, eps):
+    h = rand((n, dim), torch.float32, 2, 3.0)
+    delta = rand((n, dim), dtype, 3)
+    w = 1 + 0.1 * rand((dim,), torch.float32, 4)
+    for d in (None, delta):
+        h1, h2 = h.clone(), h.clone()
+        got = ops.rmsnorm(h1, d, w, eps, out_dtype=dtype)
+        want = TWIN.rmsnorm(h2, d, w, eps, out_dtype=dtype)
+        assert got.dtype == dtype
+        torch.testing.assert_close(got.float(), want.float(), atol=tol(dtype, 2e-5), rtol=tol(dtype, 1e-5, 1e-2))
+        # the sum replaced the stream (exactly: it is one float32 addition per element)
+        assert torch.equal(h1, h2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm_rows_leaves_stream_alone(ops, dtype):
+    h = rand((19, 200), torch.float32, 5)
+    delta = rand((19, 200), dtype, 6)
+    w = rand((200,), torch.float32, 7)
+    rows = torch.tensor([18, 0, 7, 7], dtype=torch.int32).cuda()
+    before = h.clone()
+    got = ops.rmsnorm(h, delta, w, 1e-6, out_dtype=dtype, rows=rows)
+    want = TWIN.rmsnorm(before.clone(), delta, w, 1e-6, out_dtype=dtype, rows=rows)
+    assert torch.equal(h, before)
+    torch.testing.assert_close(got.float(), want.float(), atol=tol(dtype, 2e-5), rtol=tol(dtype, 1e-5, 1e-2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,hidden", [(1, 8), (5, 192), (64, 1000), (3, 14336)])
+def test_swiglu(ops, dtype, n, hidden):
+    x = rand((n, 2 * hidden), dtype, 8, 3.0)
+    got, want = ops.swiglu(x), TWIN.swiglu(x)
+    torch.testing.assert_close(got.float(), want.float(), atol=tol(dtype, 1e-5), rtol=tol(dtype, 1e-5, 1e-2))
+
+
+# ------------------------------------------------------------------------------------ gemm
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (1, 1000, 96), (7, 65, 17), (64, 64, 16), (65, 129, 100),
+                                   (200, 96, 4096), (3, 512, 14336)])
+def test_gemm_simt_float32_is_true_32bit(ops, M, N, K):
+    x, w = rand((M, K), torch.float32, 9), rand((N, K), torch.float32, 10)
+    got = ops.linear(x, w)
+    want = (x.double() @ w.double().t())
+    err = (got.double() - want).abs().max().item()
+    scale = want.abs().max().item() + 1e-6
+    # float32 accumulation error grows like sqrt(K) * eps; a tf32 or bf16 product would be 1e-3 off
+    assert err / scale < 2e-6 * math.sqrt(K) + 1e-6, (err, scale)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1000, 96), (7, 65, 17), (33, 130, 200)])
+@pytest.mark.parametrize("out_dtype", DTYPES)
+def test_gemm_simt_bfloat16_operands(ops, M, N, K, out_dtype):
+    x, w = rand((M, K), torch.bfloat16, 11), rand((N, K), torch.bfloat16, 12)
+    got = ops.gemm_simt(x, w, out_dtype)
+    want = TWIN.gemm_simt(x, w, out_dtype)
+    torch.testing.assert_close(got.float(), want.float(), atol=tol(out_dtype, 1e-4, 5e-2), rtol=tol(out_dtype, 1e-5, 1e-2))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1000, 96), (5, 128, 64), (300, 200, 264)])
+def test_linear_bfloat16(ops, M, N, K):
+    x, w = rand((M, K), torch.bfloat16, 13), rand((N, K), torch.bfloat16, 14)
+    for out_dtype in DTYPES:
+        got = ops.linear(x, w, out_dtype=out_dtype)
+        assert got.dtype == out_dtype
+        want = x.float() @ w.float().t()
+        torch.testing.assert_close(got.float(), want, atol=tol(out_dtype, 1e-3, 8e-2), rtol=tol(out_dtype, 1e-4, 1e-2))
+
+
+# ------------------------------------------------------------------------------------ rope
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KV,hd,P", [(4, 2, 16, 16), (3, 1, 32, 8), (5, 5, 48, 4), (32, 8, 128, 16)])
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_rope_kv_write(ops, dtype, H, KV, hd, P, interleaved):
+    T, n_pages, max_pos = 37, 12, 300
+    qkv = rand((T, (H + 2 * KV) * hd), dtype, 15)
+    pos = torch.randint(0, max_pos, (T,), dtype=torch.int32).cuda()
+    ang = torch.arange(max_pos).float()[:, None] * (1.0 / 100 ** (torch.arange(hd // 2).float() / (hd // 2)))[None, :]
+    table = torch.stack([ang.cos(), ang.sin()], -1).contiguous().cuda()
+    slots = torch.randperm(n_pages * P)[:T].to(torch.int32).cuda()
+    pages = [torch.full((n_pages, KV, P, hd), 7.0, dtype=dtype).cuda() for _ in range(4)]
+    kw = dict(n_heads=H, n_kv_heads=KV, head_dim=hd, interleaved=interleaved, slot_mapping=slots, page_size=P)
+    q1 = ops.rope_kv_write(qkv, pos, table, k_pages=pages[0], v_pages=pages[1], **kw)
+    q2 = TWIN.rope_kv_write(qkv, pos, table, k_pages=pages[2], v_pages=pages[3], **kw)
+    a = tol(dtype, 1e-5, 2e-2)
+    torch.testing.assert_close(q1.float(), q2.float(), atol=a, rtol=a)
+    torch.testing.assert_close(pages[0].float(), pages[2].float(), atol=a, rtol=a)
+    assert torch.equal(pages[1], pages[3])          # values are copied bit for bit
+    assert (pages[0] == 7.0).any()                   # untouched slots stay untouched
+    # a run that reads another run's cache writes nothing
+    q3 = ops.rope_kv_write(qkv, pos, table, k_pages=None, v_pages=None, **kw)
+    assert torch.equal(q1, q3)
+
+
+# ------------------------------------------------------------------------------- attention
+
+def build_paged(seq_lens, q_lens, H, KV, hd, P, dtype, seed, n_extra_pages=3, peak=None):
+    """Random queries and a shuffled page pool holding random keys/values for each request."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(seq_lens)
+    blocks = [-(-L // P) for L in seq_lens]
+    n_pages = sum(blocks) + n_extra_pages
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    max_blocks = max(blocks) + 2
+    table = torch.full((B, max_blocks), -1, dtype=torch.int32)
+    k_pages = torch.randn((n_pages, KV, P, hd), generator=g)
+    v_pages = torch.randn((n_pages, KV, P, hd), generator=g)
+    it = iter(perm)
+    for b in range(B):
+        for j in range(blocks[b]):
+            table[b, j] = next(it)
+    T = sum(q_lens)
+    q = torch.randn((T, H, hd), generator=g)
+    q_start = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
+    if peak is not None:
+        # make one far key dominate: the query of (request b, head h) becomes a multiple of that key
+        b, key_pos, boost = peak
+        page, slot = table[b, key_pos // P].item(), key_pos % P
+        for h in range(H):
+            q[q_start[b]:q_start[b + 1], h] = boost * k_pages[page, h // (H // KV), slot]
+    dev = lambda t: t.cuda()
+    return dict(q=dev(q.to(dtype)), k_pages=dev(k_pages.to(dtype)), v_pages=dev(v_pages.to(dtype)),
+                block_table=dev(table), q_start=dev(q_start),
+                kv_len=dev(torch.tensor(seq_lens, dtype=torch.int32)), n_seqs=B,
+                max_q_len=max(q_lens), max_kv_len=max(seq_lens), page_size=P)
+
+
+ATTN_CASES = [
+    # seq_lens, q_lens, H, KV, hd, P, window
+    ([5], [5], 4, 2, 16, 16, None),                       # one short prompt
+    ([33, 1, 64, 7], [33, 1, 64, 7], 4, 2, 16, 16, None), # whole prompts, ragged
+    ([40, 100, 17], [1, 1, 1], 3, 1, 32, 8, None),        # decode, group of 3
+    ([90, 41, 64, 130], [24, 1, 2, 1], 3, 1, 32, 8, None),  # portions beside decoded tokens
+    ([70, 9], [70, 3], 6, 2, 48, 4, None),                # head_dim 48, page 4
+    ([300, 257], [300, 1], 8, 2, 64, 16, None),
+    ([129, 50], [2, 50], 32, 8, 128, 16, None),           # the 8B head layout
+    ([77], [5], 20, 1, 16, 16, None),                     # 20 query heads on one kv head (> 16 rows)
+    ([100, 60], [100, 1], 2, 2, 256, 32, None),           # head_dim 256, no grouping
+    ([200, 90, 33], [200, 1, 5], 4, 2, 32, 8, 17),        # sliding window over page edges
+    ([64, 65], [64, 1], 4, 4, 16, 16, 16),                # window exactly one page
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ATTN_CASES, ids=[str(i) for i in range(len(ATTN_CASES))])
+def test_paged_attention_matches_twin(ops, dtype, case):
+    seq_lens, q_lens, H, KV, hd, P, window = case
+    a = build_paged(seq_lens, q_lens, H, KV, hd, P, dtype, seed=len(seq_lens) * 100 + hd)
+    scale = hd ** -0.5
+    got = ops.paged_attention(**a, scale=scale, window=window)
+    want = TWIN.paged_attention(**a, scale=scale, window=window)
+    t = tol(dtype, 2e-5, 2e-2)
+    torch.testing.assert_close(got.float(), want.float(), atol=t, rtol=t)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("B,L", [(1, 2000), (2, 777), (3, 4100)])
+def test_decode_attention_split_over_keys(ops, dtype, B, L):
+    """Few long requests: the key range is split over CTAs and merged; same answer as unsplit."""
+    lens = [L - 13 * i for i in range(B)]
+    a = build_paged(lens, [1] * B, 8, 2, 64, 16, dtype, seed=L)
+    split = ops.paged_attention(**a, scale=0.125, window=None, allow_split=True)
+    whole = ops.paged_attention(**a, scale=0.125, window=None, allow_split=False)
+    want = TWIN.paged_attention(**a, scale=0.125, window=None)
+    t = tol(dtype, 2e-5, 2e-2)
+    torch.testing.assert_close(split.float(), want.float(), atol=t, rtol=t)
+    torch.testing.assert_close(whole.float(), want.float(), atol=t, rtol=t)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("key_pos", [0, 15, 16, 511, 640])
+def test_attention_finds_one_far_key_among_hundreds(ops, dtype, key_pos):
+    """Random scores hide a dropped key; here one key takes nearly all the weight, so the output
+    must equal that key's value."""
+    L, H, KV, hd, P = 700, 4, 2, 32, 16
+    a = build_paged([L, 40], [1, 1], H, KV, hd, P, dtype, seed=key_pos, peak=(0, key_pos, 6.0))
+    got = ops.paged_attention(**a, scale=hd ** -0.5, window=None).float()
+    page, slot = a["block_table"][0, key_pos // P].item(), key_pos % P
+    for h in range(H):
+        v = a["v_pages"][page, h // (H // KV), slot].float()
+        assert (got[0, h] - v).abs().max().item() < 0.05, (h, (got[0, h] - v).abs().max().item())
+    want = TWIN.paged_attention(**a, scale=hd ** -0.5, window=None).float()
+    t = tol(dtype, 2e-5, 2e-2)
+    torch.testing.assert_close(got, want, atol=t, rtol=t)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_window_edge_is_exact(ops, dtype):
+    """The key just outside the window gets a huge score: if the edge were off by one it would
+    take over the output."""
+    L, H, KV, hd, P, w = 100, 2, 1, 16, 8, 24
+    for edge_inside in (False, True):
+        key_pos = (L - 1) - w + (1 if edge_inside else 0)   # last query sits at L - 1
+        a = build_paged([L], [1], H, KV, hd, P, dtype, seed=3, peak=(0, key_pos, 8.0))
+        got = ops.paged_attention(**a, scale=hd ** -0.5, window=w).float()
+        page, slot = a["block_table"][0, key_pos // P].item(), key_pos % P
+        v = a["v_pages"][page, 0, slot].float()
+        close = (got[0, 0] - v).abs().max().item() < 0.05
+        assert close == edge_inside
+        want = TWIN.paged_attention(**a, scale=hd ** -0.5, window=w).float()
+        torch.testing.assert_close(got, want, atol=tol(dtype, 2e-5, 2e-2), rtol=tol(dtype, 2e-5, 2e-2))
+
+
+def test_attention_refuses_sizes_it_cannot_do(ops):
+    from torchllms_b200.kernels.native import KernelError
+    with pytest.raises(KernelError):
+        ops.check_attention_sizes(4, 2, 24, torch.float32)     # head_dim no multiple of 16
+    with pytest.raises(KernelError):
+        ops.check_attention_sizes(4, 3, 32, torch.float32)     # heads no multiple of kv heads
+    with pytest.raises(KernelError):
+        ops.check_attention_sizes(4, 2, 512, torch.bfloat16)   # too wide
+    with pytest.raises(KernelError):
+        ops.embed(torch.zeros(3, dtype=torch.int32), torch.zeros(4, 4))  # CPU tensors
+
+
+# -------------------------------------------------------------------------------- sampling
+
+def test_greedy_is_first_argmax(ops):
+    logits = rand((9, 1000), torch.float32, 20)
+    logits[3, 17] = logits[3, 900] = 50.0    # a tie: the lower index wins
+    logits[4, 999] = 60.0
+    got = ops.sample(logits)
+    assert got.tolist() == torch.argmax(logits, -1).tolist()
+    assert got[3].item() == 17 and got[4].item() == 999
+
+
+@pytest.mark.parametrize("vocab", [50, 1000, 128256])
+def test_sampling_matches_twin(ops, vocab):
+    n = 6
+    logits = rand((n, vocab), torch.float32, 21, 2.0)
+    temp = torch.tensor([0.0, 0.7, 1.0, 1.3, 0.8, 1e-7], dtype=torch.float32).cuda()
+    top_k = torch.tensor([0, 0, 5, vocab + 3, 1, 0], dtype=torch.int32).cuda()
+    keys = torch.tensor([mix64(i + 77) - (1 << 63) for i in range(n)], dtype=torch.int64).cuda()
+    got = ops.sample(logits, temp, top_k, keys).tolist()
+    want = TWIN.sample(logits, temp, top_k, keys).tolist()
+    # log differs by an ulp between the GPU and numpy: accept the GPU's choice if its twin score is the best within 1e-4
+    for r in range(n):
+        if got[r] != want[r]:
+            t = max(float(temp[r]), 1e-5)
+            score = logits[r].cpu().numpy() / np.float32(t) + noise_row(int(keys[r]) & ((1 << 64) - 1), vocab)
+            assert abs(score[got[r]] - score[want[r]]) < 1e-4 * max(1.0, abs(score[want[r]]))
+    assert got[0] == int(torch.argmax(logits[0]))       # temperature 0 is greedy
+    assert got[4] == int(torch.argmax(logits[4]))       # top-1 is greedy
+    assert got[5] == int(torch.argmax(logits[5]))       # a vanishing temperature is clamped, hence greedy
+
+
+def test_sampling_follows_the_softmax(ops):
+    """Frequencies over many keys approach softmax(logits / T), and top-k never leaves its set."""
+    vocab, n = 12, 20000
+    base = torch.tensor([2.0, 1.0, 0.5, 0.0, -0.5, -1.0, 1.5, -3.0, 0.2, 0.1, -0.1, 0.7])
+    logits = base[None, :].repeat(n, 1).cuda()
+    temp = torch.full((n,), 0.8, dtype=torch.float32).cuda()
+    keys = torch.tensor([mix64(1234567 * i + 1) - (1 << 63) for i in range(n)], dtype=torch.int64).cuda()
+    got = ops.sample(logits, temp, None, keys).cpu().numpy()
+    freq = np.bincount(got, minlength=vocab) / n
+    p = torch.softmax(base / 0.8, -1).numpy()
+    assert np.abs(freq - p).max() < 4 * np.sqrt(p.max() / n) + 2e-3
+    top_k = torch.full((n,), 3, dtype=torch.int32).cuda()
+    got3 = ops.sample(logits, temp, top_k, keys).cpu().numpy()
+    assert set(np.unique(got3)) <= {0, 1, 6}
+    p3 = torch.softmax(base[[0, 1, 6]] / 0.8, -1).numpy()
+    f3 = np.array([(got3 == i).mean() for i in (0, 1, 6)])
+    assert np.abs(f3 - p3).max() < 0.02

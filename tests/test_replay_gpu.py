@@ -1,0 +1,89 @@
+"""Trace replay through bin/trace_run against the plain implementation: every way of cutting
+and batching gives the same logits, in 32-bit and in bfloat16."""
+
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import traces
+from helpers import TINY, tiny_folder
+from helpers import run_trace
+from plain_llama import PlainModel
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [1, 7, 33, 64, 97, 120, 50], "B": [2, 5, 17, 40, 100, 200, 65, 129]}
+# float32: the reference's own gate is 1e-3 (torchllms/inference/validate_qwen3.py:579-584); these
+# models are tiny, so a tenth of it.  bfloat16: weights are stored in bfloat16 and read exactly by
+# both sides; what differs is the rounding of activations to 8 bits between kernels (about 0.4 %
+# each, a few dozen of them), measured against the spread of the logits.
+F32_ATOL = 1e-4
+BF16_REL = 0.04
+
+
+def requests_for(name):
+    cfg, seed, _ = TINY[name]
+    rng = random.Random(seed + 100)
+    return {f"r{i}": [rng.randrange(cfg["vocab_size"]) for _ in range(n)] for i, n in enumerate(LENGTHS[name])}
+
+
+@pytest.fixture(scope="module")
+def setups(tmp_path_factory):
+    out = {}
+    for name in TINY:
+        for dtype in ("float32", "bfloat16"):
+            store = torch.float32 if dtype == "float32" else torch.bfloat16
+            folder = tiny_folder(tmp_path_factory.mktemp(f"{name}_{dtype}"), name, dtype=store)
+            reqs = requests_for(name)
+            plain = PlainModel(folder)
+            ref = {rid: plain.logits(toks).numpy() for rid, toks in reqs.items()}
+            out[(name, dtype)] = (folder, reqs, ref)
+    return out
+
+
+def compare(got, places, ref, dtype):
+    assert set(got) == set(places)
+    worst = 0.0
+    flips = 0
+    spread = float(np.std(np.concatenate([r.ravel() for r in ref.values()])))
+    tol = F32_ATOL if dtype == "float32" else BF16_REL * spread
+    for step, rows in places.items():
+        want = np.stack([ref[rid][pos] for rid, pos in rows])
+        assert got[step].shape == want.shape
+        assert np.isfinite(got[step]).all()
+        err = np.abs(got[step] - want).max(axis=1)
+        bad = np.nonzero(err > tol)[0]
+        assert bad.size == 0, (f"step {step}: first wrong row {bad[0]} = request/position {rows[bad[0]]}, "
+                               f"error {err[bad[0]]:.3g} > {tol:.3g}")
+        worst = max(worst, float(err.max()))
+        top2 = np.sort(want, axis=1)[:, -2:]
+        clear = (top2[:, 1] - top2[:, 0]) > 2 * tol
+        flips += int((np.argmax(got[step], 1)[clear] != np.argmax(want, 1)[clear]).sum())
+    assert flips == 0
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("mode", ["whole", "tail_one_by_one", "portions", "mixed"])
+def test_replay(setups, tmp_path, name, dtype, mode):
+    folder, reqs, ref = setups[(name, dtype)]
+    steps, places, peak = getattr(traces, mode)(reqs)
+    got = run_trace(folder, dtype, steps, tmp_path / "out", max_tokens=peak)
+    worst = compare(got, places, ref, dtype)
+    print(f"{name} {dtype} {mode}: {len(steps)} steps, pool {peak} tokens, worst error {worst:.3g}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_first_tokens_and_long_decoding(setups, tmp_path, dtype):
+    """The first tokens of a sequence one by one from an empty cache, then decoding on for long."""
+    folder, reqs, ref = setups[("B", dtype)]
+    rid = "r5"                                   # 200 tokens
+    toks = reqs[rid]
+    steps = [{"step": i, "entries": [{"id": rid, "tokens": [t], "want": [0]}], "end": []} for i, t in enumerate(toks)]
+    steps[-1]["end"] = [rid]
+    places = {i: [(rid, i)] for i in range(len(toks))}
+    got = run_trace(folder, dtype, steps, tmp_path / "out", max_tokens=256)
+    compare(got, places, ref, dtype)
