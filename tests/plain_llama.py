@@ -94,36 +94,52 @@ def swiglu_ffn(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, w3: torch.Te
     return (torch.nn.functional.silu(x @ w1.T) * (x @ w3.T)) @ w2.T
 
 
-def attention_layer(x, wq, wk, wv, wo, cfg, cos, sin):
-    """torchllms/models/networks.py:513-558: project, view as heads, rope q and k, attend, project."""
+def _same(t: torch.Tensor) -> torch.Tensor:
+    return t
+
+
+def to_bfloat16_and_back(t: torch.Tensor) -> torch.Tensor:
+    """What storing an activation in bfloat16 between two kernels does to it."""
+    return t.to(torch.bfloat16).to(t.dtype)
+
+
+def attention_layer(x, wq, wk, wv, wo, cfg, cos, sin, stored=_same):
+    """torchllms/models/networks.py:513-558: project, view as heads, rope q and k, attend, project.
+    ``stored`` is applied wherever the engine keeps an intermediate in its activation dtype."""
     S = x.shape[0]
-    q = (x @ wq.T).view(S, cfg["n_heads"], cfg["head_dim"])
-    k = (x @ wk.T).view(S, cfg["n_kv_heads"], cfg["head_dim"])
-    v = (x @ wv.T).view(S, cfg["n_kv_heads"], cfg["head_dim"])
-    q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
-    return causal_attention(q, k, v) @ wo.T
+    q = stored(x @ wq.T).view(S, cfg["n_heads"], cfg["head_dim"])
+    k = stored(x @ wk.T).view(S, cfg["n_kv_heads"], cfg["head_dim"])
+    v = stored(x @ wv.T).view(S, cfg["n_kv_heads"], cfg["head_dim"])
+    q, k = stored(apply_rope(q, cos, sin)), stored(apply_rope(k, cos, sin))
+    return stored(stored(causal_attention(q, k, v)) @ wo.T)
 
 
-def block(x, w: Dict[str, torch.Tensor], prefix: str, cfg, cos, sin):
+def block(x, w: Dict[str, torch.Tensor], prefix: str, cfg, cos, sin, stored=_same):
     """torchllms/models/networks.py:635-644: pre-norm residual block."""
     g = lambda n: w[f"{prefix}.{n}"]
-    h = x + attention_layer(rms_norm(x, g("attention_norm.weight"), cfg["eps"]),
+    h = x + attention_layer(stored(rms_norm(x, g("attention_norm.weight"), cfg["eps"])),
                             g("attention.wq.weight"), g("attention.wk.weight"),
-                            g("attention.wv.weight"), g("attention.wo.weight"), cfg, cos, sin)
-    return h + swiglu_ffn(rms_norm(h, g("ffn_norm.weight"), cfg["eps"]),
-                          g("feed_forward.w1.weight"), g("feed_forward.w2.weight"), g("feed_forward.w3.weight"))
+                            g("attention.wv.weight"), g("attention.wo.weight"), cfg, cos, sin, stored)
+    n = stored(rms_norm(h, g("ffn_norm.weight"), cfg["eps"]))
+    gate, up = stored(n @ g("feed_forward.w1.weight").T), stored(n @ g("feed_forward.w3.weight").T)
+    act = stored(torch.nn.functional.silu(gate) * up)           # :604-605
+    return h + stored(act @ g("feed_forward.w2.weight").T)
 
 
-def forward_logits(w: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int]) -> torch.Tensor:
+def forward_logits(w: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int], stored=_same) -> torch.Tensor:
     """torchllms/models/networks.py:1017-1047: embed, blocks, final norm, head (tied :806-809).
-    Returns [len(tokens), vocab] logits for the whole sequence."""
+    Returns [len(tokens), vocab] logits for the whole sequence.
+
+    With ``stored=to_bfloat16_and_back`` (and bfloat16-valued weights) this is the arithmetic of
+    the engine's bfloat16 mode: float32 residual stream, norms, rotation, softmax and sums, with
+    every intermediate that crosses from one kernel to the next rounded to bfloat16."""
     ids = torch.as_tensor(list(tokens), dtype=torch.long)
     x = w["tok_embeddings.weight"][ids]
     inv = rope_frequencies(cfg["head_dim"], cfg["rope_theta"], cfg["rope_scaling"])
     cos, sin = rope_angles(inv, torch.arange(len(ids)))
     for i in range(cfg["n_layers"]):
-        x = block(x, w, f"layers.{i}", cfg, cos, sin)
-    x = rms_norm(x, w["norm.weight"], cfg["eps"])
+        x = block(x, w, f"layers.{i}", cfg, cos, sin, stored)
+    x = stored(rms_norm(x, w["norm.weight"], cfg["eps"]))
     head = w["tok_embeddings.weight"] if cfg["tie"] else w["output.weight"]
     return x @ head.T
 
@@ -184,8 +200,8 @@ class PlainModel:
         self.weights = read_weights(folder, self.cfg, dtype)
 
     @torch.no_grad()
-    def logits(self, tokens: Sequence[int]) -> torch.Tensor:
-        return forward_logits(self.weights, self.cfg, tokens).float()
+    def logits(self, tokens: Sequence[int], stored=_same) -> torch.Tensor:
+        return forward_logits(self.weights, self.cfg, tokens, stored).float()
 
     @torch.no_grad()
     def greedy(self, prompt: Sequence[int], n_new: int) -> List[int]:

@@ -220,7 +220,7 @@ def test_attention_finds_one_far_key_among_hundreds(ops, dtype, key_pos):
     """Random scores hide a dropped key; here one key takes nearly all the weight, so the output
     must equal that key's value."""
     L, H, KV, hd, P = 700, 4, 2, 32, 16
-    a = build_paged([L, 40], [1, 1], H, KV, hd, P, dtype, seed=key_pos, peak=(0, key_pos, 6.0))
+    a = build_paged([L, 40], [1, 1], H, KV, hd, P, dtype, seed=key_pos, peak=(0, key_pos, 10.0))
     got = ops.paged_attention(**a, scale=hd ** -0.5, window=None).float()
     page, slot = a["block_table"][0, key_pos // P].item(), key_pos % P
     for h in range(H):
@@ -238,7 +238,7 @@ def test_window_edge_is_exact(ops, dtype):
     L, H, KV, hd, P, w = 100, 2, 1, 16, 8, 24
     for edge_inside in (False, True):
         key_pos = (L - 1) - w + (1 if edge_inside else 0)   # last query sits at L - 1
-        a = build_paged([L], [1], H, KV, hd, P, dtype, seed=3, peak=(0, key_pos, 8.0))
+        a = build_paged([L], [1], H, KV, hd, P, dtype, seed=3, peak=(0, key_pos, 12.0))
         got = ops.paged_attention(**a, scale=hd ** -0.5, window=w).float()
         page, slot = a["block_table"][0, key_pos // P].item(), key_pos % P
         v = a["v_pages"][page, 0, slot].float()

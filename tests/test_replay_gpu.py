@@ -10,17 +10,21 @@ import torch
 import traces
 from helpers import TINY, tiny_folder
 from helpers import run_trace
-from plain_llama import PlainModel
+from plain_llama import PlainModel, to_bfloat16_and_back
 
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [1, 7, 33, 64, 97, 120, 50], "B": [2, 5, 17, 40, 100, 200, 65, 129]}
 # float32: the reference's own gate is 1e-3 (torchllms/inference/validate_qwen3.py:579-584); these
-# models are tiny, so a tenth of it.  bfloat16: weights are stored in bfloat16 and read exactly by
-# both sides; what differs is the rounding of activations to 8 bits between kernels (about 0.4 %
-# each, a few dozen of them), measured against the spread of the logits.
+# models are tiny, so a tenth of it.
+# bfloat16: weights are stored in bfloat16 and read exactly by both sides, and the plain
+# implementation rounds every intermediate where the engine stores one.  What is left is that a
+# sum taken in another order lands on the other side of a bfloat16 rounding step now and then,
+# and such a flip then travels on like any bfloat16 error does.  So the yard-stick is how much
+# bfloat16 storage itself moves these logits (plain-with-rounding against plain float32,
+# computed per model below): the engine must agree with the emulation to a quarter of that.
 F32_ATOL = 1e-4
-BF16_REL = 0.04
+BF16_SHARE = 0.25
 
 
 def requests_for(name):
@@ -38,17 +42,22 @@ def setups(tmp_path_factory):
             folder = tiny_folder(tmp_path_factory.mktemp(f"{name}_{dtype}"), name, dtype=store)
             reqs = requests_for(name)
             plain = PlainModel(folder)
-            ref = {rid: plain.logits(toks).numpy() for rid, toks in reqs.items()}
-            out[(name, dtype)] = (folder, reqs, ref)
+            # bfloat16 is compared with the plain implementation rounding where the engine stores
+            if dtype == "float32":
+                ref = {rid: plain.logits(toks).numpy() for rid, toks in reqs.items()}
+                tol = F32_ATOL
+            else:
+                ref = {rid: plain.logits(toks, stored=to_bfloat16_and_back).numpy() for rid, toks in reqs.items()}
+                moved = max(float(np.abs(ref[rid] - plain.logits(toks).numpy()).max()) for rid, toks in reqs.items())
+                tol = BF16_SHARE * moved
+            out[(name, dtype)] = (folder, reqs, ref, tol)
     return out
 
 
-def compare(got, places, ref, dtype):
+def compare(got, places, ref, tol):
     assert set(got) == set(places)
     worst = 0.0
     flips = 0
-    spread = float(np.std(np.concatenate([r.ravel() for r in ref.values()])))
-    tol = F32_ATOL if dtype == "float32" else BF16_REL * spread
     for step, rows in places.items():
         want = np.stack([ref[rid][pos] for rid, pos in rows])
         assert got[step].shape == want.shape
@@ -69,21 +78,21 @@ def compare(got, places, ref, dtype):
 @pytest.mark.parametrize("name", ["A", "B"])
 @pytest.mark.parametrize("mode", ["whole", "tail_one_by_one", "portions", "mixed"])
 def test_replay(setups, tmp_path, name, dtype, mode):
-    folder, reqs, ref = setups[(name, dtype)]
+    folder, reqs, ref, tol = setups[(name, dtype)]
     steps, places, peak = getattr(traces, mode)(reqs)
     got = run_trace(folder, dtype, steps, tmp_path / "out", max_tokens=peak)
-    worst = compare(got, places, ref, dtype)
-    print(f"{name} {dtype} {mode}: {len(steps)} steps, pool {peak} tokens, worst error {worst:.3g}")
+    worst = compare(got, places, ref, tol)
+    print(f"{name} {dtype} {mode}: {len(steps)} steps, pool {peak} tokens, worst error {worst:.3g} (allowed {tol:.3g})")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_replay_first_tokens_and_long_decoding(setups, tmp_path, dtype):
     """The first tokens of a sequence one by one from an empty cache, then decoding on for long."""
-    folder, reqs, ref = setups[("B", dtype)]
+    folder, reqs, ref, tol = setups[("B", dtype)]
     rid = "r5"                                   # 200 tokens
     toks = reqs[rid]
     steps = [{"step": i, "entries": [{"id": rid, "tokens": [t], "want": [0]}], "end": []} for i, t in enumerate(toks)]
     steps[-1]["end"] = [rid]
     places = {i: [(rid, i)] for i in range(len(toks))}
     got = run_trace(folder, dtype, steps, tmp_path / "out", max_tokens=256)
-    compare(got, places, ref, dtype)
+    compare(got, places, ref, tol)

@@ -270,6 +270,16 @@ class CacheManager:
                 need[gi] += self._blocks_wanted(req, gi, n)
         return all(need[gi] <= g.allocator.n_free for gi, g in enumerate(self.groups))
 
+    def room_for(self, handle: int, others: Iterable[Tuple[int, int]] = ()) -> int:
+        """How many more tokens this request could take after ``others`` took theirs."""
+        req = self._req(handle)
+        others = list(others)
+        room = self.max_len - req.length
+        for gi, g in enumerate(self.groups):
+            free = g.allocator.n_free - sum(self._blocks_wanted(self._req(h), gi, n) for h, n in others)
+            room = min(room, (len(req.blocks[gi]) + max(free, 0)) * self.page_size - req.length)
+        return max(room, 0)
+
     def extend_many(self, wants: Sequence[Tuple[int, int]]) -> List[int]:
         """Make room for ``n`` more tokens of each request, all or nothing.
 

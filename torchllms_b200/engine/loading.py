@@ -41,13 +41,20 @@ def model_dir_of(path) -> Path:
 
 def load_model(path, *, dtype="bfloat16", device="cuda", overrides: Optional[Mapping[str, Any]] = None,
                max_positions: Optional[int] = None, ops=None) -> Tuple[Architecture, Any, Model]:
-    folder = model_dir_of(path)
+    """``path`` is a model folder, a safetensors file, or a list of them: tensors of later
+    entries replace those of earlier ones (the reference loads several checkpoint paths in order,
+    torchllms/models/utils.py:102-130); the configuration is read beside the first."""
+    paths = [path] if isinstance(path, (str, Path)) else list(path)
+    folder = model_dir_of(paths[0])
     arch, config = load_config(folder, overrides)
     spec = arch.build_spec(config)
     model = Model(spec, dtype=parse_dtype(dtype), device=device, ops=ops or get_ops(),
                   max_positions=max_positions)
-    source = TensorSource(path if Path(path).is_file() and str(path).endswith(".safetensors") else folder)
-    found = arch.adapt_tensors(config, source_tensors(source))
+    found: Dict[str, LazyTensor] = {}
+    for p in paths:
+        p = Path(p)
+        source = TensorSource(p if p.is_file() and p.suffix == ".safetensors" else model_dir_of(p))
+        found.update(arch.adapt_tensors(config, source_tensors(source)))
     expected = model.expected_tensors()
     if spec.tie_head and spec.head_tensor in found and spec.embedding_tensor in found:
         # A tied model stores one table.  A second copy is tolerated only if it is the same table.

@@ -1,0 +1,3 @@
+from .llm import LLM, GenerationResult
+
+__all__ = ["LLM", "GenerationResult"]
