@@ -1,0 +1,257 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+The workload is the Llama-3.1-8B shape (32 layers, dim 4096, 32 heads, 8 kv heads, head_dim 128,
+SwiGLU hidden 14336, vocabulary 128256, llama3 rope scaling, untied head) in bfloat16 with random
+weights and synthetic token ids: requests with 2,048-token prompts decode with a batch of 8
+(headline ``value``), of 1 and of 64 (``points``), and one 2,048-token prompt is prefilled
+(``prefill``).  A step is one decode step.  One JSON line is printed.
+
+``value`` times K decode steps on the device with CUDA events (engine step plus the sampling
+kernel; the tokens fed are host lists prepared beforehand, so the device never waits for a
+read-back).  ``e2e`` is the same batch through ``LLM.generate``: scheduler, upload of each step's
+index data from pinned memory, sampling, and the read-back of the sampled tokens every step.
+Every decode step streams all weights (16 GB, far more than the 126 MB L2), so no L2 flush is
+needed between timed iterations.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SHAPE_8B = dict(n_layers=32, dim=4096, n_heads=32, n_kv_heads=8, head_dim=128, ffn_hidden=14336,
+                vocab_size=128256, norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=False)
+ROPE_8B = dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+               original_max_position_embeddings=8192)
+PROMPT_LEN = 2048
+CONTEXT = 8192
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def load_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(raw.get("bf16_tflops_sustained", raw["bf16_tflops"])),
+                    "source": "measured"}
+        except (ValueError, KeyError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.lines = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", os.environ.get("CUDA_VISIBLE_DEVICES", "0").split(",")[0],
+                 f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        mhz, max_mhz, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                mhz.append(int(float(parts[0])))
+                max_mhz = max(max_mhz, int(float(parts[1])))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max_mhz or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def reference_arm(args):
+    """The unmodified reference through its own public API, if it is installed under baseline/_ref."""
+    ref = ROOT / "baseline" / "_ref"
+    why = None
+    if not (ref / "torchllms").is_dir():
+        why = "reference not installed under baseline/_ref (offline pip install not done on this box)"
+    else:
+        why = ("reference LLM needs a tokenizer folder and a consolidated.00.pth checkpoint of the 8B shape; "
+               "no arm that drives its stock generate() with synthetic ids is wired up yet")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=SHAPE_8B["n_layers"], help="fewer layers than the shape has (named in config)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--skip-points", action="store_true", help="only the headline batch and the prefill")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(json.dumps({"error": f"this engine runs on one GPU; --gpus {args.gpus} is not supported", "n_gpus": args.gpus}))
+        return 2
+    if args.impl == "reference":
+        return reference_arm(args)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    from torchllms_b200.config import LlamaConfig, RopeScaling
+    from torchllms_b200.engine.step import StepEntry
+    from torchllms_b200.inference import LLM
+
+    peaks = load_peaks()
+    shape = dict(SHAPE_8B, n_layers=args.layers)
+    cfg = LlamaConfig(architecture="LlamaForCausalLM", rope_scaling=RopeScaling(**ROPE_8B), max_seq_len=CONTEXT, **shape)
+    max_b = 64 if not args.skip_points else args.batch
+    llm = LLM(config=cfg, random_seed=0, precision="bfloat16", max_len=CONTEXT, max_bsz=max(max_b, args.batch),
+              max_num_batched_tokens=PROMPT_LEN + 64, page_size=16)
+    engine, ops = llm.engine, llm.model.ops
+    gen = torch.Generator().manual_seed(1234)
+
+    def prompts(n, length=PROMPT_LEN):
+        return torch.randint(0, cfg.vocab_size, (n, length), generator=gen).tolist()
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    # ------------------------------------------------------------------ prefill, 2,048 tokens
+    def prefill_once():
+        h = engine.claim()
+        toks = prompts(1)[0]
+        torch.cuda.synchronize()
+        a, b = ev(), ev()
+        a.record()
+        engine.step([StepEntry(h, toks, [PROMPT_LEN - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        engine.release(h)
+        return a.elapsed_time(b)
+
+    for _ in range(3):
+        prefill_once()
+    pre_ms = sorted(prefill_once() for _ in range(5))[2]
+    # 2 flops per weight per token; q, k, v, o projections: dim * hd * (2 H + 2 KV) weights; gate, up, down:
+    # 3 * dim * hidden; the head runs on one row; causal attention: QK^T and PV, each 2 * H * hd * T^2 / 2
+    lin = PROMPT_LEN * (args.layers * (2 * cfg.dim * cfg.head_dim * (2 * cfg.n_heads + 2 * cfg.n_kv_heads)
+                                        + 6 * cfg.dim * cfg.ffn_hidden)) + 2 * cfg.dim * cfg.vocab_size
+    attn = args.layers * 2 * cfg.n_heads * cfg.head_dim * PROMPT_LEN * PROMPT_LEN
+    pre_flops = lin + attn
+    prefill = {"value": round(PROMPT_LEN / (pre_ms / 1e3), 1), "tokens": PROMPT_LEN, "ms": round(pre_ms, 3),
+               "frac": round(pre_flops / (pre_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
+
+    # ------------------------------------------------------------------ decode at a batch size
+    kv_bytes_per_token = args.layers * 2 * cfg.n_kv_heads * cfg.head_dim * 2
+
+    def decode_run(batch, steps, warmup, with_clocks=False):
+        handles = [engine.claim() for _ in range(batch)]
+        ps = prompts(batch)
+        for h, p in zip(handles, ps):                       # prefill, one prompt per step
+            engine.step([StepEntry(h, p, [])])
+        feed = torch.randint(0, cfg.vocab_size, (warmup + steps, batch), generator=gen).tolist()
+        for i in range(warmup):
+            logits = engine.step([StepEntry(h, [t]) for h, t in zip(handles, feed[i])])
+            ops.sample(logits)
+        torch.cuda.synchronize()
+        launches0 = ops.launches
+        a, b = ev(), ev()
+        clocks = ClockSampler() if with_clocks else None
+        if clocks:
+            clocks.__enter__()
+        a.record()
+        for i in range(warmup, warmup + steps):
+            logits = engine.step([StepEntry(h, [t]) for h, t in zip(handles, feed[i])])
+            ops.sample(logits)
+        b.record()
+        torch.cuda.synchronize()
+        if clocks:
+            clocks.__exit__()
+        ms = a.elapsed_time(b) / steps
+        for h in handles:
+            engine.release(h)
+        mean_ctx = PROMPT_LEN + warmup + steps / 2
+        step_bytes = llm.model.weight_bytes() + batch * mean_ctx * kv_bytes_per_token
+        return {"ms": ms, "tok_s": batch / (ms / 1e3), "bytes": step_bytes, "launches": ops.launches - launches0,
+                "clocks": clocks.summary() if clocks else None}
+
+    head = decode_run(args.batch, args.steps, args.warmup, with_clocks=True)
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(decode_run(b, max(args.steps // 2, 8), 3)["tok_s"], 1)
+    achieved = head["bytes"] / (head["ms"] / 1e3) / 1e9
+
+    # ------------------------------------------------------------------ end to end through LLM.generate
+    n_new = args.warmup + args.steps
+    llm.generate(prompt_token_ids=prompts(args.batch, 64), max_new_tokens=4)        # warm the path
+    llm.generate(prompt_token_ids=prompts(args.batch), max_new_tokens=n_new)
+    st = llm.last_stats
+    e2e_tok_s = st.decode_step_tokens / st.decode_seconds if st.decode_seconds > 0 else None
+    buf = engine._buf
+    h2d = 4 * (buf.sections["block_table0"][0] + args.batch * buf.NB) if buf.G else 0
+    e2e = {"value": round(e2e_tok_s, 1) if e2e_tok_s else None, "unit": "tokens/s",
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch}
+
+    out = {
+        "metric": "decode tok/s at batch 8 (Llama-3.1-8B shape, 2,048-token prompts)",
+        "value": round(head["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(head["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights N(0, 0.02))",
+        "config": {"model": "llama-3.1-8b-shape", "n_layers": args.layers, "n_layers_full": SHAPE_8B["n_layers"],
+                   "dim": cfg.dim, "n_heads": cfg.n_heads, "n_kv_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim,
+                   "ffn_hidden": cfg.ffn_hidden, "vocab_size": cfg.vocab_size, "global_batch": args.batch,
+                   "seq_len": PROMPT_LEN, "context": CONTEXT, "page_size": 16, "parallelism": "single-gpu",
+                   "l2": "inputs larger than L2 (16 GB of weights per step)"},
+        "e2e": e2e, "gpu_launches": head["launches"], "clocks": head["clocks"],
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4), "peaks": peaks["source"]},
+        "points": points,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

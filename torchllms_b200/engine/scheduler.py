@@ -20,6 +20,7 @@ finished with an error instead of blocking the queue.
 
 from __future__ import annotations
 
+import time
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, Iterable, List, Optional, Sequence, Set, Tuple
@@ -58,6 +59,9 @@ class SchedulerStats:
     decode_tokens: int = 0
     preemptions: int = 0
     max_running: int = 0
+    decode_steps: int = 0            # steps that held decode tokens only
+    decode_step_tokens: int = 0
+    decode_seconds: float = 0.0      # wall time of those steps, sampling and its read-back included
 
 
 class Scheduler:
@@ -190,6 +194,8 @@ class Scheduler:
             entries.append(StepEntry(r.handle, toks, [n - 1] if completes else []))
             if completes:
                 samplers.append(r)
+        pure_decode = all(n == 1 and r.n_fed > 0 and r.generated for r, n in planned)
+        t0 = time.perf_counter()
         logits = self.engine.step(entries)
         self.trace.append([(r.index, n) for r, n in planned])
         self.stats.steps += 1
@@ -215,6 +221,10 @@ class Scheduler:
                     r.handle = None
                     self.running.remove(r)
                     finished_now.append(r)
+        if pure_decode:
+            self.stats.decode_steps += 1
+            self.stats.decode_step_tokens += len(planned)
+            self.stats.decode_seconds += time.perf_counter() - t0
         return finished_now
 
     def run(self, requests: Sequence[Request]) -> Sequence[Request]:

@@ -67,6 +67,7 @@ class NativeOps:
             raise KernelError(
                 "torchllms_b200 runs on a CUDA GPU (sm_100a) only: torch.cuda.is_available() is False "
                 "and there is no CPU implementation")
+        self.launches = 0          # kernels of this library launched so far (a bench counts with it)
         self._workspace: Dict[Tuple[int, str], torch.Tensor] = {}
         self._mm_out_dtype: Optional[bool] = None
 
@@ -99,6 +100,7 @@ class NativeOps:
         rc = self._lib("elementwise").tl_embed(_ptr(token_ids), _ptr(table), _DT[table.dtype], _ptr(out),
                                               n, dim, vocab, _stream())
         _check(rc, "embed")
+        self.launches += 1
         return out
 
     def rmsnorm(self, h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
@@ -121,6 +123,7 @@ class NativeOps:
             _ptr(h), _ptr(delta), _DT[delta.dtype] if delta is not None else 0, _ptr(weight), _ptr(out),
             _DT[out_dtype], _ptr(rows), n_out, dim, ctypes.c_float(eps), write_back, _stream())
         _check(rc, "rmsnorm")
+        self.launches += 1
         return out
 
     def swiglu(self, gate_up: torch.Tensor) -> torch.Tensor:
@@ -131,6 +134,7 @@ class NativeOps:
         out = torch.empty((n, hidden), dtype=gate_up.dtype, device=gate_up.device)
         rc = self._lib("elementwise").tl_swiglu(_ptr(gate_up), _ptr(out), _DT[gate_up.dtype], n, hidden, _stream())
         _check(rc, "swiglu")
+        self.launches += 1
         return out
 
     # ------------------------------------------------------------------ linear
@@ -170,6 +174,7 @@ class NativeOps:
         rc = self._lib("gemm_simt").tl_gemm_simt(_ptr(x), _ptr(w), _ptr(out), _DT[x.dtype], _DT[out_dtype],
                                                 M, N, K, _stream())
         _check(rc, "gemm_simt")
+        self.launches += 1
         return out
 
     # -------------------------------------------------------------------- rope
@@ -199,6 +204,7 @@ class NativeOps:
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _DT[qkv.dtype], T, n_heads, n_kv_heads, head_dim,
             page_size, table.shape[0], 1 if interleaved else 0, _stream())
         _check(rc, "rope_kv_write")
+        self.launches += 1
         return q
 
     # --------------------------------------------------------------- attention
@@ -245,6 +251,7 @@ class NativeOps:
             page_size, max_q_len, max_kv_len, int(window or 0), ctypes.c_float(scale),
             1 if allow_split else 0, _stream())
         _check(rc, "paged_attention")
+        self.launches += 2 if n_splits.value > 1 else 1
         return out
 
     # ---------------------------------------------------------------- sampling
@@ -269,6 +276,7 @@ class NativeOps:
             _ptr(logits), ctypes.c_longlong(logits.stride(0)), n, vocab, _ptr(temperature), _ptr(top_k),
             _ptr(row_keys), _ptr(out), _stream())
         _check(rc, "sample")
+        self.launches += 1
         return out
 
 
