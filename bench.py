@@ -56,18 +56,22 @@ def load_peaks():
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
 
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self):
         self.lines = []
         self.proc = None
+        self.window = None      # (start, end) of the timed region, host clock
+
+    def mark(self, start: float, end: float):
+        self.window = (start, end)
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", os.environ.get("CUDA_VISIBLE_DEVICES", "0").split(",")[0],
-                 f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                 f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -89,16 +93,27 @@ class ClockSampler:
     def summary(self):
         mhz, max_mhz, reasons = [], 0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        import datetime
+        rows = []
         for line in self.lines:
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 6:
+            if len(parts) < 7:
                 continue
             try:
-                mhz.append(int(float(parts[0])))
-                max_mhz = max(max_mhz, int(float(parts[1])))
+                stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((stamp, int(float(parts[1])), int(float(parts[2])), parts[3:7]))
             except ValueError:
                 continue
-            for name, flag in zip(names, parts[2:6]):
+        inside = rows
+        if self.window is not None:
+            for slack in (0.0, 0.25, 1.0):      # a short region may fall between two samples
+                inside = [r for r in rows if self.window[0] - slack <= r[0] <= self.window[1] + slack]
+                if inside:
+                    break
+        for _stamp, sm, sm_max, flags in inside:
+            mhz.append(sm)
+            max_mhz = max(max_mhz, sm_max)
+            for name, flag in zip(names, flags):
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         mhz.sort()
@@ -128,6 +143,8 @@ def main():
     ap.add_argument("--layers", type=int, default=SHAPE_8B["n_layers"], help="fewer layers than the shape has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch and the prefill")
+    ap.add_argument("--profile", action="store_true",
+                    help="also print, on standard error, per-kernel times of one prefill and one decode step")
     args = ap.parse_args()
     if args.gpus != 1:
         print(json.dumps({"error": f"this engine runs on one GPU; --gpus {args.gpus} is not supported", "n_gpus": args.gpus}))
@@ -185,6 +202,9 @@ def main():
     kv_bytes_per_token = args.layers * 2 * cfg.n_kv_heads * cfg.head_dim * 2
 
     def decode_run(batch, steps, warmup, with_clocks=False):
+        clocks = ClockSampler() if with_clocks else None
+        if clocks:
+            clocks.__enter__()
         handles = [engine.claim() for _ in range(batch)]
         ps = prompts(batch)
         for h, p in zip(handles, ps):                       # prefill, one prompt per step
@@ -196,9 +216,7 @@ def main():
         torch.cuda.synchronize()
         launches0 = ops.launches
         a, b = ev(), ev()
-        clocks = ClockSampler() if with_clocks else None
-        if clocks:
-            clocks.__enter__()
+        t_start = time.time()
         a.record()
         for i in range(warmup, warmup + steps):
             logits = engine.step([StepEntry(h, [t]) for h, t in zip(handles, feed[i])])
@@ -206,6 +224,8 @@ def main():
         b.record()
         torch.cuda.synchronize()
         if clocks:
+            clocks.mark(t_start, time.time())
+            time.sleep(0.15)
             clocks.__exit__()
         ms = a.elapsed_time(b) / steps
         for h in handles:
@@ -221,6 +241,26 @@ def main():
         for b in (1, 64):
             points[f"decode_b{b}"] = round(decode_run(b, max(args.steps // 2, 8), 3)["tok_s"], 1)
     achieved = head["bytes"] / (head["ms"] / 1e3) / 1e9
+
+    if args.profile:
+        def table(title, prof):
+            total = sum(ms for _n, ms in prof.values())
+            print(f"-- {title}: {total:.3f} ms in kernels", file=sys.stderr)
+            for name, (calls, ms) in sorted(prof.items(), key=lambda kv: -kv[1][1]):
+                print(f"   {name:16s} {calls:5d} calls {ms:9.3f} ms {100 * ms / total:5.1f} %", file=sys.stderr)
+        h = engine.claim()
+        with ops.profile() as prof:
+            engine.step([StepEntry(h, prompts(1)[0], [PROMPT_LEN - 1])])
+        table("prefill of 2,048 tokens", prof)
+        hs = [engine.claim() for _ in range(args.batch - 1)]
+        for x in hs:
+            engine.step([StepEntry(x, prompts(1)[0], [])])
+        with ops.profile() as prof:
+            logits = engine.step([StepEntry(x, [1]) for x in [h] + hs])
+            ops.sample(logits)
+        table(f"decode step, batch {args.batch}, context 2,048", prof)
+        for x in [h] + hs:
+            engine.release(x)
 
     # ------------------------------------------------------------------ end to end through LLM.generate
     n_new = args.warmup + args.steps

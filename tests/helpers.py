@@ -72,7 +72,7 @@ def write_model_folder(folder, cfg: dict, tensors: Dict[str, torch.Tensor], dtyp
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
     (folder / "config.json").write_text(json.dumps(cfg))
-    save_file({k: v.to(dtype).contiguous() for k, v in tensors.items()}, str(folder / "model.safetensors"))
+    save_file({k: (v.to(dtype) if v.is_floating_point() else v).contiguous() for k, v in tensors.items()}, str(folder / "model.safetensors"))
     return folder
 
 

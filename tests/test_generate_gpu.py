@@ -1,0 +1,73 @@
+"""Greedy generation through the Python entry point on the GPU against the plain implementation."""
+
+import pytest
+import torch
+
+from helpers import TINY, tiny_folder
+from plain_llama import PlainModel, to_bfloat16_and_back
+
+pytestmark = pytest.mark.gpu
+
+PROMPTS = {"A": [[1, 2, 3], [5], [7] * 40, list(range(100, 164)), [11, 12] * 30],
+           "B": [[999, 0], [5, 17, 3, 41, 8], list(range(200, 300)), [3] * 17, [900 - i for i in range(200)]]}
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_float32_matches_plain_token_for_token(tmp_path, name):
+    from torchllms_b200.inference import LLM
+    cfg, _, page = TINY[name]
+    folder = tiny_folder(tmp_path, name)
+    llm = LLM(folder, precision="float32", max_len=cfg["max_position_embeddings"], max_bsz=3, page_size=page,
+              max_num_batched_tokens=64, prefill_chunk=24)
+    got = llm.generate(prompt_token_ids=PROMPTS[name], max_new_tokens=16)
+    plain = PlainModel(folder)
+    for p, r in zip(PROMPTS[name], got):
+        assert r.token_ids == plain.greedy(p, 16), p
+    llm.engine.cache.check_invariants()
+    assert llm.engine.cache.n_live() == 0
+    # tight pool: the same tokens although requests are pre-empted and recomputed
+    per_token = cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * cfg["head_dim"] * 2 * 4
+    pool_tokens = max(len(p) for p in PROMPTS[name]) + 16 + 2 * page
+    small = LLM(folder, precision="float32", max_len=cfg["max_position_embeddings"], max_bsz=3, page_size=page,
+                kv_memory_gb=pool_tokens * per_token / 2 ** 30, max_num_batched_tokens=64, prefill_chunk=24)
+    assert small.engine.cache.groups[0].allocator.n_pages == pool_tokens // page
+    assert [r.token_ids for r in small.generate(prompt_token_ids=PROMPTS[name], max_new_tokens=16)] == [r.token_ids for r in got]
+    assert small.last_stats.preemptions > 0 or small.last_stats.max_running < 3
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_bfloat16_follows_plain_while_the_margin_is_clear(tmp_path, name):
+    from torchllms_b200.inference import LLM
+    cfg, _, page = TINY[name]
+    folder = tiny_folder(tmp_path, name, dtype=torch.bfloat16)
+    llm = LLM(folder, precision="bfloat16", max_len=cfg["max_position_embeddings"], max_bsz=4, page_size=page,
+              max_num_batched_tokens=64, prefill_chunk=24)
+    got = llm.generate(prompt_token_ids=PROMPTS[name], max_new_tokens=12)
+    plain = PlainModel(folder)
+    checked = 0
+    for p, r in zip(PROMPTS[name], got):
+        seq = list(p)
+        for tok in r.token_ids:
+            logits = plain.logits(seq, stored=to_bfloat16_and_back)[-1]
+            top = torch.topk(logits, 2).values
+            if float(top[0] - top[1]) < 0.1:
+                break                                  # a near tie: either token is a fair answer, stop comparing
+            assert tok == int(torch.argmax(logits)), (p, len(seq))
+            checked += 1
+            seq.append(tok)
+    assert checked >= 20
+
+
+def test_temperature_sampling_is_reproducible_and_seeded(tmp_path):
+    from torchllms_b200.inference import LLM
+    cfg, _, page = TINY["A"]
+    folder = tiny_folder(tmp_path, "A")
+    a = LLM(folder, precision="float32", max_len=128, max_bsz=4, page_size=page, max_num_batched_tokens=64, prefill_chunk=24)
+    b = LLM(folder, precision="float32", max_len=128, max_bsz=2, page_size=page, max_num_batched_tokens=9, prefill_chunk=4)
+    kw = dict(prompt_token_ids=PROMPTS["A"], max_new_tokens=10, temperature=0.8, seed=7)
+    ra, rb = a.generate(**kw), b.generate(**kw)
+    assert [r.token_ids for r in ra] == [r.token_ids for r in rb]
+    assert [r.token_ids for r in a.generate(**dict(kw, seed=8))] != [r.token_ids for r in ra]
+    top1 = a.generate(prompt_token_ids=PROMPTS["A"], max_new_tokens=10, temperature=1.5, top_k=1)
+    greedy = a.generate(prompt_token_ids=PROMPTS["A"], max_new_tokens=10)
+    assert [r.token_ids for r in top1] == [r.token_ids for r in greedy]

@@ -344,18 +344,20 @@ class CacheManager:
         if not 0 <= new_length <= req.length:
             raise CacheError(f"request {handle}: cannot truncate {req.length} tokens to {new_length}")
         keep = -(-new_length // self.page_size)
-        for gi, g in enumerate(self.groups):
+        for gi, g in enumerate(self.groups):       # check every group before touching any
             if g.need.kind == "window" and req.first_block[gi] > 0:
                 first_needed = new_length - g.need.window + 1
                 if first_needed < req.first_block[gi] * self.page_size:
                     raise CacheError(
                         f"request {handle}: truncating to {new_length} would need keys that window "
                         f"group {gi} has already given back")
+        for gi, g in enumerate(self.groups):
             while len(req.blocks[gi]) > keep:
                 p = req.blocks[gi].pop()
                 if p != FREED:
                     g.allocator.release(p)
                 self._tables[gi][req.slot, len(req.blocks[gi])] = FREED
+            req.first_block[gi] = min(req.first_block[gi], len(req.blocks[gi]))
         req.length = new_length
 
     # ---------------------------------------------------------- step-side views

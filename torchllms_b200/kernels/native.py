@@ -8,7 +8,9 @@ so they order with PyTorch's own work and can be captured into CUDA graphs.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
+import functools
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -57,6 +59,24 @@ def _cuda_contig(t: torch.Tensor, name: str, dtype=None) -> None:
         _need(t.dtype == dtype, f"{name} must be {dtype}, got {t.dtype}")
 
 
+def _timed(fn):
+    """While a profile is being taken, bracket the call with CUDA events."""
+    name = fn.__name__
+
+    @functools.wraps(fn)
+    def wrapper(self, *args, **kwargs):
+        prof = self._profile
+        if prof is None:
+            return fn(self, *args, **kwargs)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        out = fn(self, *args, **kwargs)
+        b.record()
+        prof.append((name, a, b))
+        return out
+    return wrapper
+
+
 class NativeOps:
     """The kernels as methods.  Libraries are compiled and loaded on first use."""
 
@@ -70,6 +90,7 @@ class NativeOps:
         self.launches = 0          # kernels of this library launched so far (a bench counts with it)
         self._workspace: Dict[Tuple[int, str], torch.Tensor] = {}
         self._mm_out_dtype: Optional[bool] = None
+        self._profile = None
 
     # ------------------------------------------------------------ libraries
     def prepare(self, dtype: torch.dtype, sampling: bool = True) -> None:
@@ -82,6 +103,22 @@ class NativeOps:
     def _lib(self, name: str):
         return load_library(name)
 
+    @contextlib.contextmanager
+    def profile(self):
+        """Time every call made inside the block; yields a dict name -> [calls, milliseconds]
+        that is filled when the block ends (the stream is synchronised then)."""
+        result: Dict[str, list] = {}
+        self._profile = []
+        try:
+            yield result
+        finally:
+            records, self._profile = self._profile, None
+            torch.cuda.synchronize()
+            for name, a, b in records:
+                entry = result.setdefault(name, [0, 0.0])
+                entry[0] += 1
+                entry[1] += a.elapsed_time(b)
+
     # ------------------------------------------------------------- checks
     def check_attention_sizes(self, n_heads: int, n_kv_heads: int, head_dim: int, dtype: torch.dtype) -> None:
         _need(dtype in _DT, f"attention supports float32 and bfloat16, not {dtype}")
@@ -91,6 +128,7 @@ class NativeOps:
               f"head_dim must be a multiple of 16 between 16 and 256, got {head_dim}")
 
     # ------------------------------------------------------------ elementwise
+    @_timed
     def embed(self, token_ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
         _cuda_contig(token_ids, "token_ids", torch.int32)
         _cuda_contig(table, "embedding table")
@@ -103,6 +141,7 @@ class NativeOps:
         self.launches += 1
         return out
 
+    @_timed
     def rmsnorm(self, h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         _cuda_contig(h, "residual stream", torch.float32)
@@ -126,6 +165,7 @@ class NativeOps:
         self.launches += 1
         return out
 
+    @_timed
     def swiglu(self, gate_up: torch.Tensor) -> torch.Tensor:
         _cuda_contig(gate_up, "gate_up")
         _need(gate_up.dim() == 2 and gate_up.shape[1] % 2 == 0 and gate_up.dtype in _DT,
@@ -138,6 +178,7 @@ class NativeOps:
         return out
 
     # ------------------------------------------------------------------ linear
+    @_timed
     def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """``x [M, K] @ w[N, K]^T``.  float32 runs on the CUDA cores (true 32-bit);
         bfloat16 uses the library product, as the reference's ``nn.Linear`` does."""
@@ -178,6 +219,7 @@ class NativeOps:
         return out
 
     # -------------------------------------------------------------------- rope
+    @_timed
     def rope_kv_write(self, qkv: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, *,
                       n_heads: int, n_kv_heads: int, head_dim: int, interleaved: bool,
                       k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
@@ -218,6 +260,7 @@ class NativeOps:
             self._workspace[key] = buf
         return buf
 
+    @_timed
     def paged_attention(self, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                         block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor, *,
                         n_seqs: int, max_q_len: int, max_kv_len: int, scale: float,
@@ -255,6 +298,7 @@ class NativeOps:
         return out
 
     # ---------------------------------------------------------------- sampling
+    @_timed
     def sample(self, logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
                top_k: Optional[torch.Tensor] = None, row_keys: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Next token of every row.  ``temperature`` (float32), ``top_k`` (int32) and
