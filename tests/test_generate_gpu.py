@@ -35,6 +35,11 @@ def test_greedy_float32_matches_plain_token_for_token(tmp_path, name):
     assert small.last_stats.preemptions > 0 or small.last_stats.max_running < 3
 
 
+# how far apart the two best logits must be before bfloat16 has to agree on the winner: twice what
+# the replay tests allow these models (a quarter of what bfloat16 storage moves their logits)
+MARGIN = {"A": 0.03, "B": 0.12}
+
+
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_greedy_bfloat16_follows_plain_while_the_margin_is_clear(tmp_path, name):
     from torchllms_b200.inference import LLM
@@ -47,15 +52,16 @@ def test_greedy_bfloat16_follows_plain_while_the_margin_is_clear(tmp_path, name)
     checked = 0
     for p, r in zip(PROMPTS[name], got):
         seq = list(p)
-        for tok in r.token_ids:
+        for tok in r.token_ids:                        # follow the engine's tokens, judge each one
             logits = plain.logits(seq, stored=to_bfloat16_and_back)[-1]
-            top = torch.topk(logits, 2).values
-            if float(top[0] - top[1]) < 0.1:
-                break                                  # a near tie: either token is a fair answer, stop comparing
-            assert tok == int(torch.argmax(logits)), (p, len(seq))
-            checked += 1
+            top = torch.topk(logits, 2)
+            if float(top.values[0] - top.values[1]) >= MARGIN[name]:
+                assert tok == int(top.indices[0]), (p, len(seq))
+                checked += 1
+            else:                                      # a near tie: either of the two is a fair answer
+                assert tok in top.indices.tolist() or float(top.values[0] - logits[tok]) < MARGIN[name], (p, len(seq))
             seq.append(tok)
-    assert checked >= 20
+    assert checked >= 15
 
 
 def test_temperature_sampling_is_reproducible_and_seeded(tmp_path):
