@@ -185,43 +185,58 @@ ATTN_CASES = [
     ([100, 60], [100, 1], 2, 2, 256, 32, None),           # head_dim 256, no grouping
     ([200, 90, 33], [200, 1, 5], 4, 2, 32, 8, 17),        # sliding window over page edges
     ([64, 65], [64, 1], 4, 4, 16, 16, 16),                # window exactly one page
+    ([1000, 300, 5], [1, 1, 1], 32, 8, 128, 16, None),    # decoding in the 8B head layout
+    ([500, 77], [3, 2], 8, 2, 64, 16, None),              # portions so short that a request's rows fit one tile
+    ([150], [150], 10, 2, 32, 8, None),                   # group of 5: 3 tokens to a 16-row tile, one row idle
+    ([90, 20], [90, 1], 16, 1, 64, 16, None),             # group of 16
+    ([700, 650], [1, 1], 4, 2, 32, 16, 100),              # decoding behind a window
+    ([2100], [2100], 8, 8, 128, 16, None),                # a long prompt, many key tiles
 ]
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+IMPLS = [(torch.float32, "general"), (torch.bfloat16, "general"), (torch.bfloat16, "mma")]
+
+
+def mma_takes(hd):
+    return hd in (16, 32, 64, 128)
+
+
+@pytest.mark.parametrize("dtype,impl", IMPLS)
 @pytest.mark.parametrize("case", ATTN_CASES, ids=[str(i) for i in range(len(ATTN_CASES))])
-def test_paged_attention_matches_twin(ops, dtype, case):
+def test_paged_attention_matches_twin(ops, dtype, impl, case):
     seq_lens, q_lens, H, KV, hd, P, window = case
+    if impl == "mma" and not mma_takes(hd):
+        pytest.skip("the tensor-core kernel does not take this head size")
     a = build_paged(seq_lens, q_lens, H, KV, hd, P, dtype, seed=len(seq_lens) * 100 + hd)
     scale = hd ** -0.5
-    got = ops.paged_attention(**a, scale=scale, window=window)
+    got = ops.paged_attention(**a, scale=scale, window=window, impl=impl)
     want = TWIN.paged_attention(**a, scale=scale, window=window)
     t = tol(dtype, 2e-5, 2e-2)
     torch.testing.assert_close(got.float(), want.float(), atol=t, rtol=t)
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dtype,impl", IMPLS)
 @pytest.mark.parametrize("B,L", [(1, 2000), (2, 777), (3, 4100)])
-def test_decode_attention_split_over_keys(ops, dtype, B, L):
+def test_decode_attention_split_over_keys(ops, dtype, impl, B, L):
     """Few long requests: the key range is split over CTAs and merged; same answer as unsplit."""
     lens = [L - 13 * i for i in range(B)]
     a = build_paged(lens, [1] * B, 8, 2, 64, 16, dtype, seed=L)
-    split = ops.paged_attention(**a, scale=0.125, window=None, allow_split=True)
-    whole = ops.paged_attention(**a, scale=0.125, window=None, allow_split=False)
+    split = ops.paged_attention(**a, scale=0.125, window=None, allow_split=True, impl=impl)
+    whole = ops.paged_attention(**a, scale=0.125, window=None, allow_split=False, impl=impl)
     want = TWIN.paged_attention(**a, scale=0.125, window=None)
     t = tol(dtype, 2e-5, 2e-2)
     torch.testing.assert_close(split.float(), want.float(), atol=t, rtol=t)
     torch.testing.assert_close(whole.float(), want.float(), atol=t, rtol=t)
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dtype,impl", IMPLS)
 @pytest.mark.parametrize("key_pos", [0, 15, 16, 511, 640])
-def test_attention_finds_one_far_key_among_hundreds(ops, dtype, key_pos):
+def test_attention_finds_one_far_key_among_hundreds(ops, dtype, impl, key_pos):
     """Random scores hide a dropped key; here one key takes nearly all the weight, so the output
     must equal that key's value."""
     L, H, KV, hd, P = 700, 4, 2, 32, 16
     a = build_paged([L, 40], [1, 1], H, KV, hd, P, dtype, seed=key_pos, peak=(0, key_pos, 10.0))
-    got = ops.paged_attention(**a, scale=hd ** -0.5, window=None).float()
+    got = ops.paged_attention(**a, scale=hd ** -0.5, window=None, impl=impl).float()
     page, slot = a["block_table"][0, key_pos // P].item(), key_pos % P
     for h in range(H):
         v = a["v_pages"][page, h // (H // KV), slot].float()
@@ -231,15 +246,15 @@ def test_attention_finds_one_far_key_among_hundreds(ops, dtype, key_pos):
     torch.testing.assert_close(got, want, atol=t, rtol=t)
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-def test_window_edge_is_exact(ops, dtype):
+@pytest.mark.parametrize("dtype,impl", IMPLS)
+def test_window_edge_is_exact(ops, dtype, impl):
     """The key just outside the window gets a huge score: if the edge were off by one it would
     take over the output."""
     L, H, KV, hd, P, w = 100, 2, 1, 16, 8, 24
     for edge_inside in (False, True):
         key_pos = (L - 1) - w + (1 if edge_inside else 0)   # last query sits at L - 1
         a = build_paged([L], [1], H, KV, hd, P, dtype, seed=3, peak=(0, key_pos, 12.0))
-        got = ops.paged_attention(**a, scale=hd ** -0.5, window=w).float()
+        got = ops.paged_attention(**a, scale=hd ** -0.5, window=w, impl=impl).float()
         page, slot = a["block_table"][0, key_pos // P].item(), key_pos % P
         v = a["v_pages"][page, 0, slot].float()
         close = (got[0, 0] - v).abs().max().item() < 0.05

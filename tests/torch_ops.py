@@ -110,7 +110,7 @@ class TorchOps:
         return q
 
     def paged_attention(self, q, k_pages, v_pages, block_table, q_start, kv_len, *, n_seqs, max_q_len,
-                        max_kv_len, scale, window, page_size, allow_split=True):
+                        max_kv_len, scale, window, page_size, allow_split=True, impl="auto"):
         T, H, hd = q.shape
         KV = k_pages.shape[1]
         group = H // KV

@@ -33,7 +33,7 @@ NVCC_FLAGS = [
 # libraries that need more than the CUDA runtime
 EXTRA_LINK: Dict[str, List[str]] = {}
 
-ALL_LIBRARIES = ("elementwise", "rope", "attention", "gemm_simt", "sampling")
+ALL_LIBRARIES = ("elementwise", "rope", "attention", "attention_mma", "gemm_simt", "sampling")
 
 
 class KernelBuildError(RuntimeError):

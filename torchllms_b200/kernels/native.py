@@ -96,6 +96,8 @@ class NativeOps:
     def prepare(self, dtype: torch.dtype, sampling: bool = True) -> None:
         """Compile, side by side, what a model of this dtype will call."""
         names = ["elementwise", "rope", "attention", "gemm_simt"]
+        if dtype == torch.bfloat16:
+            names.append("attention_mma")
         if sampling:
             names.append("sampling")
         build_libraries(names)
@@ -264,7 +266,10 @@ class NativeOps:
     def paged_attention(self, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                         block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor, *,
                         n_seqs: int, max_q_len: int, max_kv_len: int, scale: float,
-                        window: Optional[int], page_size: int, allow_split: bool = True) -> torch.Tensor:
+                        window: Optional[int], page_size: int, allow_split: bool = True,
+                        impl: str = "auto") -> torch.Tensor:
+        """``impl``: ``"general"`` (CUDA cores, any supported size, both dtypes), ``"mma"`` (tensor
+        cores, bfloat16, head_dim 16/32/64/128) or ``"auto"`` (mma where it applies)."""
         _cuda_contig(q, "q")
         _cuda_contig(k_pages, "k_pages", q.dtype)
         _cuda_contig(v_pages, "v_pages", q.dtype)
@@ -280,20 +285,37 @@ class NativeOps:
         _need(block_table.shape[0] >= n_seqs and q_start.numel() >= n_seqs + 1 and kv_len.numel() >= n_seqs,
               "block_table, q_start and kv_len must cover every request of the step")
         _need(block_table.shape[1] * page_size >= max_kv_len, "block_table is too narrow for max_kv_len")
-        lib = self._lib("attention")
+        _need(impl in ("auto", "general", "mma"), f"unknown attention implementation {impl!r}")
+        mma_ok = q.dtype == torch.bfloat16 and head_dim in (16, 32, 64, 128)
+        _need(impl != "mma" or mma_ok, "the tensor-core attention kernel takes bfloat16 and head_dim 16, 32, 64 or 128")
+        use_mma = mma_ok and impl != "general"
         n_splits = ctypes.c_int(0)
         floats = ctypes.c_longlong(0)
-        rc = lib.tl_attention_plan(T, n_seqs, n_heads, n_kv_heads, head_dim, max_q_len, max_kv_len,
-                                   1 if allow_split else 0, ctypes.byref(n_splits), ctypes.byref(floats))
-        _check(rc, "attention_plan")
-        ws = self._scratch(q.device, floats.value)
         out = torch.empty_like(q)
-        rc = lib.tl_paged_attention(
-            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
-            _ptr(q_start), _ptr(kv_len), _ptr(ws), _DT[q.dtype], T, n_seqs, n_heads, n_kv_heads, head_dim,
-            page_size, max_q_len, max_kv_len, int(window or 0), ctypes.c_float(scale),
-            1 if allow_split else 0, _stream())
-        _check(rc, "paged_attention")
+        if use_mma:
+            lib = self._lib("attention_mma")
+            rc = lib.tl_attention_mma_plan(T, n_seqs, n_heads, n_kv_heads, head_dim, max_q_len, max_kv_len,
+                                           1 if allow_split else 0, ctypes.byref(n_splits), ctypes.byref(floats))
+            _check(rc, "attention_mma_plan")
+            ws = self._scratch(q.device, floats.value)
+            rc = lib.tl_paged_attention_mma(
+                _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
+                _ptr(q_start), _ptr(kv_len), _ptr(ws), T, n_seqs, n_heads, n_kv_heads, head_dim,
+                page_size, max_q_len, max_kv_len, int(window or 0), ctypes.c_float(scale),
+                1 if allow_split else 0, _stream())
+            _check(rc, "paged_attention_mma")
+        else:
+            lib = self._lib("attention")
+            rc = lib.tl_attention_plan(T, n_seqs, n_heads, n_kv_heads, head_dim, max_q_len, max_kv_len,
+                                       1 if allow_split else 0, ctypes.byref(n_splits), ctypes.byref(floats))
+            _check(rc, "attention_plan")
+            ws = self._scratch(q.device, floats.value)
+            rc = lib.tl_paged_attention(
+                _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
+                _ptr(q_start), _ptr(kv_len), _ptr(ws), _DT[q.dtype], T, n_seqs, n_heads, n_kv_heads, head_dim,
+                page_size, max_q_len, max_kv_len, int(window or 0), ctypes.c_float(scale),
+                1 if allow_split else 0, _stream())
+            _check(rc, "paged_attention")
         self.launches += 2 if n_splits.value > 1 else 1
         return out
 
