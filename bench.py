@@ -248,6 +248,7 @@ def main():
             print(f"-- {title}: {total:.3f} ms in kernels", file=sys.stderr)
             for name, (calls, ms) in sorted(prof.items(), key=lambda kv: -kv[1][1]):
                 print(f"   {name:16s} {calls:5d} calls {ms:9.3f} ms {100 * ms / total:5.1f} %", file=sys.stderr)
+        engine.use_graphs = False                      # per-kernel times need eager launches
         h = engine.claim()
         with ops.profile() as prof:
             engine.step([StepEntry(h, prompts(1)[0], [PROMPT_LEN - 1])])

@@ -40,7 +40,7 @@ struct AttnParams {
     int n_heads, n_kv_heads, head_dim, page_size;
     int group, gchunk, n_gchunks, tokens_per_tile;
     int window;  // 0: none
-    int n_splits, split_len;
+    int n_splits;
     float scale;
 };
 
@@ -94,8 +94,13 @@ __global__ void __launch_bounds__(NT) paged_attention_kernel(const AttnParams p)
     int k_lo = p.window > 0 ? max(0, qpos_min - p.window + 1) : 0;
     int k_hi = qpos_max + 1;
     if (p.n_splits > 1) {
-        k_lo = max(k_lo, split * p.split_len);
-        k_hi = min(k_hi, (split + 1) * p.split_len);
+        // every request cuts its own visible keys evenly, in whole tiles, so the launch shape
+        // depends on the batch only and not on how long the requests have grown
+        const int len = max(k_hi - k_lo, 0);
+        const int chunk = ((len + p.n_splits - 1) / p.n_splits + TK - 1) / TK * TK;
+        const int lo = k_lo + split * chunk;
+        k_hi = min(k_hi, lo + chunk);
+        k_lo = lo;
     }
 
     float m = -INFINITY, l = 0.f;
@@ -231,7 +236,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
 }
 
 struct Plan {
-    int gchunk, n_gchunks, tokens_per_tile, n_q_tiles, n_splits, split_len;
+    int gchunk, n_gchunks, tokens_per_tile, n_q_tiles, n_splits;
 };
 
 Plan make_plan(int n_seqs, int n_heads, int n_kv_heads, int max_q_len, int max_kv_len, int allow_split) {
@@ -242,18 +247,12 @@ Plan make_plan(int n_seqs, int n_heads, int n_kv_heads, int max_q_len, int max_k
     pl.tokens_per_tile = R / pl.gchunk;
     pl.n_q_tiles = (max_q_len + pl.tokens_per_tile - 1) / pl.tokens_per_tile;
     pl.n_splits = 1;
-    pl.split_len = max_kv_len;
     const long long base = (long long)pl.n_q_tiles * n_kv_heads * pl.n_gchunks * n_seqs;
     if (allow_split && base < TARGET_CTAS && max_kv_len >= 2 * MIN_SPLIT) {
-        int want = (int)((TARGET_CTAS + base - 1) / base);
+        const int want = (int)((TARGET_CTAS + base - 1) / base);
         const int most = max_kv_len / MIN_SPLIT;
-        if (want > most) want = most;
-        if (want > 1) {
-            int len = (max_kv_len + want - 1) / want;
-            len = (len + TK - 1) / TK * TK;
-            pl.split_len = len;
-            pl.n_splits = (max_kv_len + len - 1) / len;
-        }
+        pl.n_splits = want < most ? want : most;
+        if (pl.n_splits < 1) pl.n_splits = 1;
     }
     return pl;
 }
@@ -264,9 +263,11 @@ template <typename T, int HD_MAX>
 int launch(const AttnParams& p, dim3 grid, cudaStream_t s) {
     const size_t smem = smem_bytes(p.head_dim);
     auto kern = paged_attention_kernel<T, HD_MAX>;
-    if (smem > 48 * 1024) {
+    static int raised = 0;         // per instantiation: the largest limit set so far
+    if (smem > 48 * 1024 && (int)smem > raised) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
+        raised = (int)smem;
     }
     kern<<<grid, NT, smem, s>>>(p);
     TL_LAUNCH_CHECK();
@@ -321,7 +322,7 @@ extern "C" int tl_paged_attention(const void* q, const void* k_pages, const void
     p.group = n_heads / n_kv_heads; p.gchunk = pl.gchunk; p.n_gchunks = pl.n_gchunks;
     p.tokens_per_tile = pl.tokens_per_tile;
     p.window = window > 0 ? window : 0;
-    p.n_splits = pl.n_splits; p.split_len = pl.split_len;
+    p.n_splits = pl.n_splits;
     p.scale = scale;
     p.part_o = workspace;
     p.part_ml = workspace ? workspace + (size_t)n_tokens * n_heads * pl.n_splits * head_dim : nullptr;

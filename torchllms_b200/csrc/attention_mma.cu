@@ -43,7 +43,7 @@ struct MmaParams {
     int group, ng, n_gchunks;   // ng: heads of a group per 16-row tile
     int tpw;                    // tokens per 16-row tile
     int window;
-    int n_splits, split_len;
+    int n_splits;
     float scale_log2;           // scale * log2(e)
 };
 
@@ -121,8 +121,13 @@ __global__ void __launch_bounds__(NT) attention_mma_kernel(const MmaParams p) {
     int k_lo = p.window > 0 ? max(0, qpos_base + tok0 - p.window + 1) : 0;
     int k_hi = qpos_base + cta_tok_hi;                                   // last query's position + 1
     if (p.n_splits > 1) {
-        k_lo = max(k_lo, split * p.split_len);
-        k_hi = min(k_hi, (split + 1) * p.split_len);
+        // every request cuts its own visible keys evenly, in whole tiles, so the launch shape
+        // depends on the batch size only and not on how long the requests have grown
+        const int len = max(k_hi - k_lo, 0);
+        const int chunk = ((len + p.n_splits - 1) / p.n_splits + BN - 1) / BN * BN;
+        const int lo = k_lo + split * chunk;
+        k_hi = min(k_hi, lo + chunk);
+        k_lo = lo;
     }
 
     // rows of this thread: g and g + 8 of the warp's tile
@@ -361,7 +366,7 @@ __global__ void merge_partials_kernel(const float* __restrict__ part_o, const fl
 }
 
 struct Plan {
-    int ng, n_gchunks, tpw, key_split, n_q_tiles, n_splits, split_len;
+    int ng, n_gchunks, tpw, key_split, n_q_tiles, n_splits;
 };
 
 Plan make_plan(int n_seqs, int n_heads, int n_kv_heads, int max_q_len, int max_kv_len, int allow_split) {
@@ -374,19 +379,13 @@ Plan make_plan(int n_seqs, int n_heads, int n_kv_heads, int max_q_len, int max_k
     const int tokens_per_cta = pl.key_split ? pl.tpw : pl.tpw * NW;
     pl.n_q_tiles = (max_q_len + tokens_per_cta - 1) / tokens_per_cta;
     pl.n_splits = 1;
-    pl.split_len = max_kv_len;
     if (pl.key_split && allow_split) {
         const long long base = (long long)pl.n_q_tiles * n_kv_heads * pl.n_gchunks * n_seqs;
         if (base < TARGET_CTAS && max_kv_len >= 2 * MIN_SPLIT) {
             int want = (int)((TARGET_CTAS + base - 1) / base);
             const int most = max_kv_len / MIN_SPLIT;
-            if (want > most) want = most;
-            if (want > 1) {
-                int len = (max_kv_len + want - 1) / want;
-                len = (len + BN - 1) / BN * BN;
-                pl.split_len = len;
-                pl.n_splits = (max_kv_len + len - 1) / len;
-            }
+            pl.n_splits = want < most ? want : most;
+            if (pl.n_splits < 1) pl.n_splits = 1;
         }
     }
     return pl;
@@ -400,9 +399,11 @@ int launch(const MmaParams& p, dim3 grid, cudaStream_t s) {
     const size_t merge = KEY_SPLIT ? (size_t)(NW * 16 * (HD + 2)) * sizeof(float) : 0;
     if (merge > smem) smem = merge;
     auto kern = attention_mma_kernel<HD, KEY_SPLIT>;
-    if (smem > 48 * 1024) {
+    static bool raised = false;    // per instantiation: the limit is raised once (one device per process)
+    if (smem > 48 * 1024 && !raised) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
+        raised = true;
     }
     kern<<<grid, NT, smem, s>>>(p);
     TL_LAUNCH_CHECK();
@@ -452,7 +453,7 @@ extern "C" int tl_paged_attention_mma(const void* q, const void* k_pages, const 
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
     p.group = n_heads / n_kv_heads; p.ng = pl.ng; p.n_gchunks = pl.n_gchunks; p.tpw = pl.tpw;
     p.window = window > 0 ? window : 0;
-    p.n_splits = pl.n_splits; p.split_len = pl.split_len;
+    p.n_splits = pl.n_splits;
     p.scale_log2 = scale * LOG2E;
     p.part_o = workspace;
     p.part_ml = workspace ? workspace + (size_t)n_tokens * n_heads * pl.n_splits * head_dim : nullptr;

@@ -38,6 +38,7 @@ class Model:
                           mixer_norm=layer.mixer_norm, ffn_norm=layer.ffn_norm)
             self.blocks.append(BLOCKS.build(PartSpec(layer.block.kind, params), self.env))
         self.final_norm = NORMS.build(spec.final_norm, self.env)
+        self.graph_safe = self.final_norm.graph_safe and all(b.graph_safe for b in self.blocks)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
 

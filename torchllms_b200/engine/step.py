@@ -122,7 +122,7 @@ class Engine:
     """A model, its cache, and the step function over them."""
 
     def __init__(self, model: Model, *, page_size: int = 16, pool_tokens: int, max_num_seqs: int = 64,
-                 max_len: Optional[int] = None, max_step_tokens: int = 8192):
+                 max_len: Optional[int] = None, max_step_tokens: int = 8192, use_graphs: bool = True):
         self.model = model
         self.device = model.device
         self.max_len = int(max_len or model.max_positions)
@@ -136,6 +136,15 @@ class Engine:
         self.vocab_size = model.spec.vocab_size
         self.steps_run = 0
         self.tokens_run = 0
+        # Steps that hold one token per request have the same launch shapes whenever the number of
+        # requests is the same, so they are recorded once into a CUDA graph and replayed.
+        ops = model.ops
+        self.use_graphs = bool(use_graphs and self.device.type == "cuda" and model.graph_safe
+                               and getattr(ops, "graph_capturable", lambda d: False)(model.dtype))
+        self._graphs = {}          # (n_requests, n_wanted) -> (graph, logits buffer, launches)
+        self._graph_seen = {}
+        self._graph_pool = None
+        self.graph_replays = 0
 
     # ----------------------------------------------------------------- requests
     def claim(self) -> int:
@@ -146,6 +155,34 @@ class Engine:
 
     def can_run(self, wants: Sequence[Tuple[int, int]]) -> bool:
         return self.cache.can_extend(wants)
+
+    def _forward_graphed(self, ctx: StepContext, views) -> Optional[torch.Tensor]:
+        """Decode steps: the second step of a shape records a CUDA graph, later ones replay it.
+        The logits buffer of a shape is reused: its contents hold until the next step."""
+        key = (ctx.n_seqs, ctx.n_want)
+        entry = self._graphs.get(key)
+        if entry is None:
+            seen = self._graph_seen.get(key, 0)
+            self._graph_seen[key] = seen + 1
+            if seen == 0:
+                return self.model.forward(ctx, views)          # first time eager: loads libraries, sizes scratch
+            ops = self.model.ops
+            before = getattr(ops, "launches", 0)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                out = self.model.forward(ctx, views)
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            entry = (graph, out, getattr(ops, "launches", 0) - before)
+            self._graphs[key] = entry
+            if hasattr(ops, "launches"):
+                ops.launches = before
+        entry[0].replay()
+        self.graph_replays += 1
+        if hasattr(self.model.ops, "launches"):
+            self.model.ops.launches += entry[2]
+        return entry[1]
 
     # --------------------------------------------------------------------- step
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
@@ -208,8 +245,11 @@ class Engine:
             bt[:] = cache.block_table_rows(g, slots)
         buf.upload(B)
 
+        decode_only = max(q_lens) == 1
         ctx = StepContext(
-            n_tokens=T, n_seqs=B, n_want=len(want_rows), max_q_len=max(q_lens), max_kv_len=max(kv_lens),
+            n_tokens=T, n_seqs=B, n_want=len(want_rows), max_q_len=max(q_lens),
+            # decode steps plan for the longest sequence there can be, so their shape depends on B alone
+            max_kv_len=self.max_len if decode_only else max(kv_lens),
             token_ids=buf.dev_view("token_ids", T), positions=buf.dev_view("positions", T),
             seq_of_token=buf.dev_view("seq_of_token", T), q_start=buf.dev_view("q_start", B + 1),
             kv_len=buf.dev_view("kv_len", B), state_slot=buf.dev_view("state_slot", B),
@@ -219,7 +259,10 @@ class Engine:
         slot_maps = [buf.dev_view(f"slot_mapping{g}", T) for g in range(len(cache.groups))]
         views = [cache.run_view(i, block_tables, slot_maps) for i in range(cache.n_runs)]
         try:
-            logits = self.model.forward(ctx, views)
+            if decode_only and self.use_graphs:
+                logits = self._forward_graphed(ctx, views)
+            else:
+                logits = self.model.forward(ctx, views)
         except BaseException:
             for e, s in zip(entries, starts):  # leave the cache as the step found it
                 cache.truncate(e.handle, s)

@@ -89,8 +89,13 @@ class NativeOps:
                 "and there is no CPU implementation")
         self.launches = 0          # kernels of this library launched so far (a bench counts with it)
         self._workspace: Dict[Tuple[int, str], torch.Tensor] = {}
+        self._retired: list = []
         self._mm_out_dtype: Optional[bool] = None
         self._profile = None
+
+    def graph_capturable(self, dtype: torch.dtype) -> bool:
+        """Whether this library's launches for ``dtype`` may be recorded into a CUDA graph."""
+        return True
 
     # ------------------------------------------------------------ libraries
     def prepare(self, dtype: torch.dtype, sampling: bool = True) -> None:
@@ -258,7 +263,9 @@ class NativeOps:
         key = (device.index or 0, tag)
         buf = self._workspace.get(key)
         if buf is None or buf.numel() < floats:
-            buf = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+            if buf is not None:
+                self._retired.append(buf)      # a captured graph may still point into it
+            buf = torch.empty(max(floats, 1 << 22), dtype=torch.float32, device=device)
             self._workspace[key] = buf
         return buf
 

@@ -32,6 +32,7 @@ class PagedAttention(Mixer):
         self.scale = float(scale)
         self.window = None if window is None else int(window)
         self.position = POSITION_ENCODINGS.build(position, env)
+        self.graph_safe = self.position.graph_safe
         env.ops.check_attention_sizes(self.n_heads, self.n_kv_heads, self.head_dim, env.dtype)
         self.wqkv: Optional[torch.Tensor] = None
         self.wo: Optional[torch.Tensor] = None

@@ -73,6 +73,11 @@ class StateNeed:
 
 
 class Part:
+    # True when forward() only enqueues work on the current stream with shapes that depend on the
+    # step's token and request counts alone (no read-back, no host-side branching on device
+    # data): such a part may be captured into a CUDA graph and replayed.
+    graph_safe = False
+
     def expected_tensors(self) -> Dict[str, ExpectedTensor]:
         return {}
 

@@ -28,6 +28,7 @@ class PreNormBlock(Block):
         self.feed_forward = FEED_FORWARDS.build(feed_forward, env)
         self.mixer_norm = NORMS.build(mixer_norm, env)
         self.ffn_norm = NORMS.build(ffn_norm, env)
+        self.graph_safe = all(x.graph_safe for x in (self.mixer, self.feed_forward, self.mixer_norm, self.ffn_norm))
         self._subparts = ((mixer_prefix, self.mixer), (ffn_prefix, self.feed_forward),
                           (mixer_norm_prefix, self.mixer_norm), (ffn_norm_prefix, self.ffn_norm))
 

@@ -17,6 +17,8 @@ from .base import BuildEnv, FeedForward, as_compute, register_feed_forward
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, env: BuildEnv, *, dim: int, hidden: int):
         self.env = env
         self.dim, self.hidden = int(dim), int(hidden)

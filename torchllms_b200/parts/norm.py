@@ -20,6 +20,8 @@ from .base import BuildEnv, Norm, Residual, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, env: BuildEnv, *, dim: int, eps: float):
         self.env = env
         self.dim = int(dim)

@@ -57,6 +57,9 @@ class RotaryEncoding(PositionEncoding):
     """``pairing`` is ``"interleaved"`` (lanes 2i, 2i+1: the reference's and Meta's
     convention) or ``"half"`` (lanes i, i + hd/2: Hugging Face's)."""
 
+    graph_safe = True
+
+
     def __init__(self, env: BuildEnv, *, head_dim: int, theta: float,
                  scaling: Optional[Mapping[str, Any]] = None, pairing: str = "interleaved"):
         if pairing not in ("interleaved", "half"):
