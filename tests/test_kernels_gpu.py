@@ -306,6 +306,28 @@ def test_sampling_matches_twin(ops, vocab):
     assert got[5] == int(torch.argmax(logits[5]))       # a vanishing temperature is clamped, hence greedy
 
 
+@pytest.mark.parametrize("vocab", [8193, 50000, 128256])
+def test_sampling_without_top_k_over_many_ctas(ops, vocab):
+    """Large vocabularies without a rank filter take the two-stage kernels: same answers."""
+    n = 5
+    logits = rand((n, vocab), torch.float32, 31, 2.0)
+    logits[1, 4095] = logits[1, 4096] = logits[1, vocab - 1] = 40.0        # a tie across chunk borders
+    assert ops.sample(logits).tolist() == torch.argmax(logits, -1).tolist()
+    assert ops.sample(logits)[1].item() == 4095
+    temp = torch.tensor([0.0, 0.9, 1.0, 0.5, 2.0], dtype=torch.float32).cuda()
+    keys = torch.tensor([mix64(i + 5) - (1 << 63) for i in range(n)], dtype=torch.int64).cuda()
+    got = ops.sample(logits, temp, None, keys).tolist()
+    want = TWIN.sample(logits, temp, None, keys).tolist()
+    for r in range(n):
+        if got[r] != want[r]:
+            t = max(float(temp[r]), 1e-5)
+            score = logits[r].cpu().numpy() / np.float32(t) + noise_row(int(keys[r]) & ((1 << 64) - 1), vocab)
+            assert abs(score[got[r]] - score[want[r]]) < 1e-4 * max(1.0, abs(score[want[r]]))
+    # and the single-CTA kernel, asked through a top_k that filters nothing, agrees
+    top_k = torch.zeros(n, dtype=torch.int32).cuda()
+    assert ops.sample(logits, temp, top_k, keys).tolist() == got
+
+
 def test_sampling_follows_the_softmax(ops):
     """Frequencies over many keys approach softmax(logits / T), and top-k never leaves its set."""
     vocab, n = 12, 20000

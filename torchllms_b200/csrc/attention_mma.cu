@@ -23,7 +23,7 @@ namespace {
 constexpr int BN = 64;       // keys per tile
 constexpr int NW = 4;        // warps per CTA
 constexpr int NT = NW * 32;
-constexpr int TARGET_CTAS = 148 * 3;
+constexpr int TARGET_CTAS = 148 * 3;   // three CTAs of the key-split shape fit an SM
 constexpr int MIN_SPLIT = 128;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
@@ -40,6 +40,7 @@ struct MmaParams {
     float* part_ml;  // [T * H, n_splits, 2]
     int table_stride;
     int n_heads, n_kv_heads, page_size;
+    int page_shift;             // log2(page_size) when it is a power of two, else -1
     int group, ng, n_gchunks;   // ng: heads of a group per 16-row tile
     int tpw;                    // tokens per 16-row tile
     int window;
@@ -74,7 +75,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 
 template <int HD, bool KEY_SPLIT>
-__global__ void __launch_bounds__(NT) attention_mma_kernel(const MmaParams p) {
+__global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(const MmaParams p) {
     constexpr int PITCH = HD + 8;                 // bf16 elements per shared-memory row
     constexpr int QROWS = KEY_SPLIT ? 16 : 16 * NW;
     constexpr int KG = KEY_SPLIT ? 1 : 4;         // 16-key groups of a tile that one warp handles
@@ -142,20 +143,36 @@ __global__ void __launch_bounds__(NT) attention_mma_kernel(const MmaParams p) {
     const int warp_qmax = __reduce_max_sync(0xffffffffu, max(qpos[0], qpos[1]));
 
     const int* table = p.block_table + (size_t)b * p.table_stride;
+    // A thread always copies the same 16-byte column of a row: chunk c = tid + i * NT covers key
+    // (tid / CHUNKS) + i * (NT / CHUNKS), column tid % CHUNKS.
+    const int ld_part = (tid % CHUNKS) * 8;
+    const int ld_key0 = tid / CHUNKS;
+    constexpr int LD_STEP = NT / CHUNKS;          // keys between two chunks of one thread
+    constexpr int LD_ITERS = BN / LD_STEP;
+    const size_t head_off = (size_t)kvh * p.page_size * HD + ld_part;
+    const size_t page_stride = (size_t)p.n_kv_heads * p.page_size * HD;
     auto load_tile = [&](int stage, int k0) {
-        __nv_bfloat16* kd = Ks + stage * BN * PITCH;
-        __nv_bfloat16* vd = Vs + stage * BN * PITCH;
-        for (int c = tid; c < BN * CHUNKS; c += NT) {
-            const int j = c / CHUNKS, part = c - j * CHUNKS;
+        __nv_bfloat16* kd = Ks + stage * BN * PITCH + ld_part;
+        __nv_bfloat16* vd = Vs + stage * BN * PITCH + ld_part;
+#pragma unroll
+        for (int i = 0; i < LD_ITERS; ++i) {
+            const int j = ld_key0 + i * LD_STEP;
             const int kpos = k0 + j;
             if (kpos < k_hi) {   // kpos >= k_lo always: pages behind a window may be gone and are never touched
-                const int page = table[kpos / p.page_size];
-                const size_t off = (((size_t)page * p.n_kv_heads + kvh) * p.page_size + kpos % p.page_size) * HD + part * 8;
-                cp_async16(kd + j * PITCH + part * 8, p.k_pages + off);
-                cp_async16(vd + j * PITCH + part * 8, p.v_pages + off);
+                int blk, slot;
+                if (p.page_shift >= 0) {
+                    blk = kpos >> p.page_shift;
+                    slot = kpos & (p.page_size - 1);
+                } else {
+                    blk = kpos / p.page_size;
+                    slot = kpos - blk * p.page_size;
+                }
+                const size_t off = (size_t)table[blk] * page_stride + head_off + (size_t)slot * HD;
+                cp_async16(kd + j * PITCH, p.k_pages + off);
+                cp_async16(vd + j * PITCH, p.v_pages + off);
             } else {
-                *reinterpret_cast<uint4*>(kd + j * PITCH + part * 8) = make_uint4(0u, 0u, 0u, 0u);
-                *reinterpret_cast<uint4*>(vd + j * PITCH + part * 8) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(kd + j * PITCH) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(vd + j * PITCH) = make_uint4(0u, 0u, 0u, 0u);
             }
         }
     };
@@ -451,6 +468,9 @@ extern "C" int tl_paged_attention_mma(const void* q, const void* k_pages, const 
     p.out = (__nv_bfloat16*)out;
     p.block_table = block_table; p.q_start = q_start; p.kv_len = kv_len; p.table_stride = table_stride;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
+    p.page_shift = -1;
+    for (int sh = 0; sh < 31; ++sh)
+        if ((1 << sh) == page_size) p.page_shift = sh;
     p.group = n_heads / n_kv_heads; p.ng = pl.ng; p.n_gchunks = pl.n_gchunks; p.tpw = pl.tpw;
     p.window = window > 0 ? window : 0;
     p.n_splits = pl.n_splits;

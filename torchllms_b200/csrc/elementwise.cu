@@ -19,22 +19,52 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
     for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = to_float(src[d]);
 }
 
-template <typename TD, typename TO>
+// four contiguous elements as floats
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<unsigned*>(&a);
+    raw.y = *reinterpret_cast<unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// VEC = 4: dim is a multiple of 4 and every row starts 16-byte aligned; VEC = 1: anything.
+template <typename TD, typename TO, int VEC>
 __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta,
                                const float* __restrict__ weight, TO* __restrict__ out,
                                const int* __restrict__ rows, int dim, float eps, int write_back) {
-    extern __shared__ float row_buf[];  // the summed row, kept for the second pass
+    extern __shared__ __align__(16) float row_buf[];  // the summed row, kept for the second pass
     __shared__ float warp_part[32];
     const int o = blockIdx.x;
     const int r = rows ? rows[o] : o;
     float* hr = h + (size_t)r * dim;
     const TD* dr = delta ? delta + (size_t)r * dim : nullptr;
     float ss = 0.f;
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-        float x = hr[d];
-        if (dr) x += to_float(dr[d]);
-        row_buf[d] = x;
-        ss += x * x;
+    if (VEC == 4) {
+        for (int d = threadIdx.x * 4; d < dim; d += blockDim.x * 4) {
+            float4 x = load4(hr + d);
+            if (dr) {
+                const float4 y = load4(dr + d);
+                x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+            }
+            store4(row_buf + d, x);
+            ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+        }
+    } else {
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+            float x = hr[d];
+            if (dr) x += to_float(dr[d]);
+            row_buf[d] = x;
+            ss += x * x;
+        }
     }
     ss = warp_sum(ss);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
@@ -48,10 +78,19 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
     __syncthreads();
     const float rstd = rsqrtf(warp_part[0] / (float)dim + eps);
     TO* orow = out + (size_t)o * dim;
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-        const float x = row_buf[d];
-        if (write_back) hr[d] = x;
-        orow[d] = from_float<TO>(x * rstd * weight[d]);
+    if (VEC == 4) {
+        for (int d = threadIdx.x * 4; d < dim; d += blockDim.x * 4) {   // each thread re-reads what it wrote
+            const float4 x = load4(row_buf + d);
+            const float4 w = load4(weight + d);
+            if (write_back) store4(hr + d, x);
+            store4(orow + d, make_float4(x.x * rstd * w.x, x.y * rstd * w.y, x.z * rstd * w.z, x.w * rstd * w.w));
+        }
+    } else {
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+            const float x = row_buf[d];
+            if (write_back) hr[d] = x;
+            orow[d] = from_float<TO>(x * rstd * weight[d]);
+        }
     }
 }
 
@@ -89,12 +128,16 @@ static int launch_rmsnorm(float* h, const void* delta, const float* w, void* out
                           int n_out, int dim, float eps, int write_back, cudaStream_t s) {
     const size_t smem = (size_t)dim * sizeof(float);
     if (smem > 200 * 1024) return TL_TOO_LARGE;
-    auto kern = rmsnorm_kernel<TD, TO>;
+    const bool vec = dim % 4 == 0 && aligned16(h) && aligned16(w) && aligned16(out) &&
+                     (delta == nullptr || (reinterpret_cast<uintptr_t>(delta) & 7u) == 0);
+    auto kern = vec ? rmsnorm_kernel<TD, TO, 4> : rmsnorm_kernel<TD, TO, 1>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+    const int per_thread = vec ? 4 : 1;
+    int threads = (dim / per_thread + 31) / 32 * 32;
+    threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
     kern<<<n_out, threads, smem, s>>>(h, (const TD*)delta, w, (TO*)out, rows, dim, eps, write_back);
     TL_LAUNCH_CHECK();
     return TL_OK;

@@ -127,7 +127,90 @@ __global__ void __launch_bounds__(NT) sample_kernel(const float* __restrict__ lo
     }
 }
 
+// ---- two-stage form for rows without top-k: many CTAs per row, then one warp per row
+constexpr int CHUNK = 4096;      // vocabulary entries per stage-one CTA
+constexpr int NT1 = 256;
+
+__device__ __forceinline__ void better(float& bv, int& bi, float ov, int oi) {
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+}
+
+__global__ void __launch_bounds__(NT1) sample_stage1_kernel(const float* __restrict__ logits, long long row_stride, int V,
+                                                            const float* __restrict__ temperature,
+                                                            const unsigned long long* __restrict__ row_keys,
+                                                            float* __restrict__ part_v, int* __restrict__ part_i) {
+    __shared__ float best_v[NT1 / 32];
+    __shared__ int best_i[NT1 / 32];
+    const int r = blockIdx.y, chunk = blockIdx.x;
+    const float* row = logits + (size_t)r * row_stride;
+    const float temp = temperature ? temperature[r] : 0.f;
+    const bool greedy = !(temp > 0.f);
+    const float t = fmaxf(temp, 1e-5f);
+    const unsigned long long key = greedy ? 0ull : row_keys[r];
+    const int hi = min(V, (chunk + 1) * CHUNK);
+    float bv = -INFINITY;
+    int bi = V;
+    for (int i = chunk * CHUNK + threadIdx.x; i < hi; i += NT1) {
+        const float x = row[i];
+        const float s = greedy ? x : x / t + neg_log_exp1(key, (unsigned)i);
+        better(bv, bi, s, i);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        bv = lane < NT1 / 32 ? best_v[lane] : -INFINITY;
+        bi = lane < NT1 / 32 ? best_i[lane] : V;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+            better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+        if (lane == 0) {
+            part_v[(size_t)r * gridDim.x + chunk] = bv;
+            part_i[(size_t)r * gridDim.x + chunk] = bi;
+        }
+    }
+}
+
+__global__ void sample_stage2_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
+                                     int n_chunks, int V, int* __restrict__ out) {
+    const int r = blockIdx.x, lane = threadIdx.x;
+    float bv = -INFINITY;
+    int bi = V;
+    for (int c = lane; c < n_chunks; c += 32) better(bv, bi, part_v[(size_t)r * n_chunks + c], part_i[(size_t)r * n_chunks + c]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+    if (lane == 0) out[r] = bi < V ? bi : 0;
+}
+
 }  // namespace
+
+// How many 4-byte words of scratch tl_sample_wide needs for this many rows of this vocabulary.
+extern "C" long long tl_sample_wide_scratch(int n_rows, int vocab) {
+    const long long chunks = (vocab + CHUNK - 1) / CHUNK;
+    return 2 * chunks * n_rows;
+}
+
+// Rows without top-k, spread over many CTAs: same result as tl_sample.  scratch: see above.
+extern "C" int tl_sample_wide(const float* logits, long long row_stride, int n_rows, int vocab,
+                              const float* temperature, const unsigned long long* row_keys,
+                              void* scratch, int* out, void* stream) {
+    if (n_rows <= 0) return TL_OK;
+    if (vocab <= 0 || row_stride < vocab || n_rows > 65535 || scratch == nullptr) return TL_BAD_SIZE;
+    if (temperature != nullptr && row_keys == nullptr) return TL_BAD_SIZE;
+    const int chunks = (vocab + CHUNK - 1) / CHUNK;
+    float* part_v = (float*)scratch;
+    int* part_i = (int*)scratch + (size_t)chunks * n_rows;
+    cudaStream_t s = (cudaStream_t)stream;
+    sample_stage1_kernel<<<dim3(chunks, n_rows), NT1, 0, s>>>(logits, row_stride, vocab, temperature, row_keys, part_v, part_i);
+    TL_LAUNCH_CHECK();
+    sample_stage2_kernel<<<n_rows, 32, 0, s>>>(part_v, part_i, chunks, vocab, out);
+    TL_LAUNCH_CHECK();
+    return TL_OK;
+}
 
 // temperature, top_k and row_keys may be null: then every row is greedy / unfiltered.  A row
 // whose temperature is not positive is greedy.  All arrays live on the device.

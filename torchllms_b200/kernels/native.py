@@ -345,7 +345,17 @@ class NativeOps:
             _cuda_contig(top_k, "top_k", torch.int32)
             _need(top_k.numel() == n, "one top_k per row")
         out = torch.empty((n,), dtype=torch.int32, device=logits.device)
-        rc = self._lib("sampling").tl_sample(
+        lib = self._lib("sampling")
+        if top_k is None and vocab > 8192:
+            # no rank filter: spread every row over many CTAs, then pick among their candidates
+            lib.tl_sample_wide_scratch.restype = ctypes.c_longlong
+            ws = self._scratch(logits.device, lib.tl_sample_wide_scratch(n, vocab), "sampling")
+            rc = lib.tl_sample_wide(_ptr(logits), ctypes.c_longlong(logits.stride(0)), n, vocab, _ptr(temperature),
+                                    _ptr(row_keys), _ptr(ws), _ptr(out), _stream())
+            _check(rc, "sample_wide")
+            self.launches += 2
+            return out
+        rc = lib.tl_sample(
             _ptr(logits), ctypes.c_longlong(logits.stride(0)), n, vocab, _ptr(temperature), _ptr(top_k),
             _ptr(row_keys), _ptr(out), _stream())
         _check(rc, "sample")
