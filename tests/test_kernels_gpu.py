@@ -113,6 +113,44 @@ def test_linear_bfloat16(ops, M, N, K):
         torch.testing.assert_close(got.float(), want, atol=tol(out_dtype, 1e-3, 8e-2), rtol=tol(out_dtype, 1e-4, 1e-2))
 
 
+@pytest.mark.parametrize("M", [1, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,K", [(128, 64), (96, 96), (1000, 200), (6144, 4096), (4096, 14336), (300, 8)])
+def test_gemm_tcgen05_few_rows(ops, M, N, K):
+    """The tensor-core kernel for decode-sized products: partial sums over K splits add up to x @ w^T."""
+    x, w = rand((M, K), torch.bfloat16, 40 + M), rand((N, K), torch.bfloat16, 41, 0.5)
+    want = x.double() @ w.double().t()
+    for out_dtype in DTYPES:
+        got = ops.gemm_tcgen05(x, w, out_dtype)
+        ops.check_status()
+        if got.dim() == 3:
+            assert got.dtype == torch.float32 and got.shape[1:] == (M, N)
+            got = got.double().sum(0)
+        else:
+            assert got.dtype == out_dtype and got.shape == (M, N)
+            got = got.double()
+        scale = want.abs().max().item()
+        bound = (2e-6 * math.sqrt(K) + 1e-6) if out_dtype == torch.float32 or K > 256 else 5e-3
+        if out_dtype == torch.bfloat16 and got.dtype != torch.float64:
+            bound = 5e-3
+        err = (got - want).abs().max().item() / scale
+        assert err < max(bound, 5e-3 if out_dtype == torch.bfloat16 else 0), (err, out_dtype)
+    # the public entry: 2-D result whatever the splits, and partial sums on request
+    y = ops.linear(x, w)
+    assert y.shape == (M, N) and y.dtype == torch.bfloat16
+    torch.testing.assert_close(y.double(), want, atol=2e-2 * want.abs().max().item(), rtol=2e-2)
+    parts = ops.linear(x, w, partials_ok=True)
+    assert parts.dim() in (2, 3)
+
+
+def test_gemm_tcgen05_rows_do_not_depend_on_the_batch(ops):
+    """A token's product is the same bits alone, padded to 16, or among 64 rows."""
+    x, w = rand((64, 4096), torch.bfloat16, 50), rand((512, 4096), torch.bfloat16, 51, 0.3)
+    full = ops.gemm_tcgen05(x, w, torch.float32)
+    one = ops.gemm_tcgen05(x[5:6].contiguous(), w, torch.float32)
+    some = ops.gemm_tcgen05(x[:20].contiguous(), w, torch.float32)
+    assert torch.equal(full[..., 5, :], one[..., 0, :]) and torch.equal(full[..., :20, :], some)
+
+
 # ------------------------------------------------------------------------------------ rope
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -59,6 +59,8 @@ class TorchOps:
         return table[token_ids.long()].float()
 
     def rmsnorm(self, h, delta, weight, eps, out_dtype, rows=None):
+        if delta is not None and delta.dim() == 3:
+            delta = delta.float().sum(0)
         x = h if delta is None else h + delta.float()
         if rows is None:
             if delta is not None:
@@ -68,12 +70,15 @@ class TorchOps:
         y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight
         return y.to(out_dtype)
 
-    def swiglu(self, gate_up):
+    def swiglu(self, gate_up, out_dtype=None):
+        out_dtype = out_dtype or gate_up.dtype
+        if gate_up.dim() == 3:
+            gate_up = gate_up.float().sum(0)
         hidden = gate_up.shape[1] // 2
         g, u = gate_up[:, :hidden].float(), gate_up[:, hidden:].float()
-        return (g / (1 + torch.exp(-g)) * u).to(gate_up.dtype)
+        return (g / (1 + torch.exp(-g)) * u).to(out_dtype)
 
-    def linear(self, x, w, out_dtype=None):
+    def linear(self, x, w, out_dtype=None, partials_ok=False):
         out_dtype = out_dtype or x.dtype
         if x.dtype == torch.float32:
             return (x @ w.t()).to(out_dtype)
@@ -83,7 +88,10 @@ class TorchOps:
         return (x.float() @ w.float().t()).to(out_dtype)
 
     def rope_kv_write(self, qkv, positions, table, *, n_heads, n_kv_heads, head_dim, interleaved,
-                      k_pages, v_pages, slot_mapping, page_size):
+                      k_pages, v_pages, slot_mapping, page_size, out_dtype=None):
+        out_dtype = out_dtype or qkv.dtype
+        if qkv.dim() == 3:
+            qkv = qkv.float().sum(0)
         T = qkv.shape[0]
         x = qkv.float().view(T, n_heads + 2 * n_kv_heads, head_dim)
         cs = table[positions.long()]            # [T, hd/2, 2]
@@ -99,10 +107,10 @@ class TorchOps:
             out[..., 0::2], out[..., 1::2] = ya, yb
         else:
             out[..., : head_dim // 2], out[..., head_dim // 2:] = ya, yb
-        q = out[:, :n_heads].to(qkv.dtype).contiguous()
+        q = out[:, :n_heads].to(out_dtype).contiguous()
         if k_pages is not None:
-            k = out[:, n_heads:].to(qkv.dtype)
-            v = x[:, n_heads + n_kv_heads:].to(qkv.dtype)
+            k = out[:, n_heads:].to(out_dtype)
+            v = x[:, n_heads + n_kv_heads:].to(out_dtype)
             sm = slot_mapping.long()
             page, slot = sm // page_size, sm % page_size
             k_pages[page, :, slot] = k

@@ -16,6 +16,7 @@
 //              cut over several CTAs; those partials go to a float32 workspace and are combined
 //              by merge_partials_kernel (same layout as the general kernel's).
 #include "common.cuh"
+#include <limits.h>
 #include <math.h>
 
 namespace {
@@ -141,6 +142,8 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
         qpos[i] = (rr < p.tpw * ng && tok < ql) ? qpos_base + tok : -1;
     }
     const int warp_qmax = __reduce_max_sync(0xffffffffu, max(qpos[0], qpos[1]));
+    // smallest position among the warp's real rows (rows without a query are never stored)
+    const int warp_qmin = __reduce_min_sync(0xffffffffu, min(qpos[0] < 0 ? INT_MAX : qpos[0], qpos[1] < 0 ? INT_MAX : qpos[1]));
 
     const int* table = p.block_table + (size_t)b * p.table_stride;
     // A thread always copies the same 16-byte column of a row: chunk c = tid + i * NT covers key
@@ -221,16 +224,31 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
             }
             // ---- mask, streaming softmax (base 2)
             float mx[2] = {-INFINITY, -INFINITY};
+            const int share_lo = k0 + key_off, share_hi = share_lo + 16 * KG;   // this warp's keys of the tile
+            const bool all_visible = share_hi <= k_hi && share_hi - 1 <= warp_qmin &&
+                                     (p.window <= 0 || share_lo > warp_qmax - p.window);
+            if (all_visible) {       // every key counts for every row: no per-element tests
 #pragma unroll
-            for (int nt = 0; nt < 2 * KG; ++nt) {
+                for (int nt = 0; nt < 2 * KG; ++nt) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int i = e >> 1;
-                    const int kpos = k0 + key_off + nt * 8 + 2 * t + (e & 1);
-                    const bool ok = kpos <= qpos[i] && kpos < k_hi && (p.window <= 0 || kpos > qpos[i] - p.window);
-                    const float v = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
-                    s[nt][e] = v;
-                    mx[i] = fmaxf(mx[i], v);
+                    for (int e = 0; e < 4; ++e) {
+                        const float v = s[nt][e] * p.scale_log2;
+                        s[nt][e] = v;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < 2 * KG; ++nt) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = e >> 1;
+                        const int kpos = share_lo + nt * 8 + 2 * t + (e & 1);
+                        const bool ok = kpos <= qpos[i] && kpos < k_hi && (p.window <= 0 || kpos > qpos[i] - p.window);
+                        const float v = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
+                        s[nt][e] = v;
+                        mx[i] = fmaxf(mx[i], v);
+                    }
                 }
             }
             float alpha[2];
@@ -362,23 +380,37 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
     }
 }
 
-// out[row, d] = sum_i e^{m_i - M} o_i[d] / sum_i e^{m_i - M} l_i,  M = max_i m_i
+// out[row, d] = sum_i e^{m_i - M} o_i[d] / sum_i e^{m_i - M} l_i,  M = max_i m_i.
+// One CTA per row: the weights e^{m_i - M} are computed once (lanes over splits) into shared
+// memory, then every thread sums its head_dim lanes over the splits in order.
+constexpr int MERGE_MAX_SPLITS = 256;
 __global__ void merge_partials_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       __nv_bfloat16* __restrict__ out, int n_splits, int head_dim) {
+    __shared__ float wgt[MERGE_MAX_SPLITS];
+    __shared__ float red[2];
     const size_t row = blockIdx.x;
     const float* ml = part_ml + row * n_splits * 2;
-    float M = -INFINITY;
-    for (int i = 0; i < n_splits; ++i) M = fmaxf(M, ml[2 * i]);
-    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
-        float num = 0.f, den = 0.f;
-        for (int i = 0; i < n_splits; ++i) {
+    if (threadIdx.x < 32) {
+        float M = -INFINITY;
+        for (int i = threadIdx.x; i < n_splits; i += 32) M = fmaxf(M, ml[2 * i]);
+        M = warp_max(M);
+        float den = 0.f;
+        for (int i = threadIdx.x; i < n_splits; i += 32) {
             const float mi = ml[2 * i];
-            if (mi == -INFINITY) continue;
-            const float w = __expf(mi - M);
-            num = fmaf(w, part_o[(row * n_splits + i) * head_dim + d], num);
+            const float w = (mi == -INFINITY) ? 0.f : __expf(mi - M);
+            wgt[i] = w;
             den = fmaf(w, ml[2 * i + 1], den);
         }
-        out[row * head_dim + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+        den = warp_sum(den);
+        if (threadIdx.x == 0) red[0] = den;
+    }
+    __syncthreads();
+    const float den = red[0];
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float num = 0.f;
+        for (int i = 0; i < n_splits; ++i) num = fmaf(wgt[i], part_o[(row * n_splits + i) * head_dim + d], num);
+        out[row * head_dim + d] = __float2bfloat16_rn(num * inv);
     }
 }
 
@@ -396,13 +428,22 @@ Plan make_plan(int n_seqs, int n_heads, int n_kv_heads, int max_q_len, int max_k
     const int tokens_per_cta = pl.key_split ? pl.tpw : pl.tpw * NW;
     pl.n_q_tiles = (max_q_len + tokens_per_cta - 1) / tokens_per_cta;
     pl.n_splits = 1;
-    if (pl.key_split && allow_split) {
+    if (pl.key_split && allow_split && max_kv_len >= 2 * MIN_SPLIT) {
+        // CTAs run in waves of TARGET_CTAS; with s splits a CTA does 1/s of the keys.  Pick the s
+        // that makes (waves / s), the time in units of one unsplit CTA, smallest, charging each
+        // split a little for its partial results and the merge.
         const long long base = (long long)pl.n_q_tiles * n_kv_heads * pl.n_gchunks * n_seqs;
-        if (base < TARGET_CTAS && max_kv_len >= 2 * MIN_SPLIT) {
-            int want = (int)((TARGET_CTAS + base - 1) / base);
-            const int most = max_kv_len / MIN_SPLIT;
-            pl.n_splits = want < most ? want : most;
-            if (pl.n_splits < 1) pl.n_splits = 1;
+        int most = max_kv_len / MIN_SPLIT;
+        if (most > MERGE_MAX_SPLITS) most = MERGE_MAX_SPLITS;
+        if (most > 64) most = 64;
+        double best = 1e30;
+        for (int sp = 1; sp <= most; ++sp) {
+            const long long waves = (base * sp + TARGET_CTAS - 1) / TARGET_CTAS;
+            const double cost = (double)waves / sp + 0.01 * sp;
+            if (cost < best - 1e-9) {
+                best = cost;
+                pl.n_splits = sp;
+            }
         }
     }
     return pl;
@@ -489,7 +530,7 @@ extern "C" int tl_paged_attention_mma(const void* q, const void* k_pages, const 
     }
     if (rc != TL_OK) return rc;
     if (pl.n_splits > 1) {
-        merge_partials_kernel<<<dim3((unsigned)(n_tokens * n_heads)), dim3(head_dim >= 64 ? 64 : 32), 0, s>>>(
+        merge_partials_kernel<<<dim3((unsigned)n_tokens * (unsigned)n_heads), dim3(head_dim >= 128 ? 128u : 64u), 0, s>>>(
             p.part_o, p.part_ml, p.out, pl.n_splits, head_dim);
         TL_LAUNCH_CHECK();
     }

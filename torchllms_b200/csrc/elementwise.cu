@@ -37,8 +37,10 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
 }
 
 // VEC = 4: dim is a multiple of 4 and every row starts 16-byte aligned; VEC = 1: anything.
+// delta holds `splits` planes `plane` elements apart (partial sums of a split-K product); they
+// are added in order, then to the stream.
 template <typename TD, typename TO, int VEC>
-__global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+__global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta, int splits, long long plane,
                                const float* __restrict__ weight, TO* __restrict__ out,
                                const int* __restrict__ rows, int dim, float eps, int write_back) {
     extern __shared__ __align__(16) float row_buf[];  // the summed row, kept for the second pass
@@ -52,7 +54,11 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
         for (int d = threadIdx.x * 4; d < dim; d += blockDim.x * 4) {
             float4 x = load4(hr + d);
             if (dr) {
-                const float4 y = load4(dr + d);
+                float4 y = load4(dr + d);
+                for (int sp = 1; sp < splits; ++sp) {
+                    const float4 z = load4(dr + sp * plane + d);
+                    y.x += z.x; y.y += z.y; y.z += z.z; y.w += z.w;
+                }
                 x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
             }
             store4(row_buf + d, x);
@@ -61,7 +67,11 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
     } else {
         for (int d = threadIdx.x; d < dim; d += blockDim.x) {
             float x = hr[d];
-            if (dr) x += to_float(dr[d]);
+            if (dr) {
+                float y = to_float(dr[d]);
+                for (int sp = 1; sp < splits; ++sp) y += to_float(dr[sp * plane + d]);
+                x += y;
+            }
             row_buf[d] = x;
             ss += x * x;
         }
@@ -94,15 +104,20 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
     }
 }
 
-template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int hidden, long long total) {
+// `in` holds `splits` planes of [tokens, 2 * hidden] (partial sums of a split-K product), summed first
+template <typename TI, typename T>
+__global__ void swiglu_kernel(const TI* __restrict__ in, int splits, long long plane, T* __restrict__ out,
+                              int hidden, long long total) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (; i < total; i += stride) {
         const long long t = i / hidden;
         const int f = (int)(i - t * hidden);
-        const float g = to_float(in[t * 2 * hidden + f]);
-        const float u = to_float(in[t * 2 * hidden + hidden + f]);
+        float g = 0.f, u = 0.f;
+        for (int sp = 0; sp < splits; ++sp) {
+            g += to_float(in[sp * plane + t * 2 * hidden + f]);
+            u += to_float(in[sp * plane + t * 2 * hidden + hidden + f]);
+        }
         out[i] = from_float<T>(g / (1.f + expf(-g)) * u);
     }
 }
@@ -124,12 +139,12 @@ extern "C" int tl_embed(const int* ids, const void* table, int table_dtype, floa
 }
 
 template <typename TD, typename TO>
-static int launch_rmsnorm(float* h, const void* delta, const float* w, void* out, const int* rows,
-                          int n_out, int dim, float eps, int write_back, cudaStream_t s) {
+static int launch_rmsnorm(float* h, const void* delta, int splits, long long plane, const float* w, void* out,
+                          const int* rows, int n_out, int dim, float eps, int write_back, cudaStream_t s) {
     const size_t smem = (size_t)dim * sizeof(float);
     if (smem > 200 * 1024) return TL_TOO_LARGE;
-    const bool vec = dim % 4 == 0 && aligned16(h) && aligned16(w) && aligned16(out) &&
-                     (delta == nullptr || (reinterpret_cast<uintptr_t>(delta) & 7u) == 0);
+    const bool vec = dim % 4 == 0 && plane % 4 == 0 && aligned16(h) && aligned16(w) && aligned16(out) &&
+                     (delta == nullptr || aligned16(delta));
     auto kern = vec ? rmsnorm_kernel<TD, TO, 4> : rmsnorm_kernel<TD, TO, 1>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -138,40 +153,47 @@ static int launch_rmsnorm(float* h, const void* delta, const float* w, void* out
     const int per_thread = vec ? 4 : 1;
     int threads = (dim / per_thread + 31) / 32 * 32;
     threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
-    kern<<<n_out, threads, smem, s>>>(h, (const TD*)delta, w, (TO*)out, rows, dim, eps, write_back);
+    kern<<<n_out, threads, smem, s>>>(h, (const TD*)delta, splits, plane, w, (TO*)out, rows, dim, eps, write_back);
     TL_LAUNCH_CHECK();
     return TL_OK;
 }
 
-// delta may be null (then nothing is added); rows may be null (then row o is row o of h).
-extern "C" int tl_rmsnorm(float* h, const void* delta, int delta_dtype, const float* weight, void* out,
-                          int out_dtype, const int* rows, int n_out, int dim, float eps, int write_back,
-                          void* stream) {
+// delta may be null (then nothing is added); it may hold `delta_splits` planes of [rows of h, dim],
+// `delta_plane` elements apart, which are summed.  rows may be null (then row o is row o of h).
+extern "C" int tl_rmsnorm(float* h, const void* delta, int delta_dtype, int delta_splits, long long delta_plane,
+                          const float* weight, void* out, int out_dtype, const int* rows, int n_out, int dim,
+                          float eps, int write_back, void* stream) {
     if (n_out <= 0) return TL_OK;
-    if (dim <= 0) return TL_BAD_SIZE;
+    if (dim <= 0 || delta_splits < 1) return TL_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (delta_dtype == TL_F32 && out_dtype == TL_F32)
-        return launch_rmsnorm<float, float>(h, delta, weight, out, rows, n_out, dim, eps, write_back, s);
+        return launch_rmsnorm<float, float>(h, delta, delta_splits, delta_plane, weight, out, rows, n_out, dim, eps, write_back, s);
     if (delta_dtype == TL_BF16 && out_dtype == TL_BF16)
-        return launch_rmsnorm<__nv_bfloat16, __nv_bfloat16>(h, delta, weight, out, rows, n_out, dim, eps, write_back, s);
+        return launch_rmsnorm<__nv_bfloat16, __nv_bfloat16>(h, delta, delta_splits, delta_plane, weight, out, rows, n_out, dim, eps, write_back, s);
     if (delta_dtype == TL_F32 && out_dtype == TL_BF16)
-        return launch_rmsnorm<float, __nv_bfloat16>(h, delta, weight, out, rows, n_out, dim, eps, write_back, s);
+        return launch_rmsnorm<float, __nv_bfloat16>(h, delta, delta_splits, delta_plane, weight, out, rows, n_out, dim, eps, write_back, s);
     if (delta_dtype == TL_BF16 && out_dtype == TL_F32)
-        return launch_rmsnorm<__nv_bfloat16, float>(h, delta, weight, out, rows, n_out, dim, eps, write_back, s);
+        return launch_rmsnorm<__nv_bfloat16, float>(h, delta, delta_splits, delta_plane, weight, out, rows, n_out, dim, eps, write_back, s);
     return TL_BAD_DTYPE;
 }
 
-extern "C" int tl_swiglu(const void* in, void* out, int dtype, int n_tokens, int hidden, void* stream) {
+// in: [splits, n_tokens, 2 * hidden] of in_dtype (splits > 1 only for float32 partial sums); out: [n_tokens, hidden]
+extern "C" int tl_swiglu(const void* in, int in_dtype, int splits, void* out, int dtype, int n_tokens, int hidden,
+                         void* stream) {
     const long long total = (long long)n_tokens * hidden;
     if (total <= 0) return TL_OK;
+    if (splits < 1) return TL_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = 256;
     long long blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 32) blocks = 148 * 32;
-    if (dtype == TL_F32)
-        swiglu_kernel<float><<<(int)blocks, threads, 0, s>>>((const float*)in, (float*)out, hidden, total);
-    else if (dtype == TL_BF16)
-        swiglu_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, hidden, total);
+    const long long plane = 2 * total;
+    if (in_dtype == TL_F32 && dtype == TL_F32)
+        swiglu_kernel<float, float><<<(int)blocks, threads, 0, s>>>((const float*)in, splits, plane, (float*)out, hidden, total);
+    else if (in_dtype == TL_BF16 && dtype == TL_BF16)
+        swiglu_kernel<__nv_bfloat16, __nv_bfloat16><<<(int)blocks, threads, 0, s>>>((const __nv_bfloat16*)in, splits, plane, (__nv_bfloat16*)out, hidden, total);
+    else if (in_dtype == TL_F32 && dtype == TL_BF16)
+        swiglu_kernel<float, __nv_bfloat16><<<(int)blocks, threads, 0, s>>>((const float*)in, splits, plane, (__nv_bfloat16*)out, hidden, total);
     else
         return TL_BAD_DTYPE;
     TL_LAUNCH_CHECK();

@@ -1,0 +1,342 @@
+// C[M, N] = A[M, K] . W[N, K]^T in bfloat16 on the fifth-generation tensor cores, for few rows
+// (the projections of a decode step, where the work is streaming W once from HBM).
+//
+// Both operands are K-major as stored (activations row-major, weights [out, in] as nn.Linear
+// keeps them, torchllms/models/networks.py:474-493, :600-602).  The operands are swapped so that
+// 128 rows of W fill the 128 rows of a tcgen05.mma and the (padded) tokens are its N:
+//   D[w_row, token] = sum_k W[w_row, k] * A[token, k]        -> written out as C[token, w_row].
+//
+// One CTA computes one 128-row slab of W over one slice of K (split-K): the grid is
+// (slabs, splits), so that a narrow projection still puts a CTA or two on every SM.  Splits write
+// float32 partial sums C[split, M, N]; the kernels that read them (residual + norm, rope, swiglu)
+// add them up, in a fixed order, so nothing is reduced by atomics and results are reproducible.
+//
+// Inside a CTA (192 threads):
+//   warp 0, one lane : TMA producer - cp.async.bulk.tensor (no multicast) of a [128 x 64] tile of W
+//                      and a [BQ x 64] tile of A per stage into 128-byte-swizzled shared memory
+//   warp 1, one lane : issues tcgen05.mma (M 128, N BQ, K 16; four per stage), accumulator in TMEM,
+//                      tcgen05.commit frees the stage and finally signals the epilogue
+//   warps 2-5        : epilogue - tcgen05.ld of their 32 TMEM lanes, convert, coalesced stores
+// Every mbarrier wait is bounded: on a time-out the CTA records a code in the status word, drains,
+// frees its TMEM and returns.
+#include "common.cuh"
+#include <cuda.h>
+
+namespace {
+
+constexpr int BP = 128;          // rows of W per CTA (MMA M)
+constexpr int BK = 64;           // K per stage: 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NTHREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000ull * 1000ull * 1000ull;   // two seconds, then give up
+
+enum : int { ERR_TMA_WAIT = 101, ERR_MMA_WAIT = 102, ERR_EPI_WAIT = 103 };
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// false once WAIT_LIMIT_NS have passed, or as soon as another role has given up
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (unsigned i = 1;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 0u && (*abort_flag || global_ns() - t0 > WAIT_LIMIT_NS)) return false;
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ unsigned long long umma_desc(const void* tile, int k_byte_offset) {
+    const unsigned addr = smem_u32(tile) + (unsigned)k_byte_offset;
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);           // start address
+    d |= (unsigned long long)(0u) << 16;                         // leading byte offset: unused for swizzled K-major
+    d |= (unsigned long long)(1024u >> 4) << 32;                 // stride byte offset between 8-row groups
+    d |= (unsigned long long)1u << 46;                           // descriptor version of this architecture
+    d |= (unsigned long long)2u << 61;                           // layout: 128-byte swizzle
+    return d;
+}
+
+// instruction descriptor: bf16 x bf16 -> f32, both K-major, M = 128, N = n
+__host__ __device__ constexpr unsigned umma_idesc(int n) {
+    return (1u << 4)                  // accumulator format: f32
+         | (1u << 7)                  // a format: bf16
+         | (1u << 10)                 // b format: bf16
+         | ((unsigned)(n >> 3) << 17)
+         | ((unsigned)(BP >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
+                                          unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int N> struct TmemLoad;
+template <> struct TmemLoad<16> {
+    __device__ static __forceinline__ void run(unsigned taddr, unsigned (&r)[16]) {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                       "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                     : "r"(taddr));
+    }
+};
+
+struct GemmParams {
+    void* out;              // [splits, M, N], float32 or bfloat16 (bfloat16 only with one split)
+    int* status;            // error word (may live in mapped host memory)
+    int M, N, K;
+    int k_blocks_per_split; // stages each split walks
+    int out_is_f32;
+};
+
+template <int BQ, int STAGES>
+__global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                const __grid_constant__ CUtensorMap map_a,
+                                                                const GemmParams p) {
+    constexpr unsigned W_BYTES = BP * BK * 2, A_BYTES = BQ * BK * 2;
+    constexpr unsigned STAGE_BYTES = W_BYTES + A_BYTES;
+    constexpr unsigned TMEM_COLS = BQ < 32 ? 32 : BQ;
+    extern __shared__ unsigned char smem_raw[];
+    // tiles want 1024-byte alignment for the 128-byte swizzle
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
+    __shared__ __align__(8) unsigned long long full_bar[STAGES];
+    __shared__ __align__(8) unsigned long long empty_bar[STAGES];
+    __shared__ __align__(8) unsigned long long accum_bar;
+    __shared__ unsigned tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slab = blockIdx.x, split = blockIdx.y;
+    const int total_k_blocks = (p.K + BK - 1) / BK;
+    const int kb0 = split * p.k_blocks_per_split;
+    const int n_kb = max(0, min(p.k_blocks_per_split, total_k_blocks - kb0));
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_d = tmem_base_slot;
+    volatile int* aborted = &abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % STAGES;
+                if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, aborted)) {
+                    abort_flag = 1;
+                    atomicExch(p.status, ERR_TMA_WAIT);
+                    break;
+                }
+                unsigned char* wt = tiles + s * STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                tma_load_2d(wt, &map_w, &full_bar[s], (kb0 + i) * BK, slab * BP);
+                tma_load_2d(wt + W_BYTES, &map_a, &full_bar[s], (kb0 + i) * BK, 0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- tensor-core issuer
+            constexpr unsigned idesc = umma_idesc(BQ);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(&full_bar[s], (i / STAGES) & 1, aborted)) {
+                    abort_flag = 1;
+                    atomicExch(p.status, ERR_MMA_WAIT);
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                unsigned char* wt = tiles + s * STAGE_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    umma_bf16(tmem_d, umma_desc(wt, k * UMMA_K * 2), umma_desc(wt + W_BYTES, k * UMMA_K * 2), idesc,
+                              (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&empty_bar[s]);      // the stage is free once these MMAs have read it
+            }
+            if (ok) umma_commit(&accum_bar);     // everything issued so far has landed in TMEM
+        }
+    } else {
+        // ---- epilogue: warp w owns TMEM lanes 32 * (w % 4) .. + 31, i.e. rows of W of this slab
+        const int quarter = warp & 3;
+        const int w_row = slab * BP + quarter * 32 + lane;
+        bool ok = true;
+        if (n_kb > 0) {
+            ok = mbar_wait(&accum_bar, 0, aborted);
+            if (!ok && lane == 0) {
+                abort_flag = 1;
+                atomicExch(p.status, ERR_EPI_WAIT);
+            }
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const size_t plane = (size_t)p.M * p.N;
+#pragma unroll
+            for (int c0 = 0; c0 < BQ; c0 += 16) {
+                unsigned r[16];
+                if (n_kb > 0) {
+                    TmemLoad<16>::run(tmem_d + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = 0u;
+                }
+                if (w_row < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int tok = c0 + j;
+                        if (tok < p.M) {
+                            const float v = __uint_as_float(r[j]);
+                            const size_t at = (size_t)split * plane + (size_t)tok * p.N + w_row;
+                            if (p.out_is_f32) reinterpret_cast<float*>(p.out)[at] = v;
+                            else reinterpret_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(v);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// rows x K bf16, row-major; box = box_rows x 64 elements, 128-byte swizzle, zero fill outside
+int make_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr) return TL_BAD_SIZE;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS ? TL_OK : TL_BAD_SIZE;
+}
+
+template <int BQ, int STAGES>
+int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, int slabs, int splits, cudaStream_t s) {
+    constexpr size_t smem = (size_t)STAGES * (BP * BK * 2 + BQ * BK * 2) + 1024;
+    auto kern = gemm_tcgen05_kernel<BQ, STAGES>;
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        raised = true;
+    }
+    kern<<<dim3(slabs, splits), NTHREADS, smem, s>>>(mw, ma, p);
+    TL_LAUNCH_CHECK();
+    return TL_OK;
+}
+
+}  // namespace
+
+// How many K splits the kernel would use for a [N, K] weight: a function of the weight's shape
+// only, so a token's result does not depend on what else is in the batch.
+extern "C" int tl_gemm_tcgen05_splits(int N, int K) {
+    const int slabs = (N + BP - 1) / BP;
+    const int k_blocks = (K + BK - 1) / BK;
+    int splits = (2 * 148 + slabs - 1) / slabs;
+    const int most = k_blocks / 4 > 0 ? k_blocks / 4 : 1;      // at least four stages of work per CTA
+    if (splits > most) splits = most;
+    if (splits < 1) splits = 1;
+    const int per = (k_blocks + splits - 1) / splits;
+    return (k_blocks + per - 1) / per;                          // no empty split
+}
+
+// 1 if the kernel takes this problem: at most 64 rows, K a multiple of 8 (TMA wants 16-byte row
+// pitches), operands 16-byte aligned.
+extern "C" int tl_gemm_tcgen05_supports(int M, int N, int K) {
+    return (M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0) ? 1 : 0;
+}
+
+// A: [M, K] bf16, W: [N, K] bf16, out: [splits, M, N] with splits = tl_gemm_tcgen05_splits(N, K);
+// float32 when out_is_f32, else bfloat16 (then splits must be 1).  status: one int the kernel sets
+// to a non-zero code if a wait ran out (it then leaves its output unwritten).
+extern "C" int tl_gemm_tcgen05(const void* A, const void* W, void* out, int out_is_f32, int M, int N, int K,
+                               int splits, int* status, void* stream) {
+    if (M <= 0 || N <= 0) return TL_OK;
+    if (!tl_gemm_tcgen05_supports(M, N, K)) return TL_BAD_SIZE;
+    if (!aligned16(A) || !aligned16(W) || !aligned16(out) || status == nullptr) return TL_BAD_ALIGN;
+    if (splits != tl_gemm_tcgen05_splits(N, K)) return TL_BAD_SIZE;
+    if (!out_is_f32 && splits != 1) return TL_BAD_SIZE;
+    const int slabs = (N + BP - 1) / BP;
+    const int k_blocks = (K + BK - 1) / BK;
+    const int bq = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    CUtensorMap mw, ma;
+    int rc = make_map(&mw, W, N, K, BP);
+    if (rc != TL_OK) return rc;
+    rc = make_map(&ma, A, M, K, bq);
+    if (rc != TL_OK) return rc;
+    GemmParams p;
+    p.out = out; p.status = status; p.M = M; p.N = N; p.K = K;
+    p.k_blocks_per_split = (k_blocks + splits - 1) / splits;
+    p.out_is_f32 = out_is_f32;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (bq == 16) return launch<16, 6>(mw, ma, p, slabs, splits, s);
+    if (bq == 32) return launch<32, 5>(mw, ma, p, slabs, splits, s);
+    return launch<64, 4>(mw, ma, p, slabs, splits, s);
+}

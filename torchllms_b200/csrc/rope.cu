@@ -9,21 +9,26 @@
 // Pages are laid out [page, kv_head, slot_in_page, head_dim]; slot_mapping[t] = page * page_size + slot.
 #include "common.cuh"
 
-template <typename T>
-__global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const int* __restrict__ positions,
+// qkv holds `splits` planes `plane` elements apart (partial sums of a split-K product), summed first
+template <typename TI, typename T>
+__global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int splits, long long plane,
+                                     const int* __restrict__ positions,
                                      const float* __restrict__ table, const int* __restrict__ slot_mapping,
                                      T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                      int n_heads, int n_kv_heads, int head_dim, int page_size,
                                      int table_rows, int interleaved) {
     const int t = blockIdx.x;
     const int half = head_dim >> 1;
+    const int heads_per_cta = (n_heads + 2 * n_kv_heads + gridDim.y - 1) / gridDim.y;
+    const int head_lo = blockIdx.y * heads_per_cta;
+    const int head_hi = min(n_heads + 2 * n_kv_heads, head_lo + heads_per_cta);
     int pos = positions[t];
     pos = pos < 0 ? 0 : (pos >= table_rows ? table_rows - 1 : pos);  // the host keeps positions inside the table
     const float* cs = table + (size_t)pos * head_dim;                 // [half][2]
     const int row = (n_heads + 2 * n_kv_heads) * head_dim;
-    const T* src = qkv + (size_t)t * row;
+    const TI* src = qkv + (size_t)t * row;
     const int n_rot_pairs = (n_heads + n_kv_heads) * half;
-    const int n_pairs = (n_heads + 2 * n_kv_heads) * half;
+    const int n_pairs = head_hi * half;
     int page = 0, slot = 0;
     const bool write = k_pages != nullptr;
     if (write) {
@@ -31,13 +36,17 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const int* __res
         page = sm / page_size;
         slot = sm - page * page_size;
     }
-    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    for (int p = head_lo * half + threadIdx.x; p < n_pairs; p += blockDim.x) {
         const int head = p / half;       // 0 .. H + 2 KV - 1 over the packed row
         const int i = p - head * half;
         const int l0 = interleaved ? 2 * i : i;
         const int l1 = interleaved ? 2 * i + 1 : i + half;
         float x0 = to_float(src[head * head_dim + l0]);
         float x1 = to_float(src[head * head_dim + l1]);
+        for (int sp = 1; sp < splits; ++sp) {
+            x0 += to_float(src[sp * plane + head * head_dim + l0]);
+            x1 += to_float(src[sp * plane + head * head_dim + l1]);
+        }
         if (p < n_rot_pairs) {
             const float c = cs[2 * i], s = cs[2 * i + 1];
             const float y0 = x0 * c - x1 * s;
@@ -61,28 +70,33 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const int* __res
 }
 
 // k_pages / v_pages may both be null: then only q is produced (a run that reads another run's cache).
-extern "C" int tl_rope_kv_write(const void* qkv, const int* positions, const float* table,
+// qkv: [splits, n_tokens, row] of in_dtype (splits > 1 only for float32 partial sums); q, pages: dtype.
+extern "C" int tl_rope_kv_write(const void* qkv, int in_dtype, int splits, const int* positions, const float* table,
                                 const int* slot_mapping, void* q_out, void* k_pages, void* v_pages,
                                 int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                 int page_size, int table_rows, int interleaved, void* stream) {
     if (n_tokens <= 0) return TL_OK;
-    if (head_dim <= 0 || (head_dim & 1) || n_heads <= 0 || n_kv_heads <= 0 || page_size <= 0 || table_rows <= 0)
+    if (head_dim <= 0 || (head_dim & 1) || n_heads <= 0 || n_kv_heads <= 0 || page_size <= 0 || table_rows <= 0 || splits < 1)
         return TL_BAD_SIZE;
     if ((k_pages == nullptr) != (v_pages == nullptr)) return TL_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    const int pairs = (n_heads + 2 * n_kv_heads) * (head_dim / 2);
+    const int heads = n_heads + 2 * n_kv_heads;
+    // few tokens (decoding): spread a token's heads over several CTAs
+    int per_cta = n_tokens >= 256 ? heads : (4 * 128 + head_dim / 2 - 1) / (head_dim / 2);
+    if (per_cta > heads) per_cta = heads;
+    const int chunks = (heads + per_cta - 1) / per_cta;
+    const int pairs = per_cta * (head_dim / 2);
     const int threads = pairs >= 1024 ? 256 : 128;
-    if (dtype == TL_F32)
-        rope_kv_write_kernel<float><<<n_tokens, threads, 0, s>>>(
-            (const float*)qkv, positions, table, slot_mapping, (float*)q_out, (float*)k_pages, (float*)v_pages,
-            n_heads, n_kv_heads, head_dim, page_size, table_rows, interleaved);
-    else if (dtype == TL_BF16)
-        rope_kv_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(
-            (const __nv_bfloat16*)qkv, positions, table, slot_mapping, (__nv_bfloat16*)q_out,
-            (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages,
-            n_heads, n_kv_heads, head_dim, page_size, table_rows, interleaved);
-    else
-        return TL_BAD_DTYPE;
+    const long long plane = (long long)n_tokens * (n_heads + 2 * n_kv_heads) * head_dim;
+#define TL_ROPE_LAUNCH(TI, T)                                                                                   \
+    rope_kv_write_kernel<TI, T><<<dim3(n_tokens, chunks), threads, 0, s>>>(                                                   \
+        (const TI*)qkv, splits, plane, positions, table, slot_mapping, (T*)q_out, (T*)k_pages, (T*)v_pages,     \
+        n_heads, n_kv_heads, head_dim, page_size, table_rows, interleaved)
+    if (in_dtype == TL_F32 && dtype == TL_F32) TL_ROPE_LAUNCH(float, float);
+    else if (in_dtype == TL_BF16 && dtype == TL_BF16) TL_ROPE_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (in_dtype == TL_F32 && dtype == TL_BF16) TL_ROPE_LAUNCH(float, __nv_bfloat16);
+    else return TL_BAD_DTYPE;
+#undef TL_ROPE_LAUNCH
     TL_LAUNCH_CHECK();
     return TL_OK;
 }

@@ -69,7 +69,11 @@ class Replayer:
                 self.engine.release(handle)
         if logits is None:
             return None
-        return logits.to(torch.float32).cpu().numpy().astype("<f4", copy=False)
+        host = logits.to(torch.float32).cpu().numpy().astype("<f4", copy=False)
+        check = getattr(self.engine.model.ops, "check_status", None)
+        if check is not None:
+            check()          # the copy synchronised: a kernel that gave up a wait has said so by now
+        return host
 
 
 def main(argv=None) -> int:

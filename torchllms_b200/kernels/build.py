@@ -33,7 +33,7 @@ NVCC_FLAGS = [
 # libraries that need more than the CUDA runtime
 EXTRA_LINK: Dict[str, List[str]] = {}
 
-ALL_LIBRARIES = ("elementwise", "rope", "attention", "attention_mma", "gemm_simt", "sampling")
+ALL_LIBRARIES = ("elementwise", "rope", "attention", "attention_mma", "gemm_simt", "gemm_tcgen05", "sampling")
 
 
 class KernelBuildError(RuntimeError):
@@ -143,6 +143,12 @@ def compile_library(name: str) -> Path:
             pass
         raise KernelBuildError(f"nvcc failed on {src.name} (exit {proc.returncode}):\n{output}")
     os.replace(tmp, out)
+    for stale in out_dir.glob(f"{name}.*.so"):        # libraries of earlier versions of this source
+        if stale != out:
+            try:
+                stale.unlink()
+            except OSError:
+                pass
     _say(f"built {out.name} in {time.time() - t0:.1f} s")
     return out
 

@@ -90,6 +90,9 @@ class NativeOps:
         self.launches = 0          # kernels of this library launched so far (a bench counts with it)
         self._workspace: Dict[Tuple[int, str], torch.Tensor] = {}
         self._retired: list = []
+        self.use_tcgen05 = True
+        # error word of kernels with bounded waits: pinned host memory the device writes to directly
+        self._status = torch.zeros(4, dtype=torch.int32).pin_memory()
         self._mm_out_dtype: Optional[bool] = None
         self._profile = None
 
@@ -102,7 +105,7 @@ class NativeOps:
         """Compile, side by side, what a model of this dtype will call."""
         names = ["elementwise", "rope", "attention", "gemm_simt"]
         if dtype == torch.bfloat16:
-            names.append("attention_mma")
+            names += ["attention_mma", "gemm_tcgen05"]
         if sampling:
             names.append("sampling")
         build_libraries(names)
@@ -157,38 +160,59 @@ class NativeOps:
         _need(out_dtype in _DT, f"norm output dtype {out_dtype} unsupported")
         dim = h.shape[1]
         _need(dim * 4 <= 200 * 1024, f"rmsnorm keeps a row in shared memory: width {dim} exceeds 51200")
+        splits, plane = 1, 0
         if delta is not None:
             _cuda_contig(delta, "delta")
-            _need(delta.shape == h.shape and delta.dtype in _DT, "delta must have the stream's shape")
+            _need(delta.dtype in _DT, "delta must be float32 or bfloat16")
+            if delta.dim() == 3:          # partial sums of a split-K product, added up by the kernel
+                _need(delta.shape[1:] == h.shape and delta.dtype == torch.float32,
+                      "partial sums must be float32 [splits, tokens, width]")
+                splits, plane = delta.shape[0], delta.stride(0)
+            else:
+                _need(delta.shape == h.shape, "delta must have the stream's shape")
         if rows is not None:
             _cuda_contig(rows, "rows", torch.int32)
         n_out = h.shape[0] if rows is None else rows.numel()
         out = torch.empty((n_out, dim), dtype=out_dtype, device=h.device)
         write_back = 1 if (delta is not None and rows is None) else 0
         rc = self._lib("elementwise").tl_rmsnorm(
-            _ptr(h), _ptr(delta), _DT[delta.dtype] if delta is not None else 0, _ptr(weight), _ptr(out),
-            _DT[out_dtype], _ptr(rows), n_out, dim, ctypes.c_float(eps), write_back, _stream())
+            _ptr(h), _ptr(delta), _DT[delta.dtype] if delta is not None else 0, splits, ctypes.c_longlong(plane),
+            _ptr(weight), _ptr(out), _DT[out_dtype], _ptr(rows), n_out, dim, ctypes.c_float(eps), write_back, _stream())
         _check(rc, "rmsnorm")
         self.launches += 1
         return out
 
     @_timed
-    def swiglu(self, gate_up: torch.Tensor) -> torch.Tensor:
+    def swiglu(self, gate_up: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``gate_up`` is ``[tokens, 2 * hidden]``, or float32 partial sums ``[splits, tokens, 2 * hidden]``
+        (then ``out_dtype`` says what to produce)."""
         _cuda_contig(gate_up, "gate_up")
-        _need(gate_up.dim() == 2 and gate_up.shape[1] % 2 == 0 and gate_up.dtype in _DT,
+        _need(gate_up.dim() in (2, 3) and gate_up.shape[-1] % 2 == 0 and gate_up.dtype in _DT,
               "swiglu input must be [tokens, 2 * hidden] in float32/bfloat16")
-        n, hidden = gate_up.shape[0], gate_up.shape[1] // 2
-        out = torch.empty((n, hidden), dtype=gate_up.dtype, device=gate_up.device)
-        rc = self._lib("elementwise").tl_swiglu(_ptr(gate_up), _ptr(out), _DT[gate_up.dtype], n, hidden, _stream())
+        splits = gate_up.shape[0] if gate_up.dim() == 3 else 1
+        _need(splits == 1 or gate_up.dtype == torch.float32, "partial sums must be float32")
+        out_dtype = out_dtype or gate_up.dtype
+        _need(out_dtype in _DT and (out_dtype == gate_up.dtype or gate_up.dtype == torch.float32),
+              "swiglu cannot widen bfloat16 input")
+        n, hidden = gate_up.shape[-2], gate_up.shape[-1] // 2
+        out = torch.empty((n, hidden), dtype=out_dtype, device=gate_up.device)
+        rc = self._lib("elementwise").tl_swiglu(_ptr(gate_up), _DT[gate_up.dtype], splits, _ptr(out), _DT[out_dtype],
+                                               n, hidden, _stream())
         _check(rc, "swiglu")
         self.launches += 1
         return out
 
     # ------------------------------------------------------------------ linear
     @_timed
-    def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        """``x [M, K] @ w[N, K]^T``.  float32 runs on the CUDA cores (true 32-bit);
-        bfloat16 uses the library product, as the reference's ``nn.Linear`` does."""
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+               partials_ok: bool = False) -> torch.Tensor:
+        """``x [M, K] @ w[N, K]^T``.  float32 runs on the CUDA cores (true 32-bit).  bfloat16 with
+        at most 64 rows (decode steps) runs on the tcgen05 kernel that streams the weight once;
+        more rows use the library product, as the reference's ``nn.Linear`` does.
+
+        With ``partials_ok`` the result may be float32 partial sums ``[splits, M, N]`` of a
+        split-K product, for callers that hand it to a kernel which adds them up (residual +
+        norm, rope, swiglu)."""
         _cuda_contig(x, "linear input")
         _cuda_contig(w, "linear weight")
         _need(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], "linear: inner sizes differ")
@@ -199,6 +223,11 @@ class NativeOps:
         if x.dtype == torch.float32:
             _need(out_dtype == torch.float32, "a float32 product has float32 output")
             return self.gemm_simt(x, w, torch.float32)
+        if self.use_tcgen05 and M <= 64 and K % 8 == 0 and K >= 8 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+            parts = self.gemm_tcgen05(x, w, out_dtype)
+            if parts.dim() == 2 or partials_ok:
+                return parts
+            return parts.sum(0).to(out_dtype)
         if out_dtype == torch.bfloat16:
             return torch.mm(x, w.t())
         _need(out_dtype == torch.float32, f"linear: output dtype {out_dtype} unsupported")
@@ -211,6 +240,34 @@ class NativeOps:
         if self._mm_out_dtype:
             return torch.mm(x, w.t(), out_dtype=torch.float32)
         return self.gemm_simt(x, w, torch.float32)
+
+    def gemm_tcgen05(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """At most 64 rows of bfloat16 against a bfloat16 weight on the tcgen05 kernel.  Returns
+        ``[M, N]`` in ``out_dtype`` when the weight's shape needs no K split, else float32 partial
+        sums ``[splits, M, N]``."""
+        _cuda_contig(x, "gemm input", torch.bfloat16)
+        _cuda_contig(w, "gemm weight", torch.bfloat16)
+        M, K = x.shape
+        N = w.shape[0]
+        _need(x.shape[1] == w.shape[1], "gemm_tcgen05: inner sizes differ")
+        _need(1 <= M <= 64 and K % 8 == 0 and K >= 8, "gemm_tcgen05 takes 1..64 rows and K a multiple of 8")
+        _need(out_dtype in _DT, f"gemm_tcgen05: output dtype {out_dtype} unsupported")
+        lib = self._lib("gemm_tcgen05")
+        splits = lib.tl_gemm_tcgen05_splits(N, K)
+        f32 = out_dtype == torch.float32 or splits > 1
+        out = torch.empty((splits, M, N), dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
+        rc = lib.tl_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(out), 1 if f32 else 0, M, N, K, splits,
+                                 ctypes.c_void_p(self._status.data_ptr()), _stream())
+        _check(rc, "gemm_tcgen05")
+        self.launches += 1
+        return out[0] if splits == 1 else out
+
+    def check_status(self) -> None:
+        """Raise if a kernel reported that one of its bounded waits ran out (call after a sync)."""
+        code = int(self._status[0])
+        if code != 0:
+            self._status[0] = 0
+            raise KernelError(f"a kernel gave up waiting (code {code}); its output is not valid")
 
     def gemm_simt(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         _cuda_contig(x, "gemm input")
@@ -230,27 +287,35 @@ class NativeOps:
     def rope_kv_write(self, qkv: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, *,
                       n_heads: int, n_kv_heads: int, head_dim: int, interleaved: bool,
                       k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
-                      slot_mapping: Optional[torch.Tensor], page_size: int) -> torch.Tensor:
+                      slot_mapping: Optional[torch.Tensor], page_size: int,
+                      out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``qkv`` is ``[tokens, row]``, or float32 partial sums ``[splits, tokens, row]`` (then
+        ``out_dtype`` is the dtype of q and of the pages)."""
         _cuda_contig(qkv, "qkv")
         _cuda_contig(positions, "positions", torch.int32)
         _cuda_contig(table, "rotary table", torch.float32)
-        T = qkv.shape[0]
-        _need(qkv.dim() == 2 and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim and qkv.dtype in _DT,
+        splits = qkv.shape[0] if qkv.dim() == 3 else 1
+        T = qkv.shape[-2]
+        out_dtype = out_dtype or qkv.dtype
+        _need(qkv.dim() in (2, 3) and qkv.shape[-1] == (n_heads + 2 * n_kv_heads) * head_dim and qkv.dtype in _DT,
               "qkv must be [tokens, (n_heads + 2 n_kv_heads) * head_dim]")
+        _need(splits == 1 or qkv.dtype == torch.float32, "partial sums must be float32")
+        _need(out_dtype in _DT and (out_dtype == qkv.dtype or qkv.dtype == torch.float32), "rope cannot widen bfloat16 input")
         _need(table.dim() == 3 and table.shape[1] == head_dim // 2 and table.shape[2] == 2,
               "rotary table must be [positions, head_dim / 2, 2]")
         _need(positions.numel() == T, "one position per token")
         if k_pages is not None:
-            _cuda_contig(k_pages, "k_pages", qkv.dtype)
-            _cuda_contig(v_pages, "v_pages", qkv.dtype)
+            _cuda_contig(k_pages, "k_pages", out_dtype)
+            _cuda_contig(v_pages, "v_pages", out_dtype)
             _cuda_contig(slot_mapping, "slot_mapping", torch.int32)
             _need(k_pages.shape[1:] == (n_kv_heads, page_size, head_dim) and v_pages.shape == k_pages.shape,
                   "pages must be [pages, n_kv_heads, page_size, head_dim]")
             _need(slot_mapping.numel() == T, "one cache slot per token")
-        q = torch.empty((T, n_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+        q = torch.empty((T, n_heads, head_dim), dtype=out_dtype, device=qkv.device)
         rc = self._lib("rope").tl_rope_kv_write(
-            _ptr(qkv), _ptr(positions), _ptr(table), _ptr(slot_mapping if k_pages is not None else None),
-            _ptr(q), _ptr(k_pages), _ptr(v_pages), _DT[qkv.dtype], T, n_heads, n_kv_heads, head_dim,
+            _ptr(qkv), _DT[qkv.dtype], splits, _ptr(positions), _ptr(table),
+            _ptr(slot_mapping if k_pages is not None else None),
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _DT[out_dtype], T, n_heads, n_kv_heads, head_dim,
             page_size, table.shape[0], 1 if interleaved else 0, _stream())
         _check(rc, "rope_kv_write")
         self.launches += 1

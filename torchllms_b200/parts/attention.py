@@ -58,10 +58,11 @@ class PagedAttention(Mixer):
 
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         ops = self.env.ops
-        qkv = ops.linear(x, self.wqkv)
+        qkv = ops.linear(x, self.wqkv, partials_ok=True)   # rope adds up split-K partial sums
         q = self.position.encode_and_store(qkv, ctx, cache, self.n_heads, self.n_kv_heads, self.head_dim)
         o = ops.paged_attention(
             q, cache.k_pages, cache.v_pages, cache.block_table, ctx.q_start, ctx.kv_len,
             n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, max_kv_len=ctx.max_kv_len,
             scale=self.scale, window=self.window, page_size=cache.page_size)
-        return ops.linear(o.view(o.shape[0], self.n_heads * self.head_dim), self.wo)
+        # the caller's norm adds up split-K partial sums together with the residual
+        return ops.linear(o.view(o.shape[0], self.n_heads * self.head_dim), self.wo, partials_ok=True)

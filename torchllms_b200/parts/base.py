@@ -163,7 +163,9 @@ class Residual:
     """The residual stream ``h`` (float32, ``[T, dim]``) and a delta not yet added.
 
     Keeping the last delta pending lets the next norm kernel do ``h += delta``
-    and the normalisation in one pass over the row.
+    and the normalisation in one pass over the row.  The delta is ``[T, dim]`` in
+    the activation dtype, or float32 partial sums ``[splits, T, dim]`` of a
+    split-K product, which the norm kernel adds up as well.
     """
 
     __slots__ = ("h", "delta")

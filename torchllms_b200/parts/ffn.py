@@ -38,5 +38,5 @@ class SwiGLU(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         ops = self.env.ops
-        gate_up = ops.linear(x, self.w13)            # [T, 2 * hidden]: gate columns, then up columns
-        return ops.linear(ops.swiglu(gate_up), self.w2)
+        gate_up = ops.linear(x, self.w13, partials_ok=True)   # [T, 2 * hidden]: gate columns, then up columns
+        return ops.linear(ops.swiglu(gate_up, out_dtype=self.env.dtype), self.w2, partials_ok=True)

@@ -80,4 +80,4 @@ class RotaryEncoding(PositionEncoding):
             interleaved=(self.pairing == "interleaved"),
             k_pages=cache.k_pages if cache.writes else None,
             v_pages=cache.v_pages if cache.writes else None,
-            slot_mapping=cache.slot_mapping, page_size=cache.page_size)
+            slot_mapping=cache.slot_mapping, page_size=cache.page_size, out_dtype=self.env.dtype)

@@ -54,7 +54,7 @@ class Sampler:
         n = logits.shape[0]
         assert n == len(params) == len(requests) == len(token_indices)
         if all(not p.temperature > 0 for p in params):
-            return self.ops.sample(logits).tolist()
+            return self._checked(self.ops.sample(logits).tolist())
         packed = np.zeros((n, 4), dtype=np.int32)  # temperature bits | top_k | key low | key high
         packed[:, 0] = np.asarray([p.temperature for p in params], dtype=np.float32).view(np.int32)
         packed[:, 1] = [int(p.top_k or 0) for p in params]
@@ -64,4 +64,11 @@ class Sampler:
         temperature = dev[:, 0].contiguous().view(torch.float32)
         top_k = dev[:, 1].contiguous()
         row_keys = dev[:, 2:4].contiguous().view(torch.int64).reshape(n)
-        return self.ops.sample(logits, temperature, top_k, row_keys).tolist()
+        return self._checked(self.ops.sample(logits, temperature, top_k, row_keys).tolist())
+
+    def _checked(self, tokens: List[int]) -> List[int]:
+        # the read-back above synchronised the stream: a kernel that gave up a wait has said so by now
+        check = getattr(self.ops, "check_status", None)
+        if check is not None:
+            check()
+        return tokens
