@@ -229,14 +229,24 @@ ATTN_CASES = [
     ([90, 20], [90, 1], 16, 1, 64, 16, None),             # group of 16
     ([700, 650], [1, 1], 4, 2, 32, 16, 100),              # decoding behind a window
     ([2100], [2100], 8, 8, 128, 16, None),                # a long prompt, many key tiles
+    ([333, 64, 1, 65, 2000], [1, 1, 1, 1, 1], 8, 2, 128, 4, None),    # decoding, pages of 4
+    ([333, 64, 1, 65, 2000], [1, 1, 1, 1, 1], 6, 2, 64, 8, None),     # decoding, group of 3, pages of 8
+    ([900, 130], [2, 1], 16, 2, 64, 32, 77),              # two tokens of a group of 8 behind a window, pages of 32
+    ([300, 5], [1, 1], 4, 4, 128, 128, None),             # pages larger than a tile
+    ([1500, 1499, 3], [1, 1, 1], 32, 8, 128, 16, 512),    # the 8B layout decoding behind a window
 ]
 
 
-IMPLS = [(torch.float32, "general"), (torch.bfloat16, "general"), (torch.bfloat16, "mma")]
+IMPLS = [(torch.float32, "general"), (torch.bfloat16, "general"), (torch.bfloat16, "mma"), (torch.bfloat16, "decode")]
 
 
 def mma_takes(hd):
     return hd in (16, 32, 64, 128)
+
+
+def decode_takes(q_lens, H, KV, hd, P):
+    group = H // KV
+    return hd in (64, 128) and P & (P - 1) == 0 and max(q_lens) <= 16 // min(group, 16)
 
 
 @pytest.mark.parametrize("dtype,impl", IMPLS)
@@ -245,6 +255,8 @@ def test_paged_attention_matches_twin(ops, dtype, impl, case):
     seq_lens, q_lens, H, KV, hd, P, window = case
     if impl == "mma" and not mma_takes(hd):
         pytest.skip("the tensor-core kernel does not take this head size")
+    if impl == "decode" and not decode_takes(q_lens, H, KV, hd, P):
+        pytest.skip("the decode kernel does not take this step")
     a = build_paged(seq_lens, q_lens, H, KV, hd, P, dtype, seed=len(seq_lens) * 100 + hd)
     scale = hd ** -0.5
     got = ops.paged_attention(**a, scale=scale, window=window, impl=impl)
@@ -272,7 +284,7 @@ def test_decode_attention_split_over_keys(ops, dtype, impl, B, L):
 def test_attention_finds_one_far_key_among_hundreds(ops, dtype, impl, key_pos):
     """Random scores hide a dropped key; here one key takes nearly all the weight, so the output
     must equal that key's value."""
-    L, H, KV, hd, P = 700, 4, 2, 32, 16
+    L, H, KV, hd, P = 700, 4, 2, (64 if impl == "decode" else 32), 16
     a = build_paged([L, 40], [1, 1], H, KV, hd, P, dtype, seed=key_pos, peak=(0, key_pos, 10.0))
     got = ops.paged_attention(**a, scale=hd ** -0.5, window=None, impl=impl).float()
     page, slot = a["block_table"][0, key_pos // P].item(), key_pos % P
@@ -288,7 +300,7 @@ def test_attention_finds_one_far_key_among_hundreds(ops, dtype, impl, key_pos):
 def test_window_edge_is_exact(ops, dtype, impl):
     """The key just outside the window gets a huge score: if the edge were off by one it would
     take over the output."""
-    L, H, KV, hd, P, w = 100, 2, 1, 16, 8, 24
+    L, H, KV, hd, P, w = 100, 2, 1, (64 if impl == "decode" else 16), 8, 24
     for edge_inside in (False, True):
         key_pos = (L - 1) - w + (1 if edge_inside else 0)   # last query sits at L - 1
         a = build_paged([L], [1], H, KV, hd, P, dtype, seed=3, peak=(0, key_pos, 12.0))

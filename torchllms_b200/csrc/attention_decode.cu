@@ -1,0 +1,606 @@
+// Decode attention over paged bfloat16 keys and values with TMA-fed tiles (head_dim 64 or 128).
+//
+// For steps where every request brings so few tokens that its rows (token x query heads of one kv
+// group) fit one 16-row tensor-core tile: single decoded tokens above all.  Same contract and
+// the same arithmetic as the kernels in attention_mma.cu (float32 scores, running maximum and
+// sum, accumulators; probabilities multiplied as value + remainder), but the tiles are moved by
+// the TMA unit instead of by every thread: the decode step is bound by streaming K and V once
+// from HBM, and issuing 16-byte copies from all threads cost more instructions than the math.
+//
+// A CTA serves one (request, kv head, key split).  Warp 4 is the producer: for every 64-key tile it
+// looks up the pages, and issues cp.async.bulk.tensor copies (no multicast) of [page rows x 64
+// elements] boxes into 128-byte-swizzled shared memory, completing on an mbarrier per stage.
+// Warps 0-3 share the 16 rows and each takes 16 keys of every tile; they hand a stage back through a
+// second mbarrier.  No CTA-wide barrier is used until the four partial results are merged.  Key
+// splits over CTAs write float32 partials that merge_partials_kernel combines.
+// Every mbarrier wait is bounded in time; on a time-out the CTA records a code in the status
+// word, writes nothing and returns.
+#include "common.cuh"
+#include <cuda.h>
+#include <limits.h>
+#include <math.h>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace {
+
+constexpr int BN = 64;                  // keys per tile
+constexpr int NCW = 4;                  // consumer warps
+constexpr int NTHREADS = (NCW + 1) * 32;
+constexpr int MIN_SPLIT = 128;
+constexpr int MERGE_MAX_SPLITS = 64;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+constexpr unsigned long long WAIT_NS = 2000ull * 1000ull * 1000ull;
+enum : int { ERR_PRODUCER_WAIT = 211, ERR_CONSUMER_WAIT = 212 };
+
+struct DecodeParams {
+    const __nv_bfloat16* q;
+    __nv_bfloat16* out;
+    const int* block_table;
+    const int* q_start;
+    const int* kv_len;
+    float* part_o;   // [T * H, n_splits, head_dim]
+    float* part_ml;  // [T * H, n_splits, 2]
+    int* status;
+    int table_stride;
+    int n_heads, n_kv_heads, page_size, page_shift, box_rows;
+    int total_rows;             // rows of the page tensor: a copy that starts there reads only the zero fill
+    int group, ng, n_gchunks, tpw;
+    int window;
+    int n_splits;
+    float scale_log2;
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* failed) {
+    if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    for (unsigned i = 1;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 0u) {
+            unsigned long long t1;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+            if (*failed || t1 - t0 > WAIT_NS) return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float ex2(float x) {     // 2^x, one instruction; 2^-inf = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+// byte offset of (row, 16-byte chunk c of a 128-byte row) inside a 128-byte-swizzled [rows x 128 B] tile
+__device__ __forceinline__ unsigned swz(int row, int c) { return (unsigned)(row * 128 + ((c ^ (row & 7)) << 4)); }
+
+template <int HD, int STAGES>
+__global__ void __launch_bounds__(NTHREADS, 3) attention_decode_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                    const __grid_constant__ CUtensorMap map_v,
+                                                                    const DecodeParams p) {
+    constexpr int HALVES = HD / 64;                     // 64-element (128-byte) column blocks of a row
+    constexpr unsigned HALF_BYTES = BN * 128;           // one [64 keys x 128 B] block
+    constexpr unsigned KV_BYTES = HALVES * HALF_BYTES;  // K (or V) of a tile
+    constexpr unsigned STAGE_BYTES = 2 * KV_BYTES;
+    constexpr int QPITCH = HD + 8;
+    constexpr int KSTEPS = HD / 16;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(tiles + STAGES * STAGE_BYTES);   // [16][QPITCH]
+    __shared__ __align__(8) unsigned long long full_bar[STAGES];
+    __shared__ __align__(8) unsigned long long empty_bar[STAGES];
+    __shared__ int failed_flag;
+
+    const int b = blockIdx.z;
+    const int qs = p.q_start[b];
+    const int ql = p.q_start[b + 1] - qs;
+    const int kl = p.kv_len[b];
+    const int tile = blockIdx.x / p.n_splits;
+    const int split = blockIdx.x - tile * p.n_splits;
+    const int tok0 = tile * p.tpw;
+    if (tok0 >= ql) return;
+    const int kvh = blockIdx.y / p.n_gchunks;
+    const int g0 = (blockIdx.y - kvh * p.n_gchunks) * p.ng;
+    const int ng = min(p.ng, p.group - g0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    volatile int* failed = &failed_flag;
+
+    if (tid == 0) {
+        failed_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], NCW);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // queries (zero rows where the tile has none)
+    for (int c = tid; c < 16 * (HD / 8); c += NTHREADS) {
+        const int rr = c / (HD / 8), part = c - rr * (HD / 8);
+        const int tok = tok0 + rr / ng;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (rr < p.tpw * ng && tok < ql) {
+            const int head = kvh * p.group + g0 + rr % ng;
+            v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + tok) * p.n_heads + head) * HD + part * 8);
+        }
+        *reinterpret_cast<uint4*>(Qs + rr * QPITCH + part * 8) = v;
+    }
+    __syncthreads();
+
+    // ---- which keys this CTA walks: its share of the request's visible keys, in whole tiles
+    const int cta_tok_hi = min(ql, tok0 + p.tpw);
+    const int qpos_base = kl - ql;
+    int k_lo = p.window > 0 ? max(0, qpos_base + tok0 - p.window + 1) : 0;
+    int k_hi = qpos_base + cta_tok_hi;
+    if (p.n_splits > 1) {
+        const int len = max(k_hi - k_lo, 0);
+        const int chunk = ((len + p.n_splits - 1) / p.n_splits + BN - 1) / BN * BN;
+        const int lo = k_lo + split * chunk;
+        k_hi = min(k_hi, lo + chunk);
+        k_lo = lo;
+    }
+    const int k_start = k_lo & ~(p.box_rows - 1);      // copies start on a box (page) boundary; keys below k_lo are masked
+    const int n_tiles = k_hi > k_start ? (k_hi - k_start + BN - 1) / BN : 0;
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    const int g = lane >> 2, t = lane & 3;
+
+    if (warp == NCW) {
+        // ---- producer
+        if (lane == 0) {
+            const int* table = p.block_table + (size_t)b * p.table_stride;
+            for (int it = 0; it < n_tiles; ++it) {
+                const int s = it % STAGES;
+                if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1, failed)) {
+                    failed_flag = 1;
+                    atomicExch(p.status, ERR_PRODUCER_WAIT);
+                    break;
+                }
+                const int k0 = k_start + it * BN;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                unsigned char* kt = tiles + s * STAGE_BYTES;
+                for (int c = 0; c < BN / p.box_rows; ++c) {
+                    const int kpos = k0 + c * p.box_rows;
+                    // boxes past the last key start outside the tensor: the copy writes the zero fill, so
+                    // that what is multiplied by probability 0 there is finite
+                    int row = p.total_rows;
+                    if (kpos < k_hi) {
+                        const int page = table[kpos >> p.page_shift];
+                        row = (page * p.n_kv_heads + kvh) * p.page_size + (kpos & (p.page_size - 1));
+                    }
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h) {
+                        unsigned char* dst = kt + h * HALF_BYTES + c * p.box_rows * 128;
+                        tma_load_2d(dst, &map_k, &full_bar[s], h * 64, row);
+                        tma_load_2d(dst + KV_BYTES, &map_v, &full_bar[s], h * 64, row);
+                    }
+                }
+            }
+        }
+    } else {
+        // ---- consumers: the same 16 rows, 16 keys of every tile each
+        int qpos[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int rr = g + 8 * i;
+            const int tok = tok0 + rr / ng;
+            qpos[i] = (rr < p.tpw * ng && tok < ql) ? qpos_base + tok : -1;
+        }
+        const int warp_qmax = __reduce_max_sync(0xffffffffu, max(qpos[0], qpos[1]));
+        const int warp_qmin = __reduce_min_sync(0xffffffffu, min(qpos[0] < 0 ? INT_MAX : qpos[0], qpos[1] < 0 ? INT_MAX : qpos[1]));
+        unsigned qf[KSTEPS][4];
+        const int mi = lane >> 3;
+#pragma unroll
+        for (int kd = 0; kd < KSTEPS; ++kd) {
+            const int row = (lane & 7) + ((mi & 1) ? 8 : 0);
+            ldmatrix_x4(qf[kd], smem_u32(Qs + row * QPITCH + kd * 16 + ((mi & 2) ? 8 : 0)));
+        }
+        const int key_off = warp * 16;
+        // this lane's row and first chunk inside a tile, for the K fragments and for the V fragments
+        const int k_row = key_off + (lane & 7) + ((mi & 2) ? 8 : 0);
+        const int v_row = key_off + (lane & 7) + ((mi & 1) ? 8 : 0);
+        const unsigned k_lane_off = swz(k_row, mi & 1);
+        const unsigned v_lane_off = swz(v_row, (mi & 2) ? 1 : 0);
+        bool ok = true;
+        for (int it = 0; it < n_tiles; ++it) {
+            const int s = it % STAGES;
+            if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, failed)) {
+                ok = false;
+                break;
+            }
+            const int share_lo = k_start + it * BN + key_off;
+            if (share_lo <= warp_qmax && share_lo + 16 > k_lo) {
+                const unsigned kt = smem_u32(tiles + s * STAGE_BYTES);
+                // rows are 128 bytes and tiles 1024-byte aligned, so bits 4-6 of a row's address are the
+                // swizzled chunk: xor-ing a constant chunk number in is all it takes to move along K
+                const unsigned ka = kt + k_lane_off, va = kt + KV_BYTES + v_lane_off;
+                float sc[2][4];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+#pragma unroll
+                for (int kd = 0; kd < KSTEPS; ++kd) {
+                    unsigned kf[4];
+                    ldmatrix_x4(kf, (ka ^ (unsigned)(((kd * 2) & 7) << 4)) + (kd / 4) * HALF_BYTES);
+                    mma_bf16(sc[0], qf[kd], kf[0], kf[1]);
+                    mma_bf16(sc[1], qf[kd], kf[2], kf[3]);
+                }
+                float mx[2] = {-INFINITY, -INFINITY};
+                const bool all_visible = share_lo >= k_lo && share_lo + 16 <= k_hi && share_lo + 15 <= warp_qmin &&
+                                         (p.window <= 0 || share_lo > warp_qmax - p.window);
+                if (!all_visible) {
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int i = e >> 1;
+                            const int kpos = share_lo + nt * 8 + 2 * t + (e & 1);
+                            const bool vis = kpos >= k_lo && kpos < k_hi && kpos <= qpos[i] &&
+                                             (p.window <= 0 || kpos > qpos[i] - p.window);
+                            if (!vis) sc[nt][e] = -INFINITY;
+                        }
+                }
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], sc[nt][e]);
+                float alpha[2], m_safe[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+                    const float m_new = fmaxf(m[i], mx[i] * p.scale_log2);      // maxima live on the base-2 scale
+                    m_safe[i] = (m_new == -INFINITY) ? 0.f : m_new;               // no key seen yet: keep exponents finite
+                    alpha[i] = ex2(m[i] - m_safe[i]);
+                    m[i] = m_new;
+                    l[i] *= alpha[i];
+                }
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float pv = ex2(fmaf(sc[nt][e], p.scale_log2, -m_safe[e >> 1]));
+                        sc[nt][e] = pv;
+                        l[e >> 1] += pv;
+                    }
+                if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+                    for (int i = 0; i < HD / 8; ++i) {
+                        o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+                        o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+                    }
+                }
+                // probabilities as value + remainder in bfloat16: the product keeps 16 bits of them
+                unsigned ph[4], pl[4];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const float a = sc[r >> 1][(r & 1) * 2], c = sc[r >> 1][(r & 1) * 2 + 1];
+                    const __nv_bfloat162 hi = __floats2bfloat162_rn(a, c);
+                    const float2 back = __bfloat1622float2(hi);
+                    ph[r] = *reinterpret_cast<const unsigned*>(&hi);
+                    pl[r] = pack_bf16(a - back.x, c - back.y);
+                }
+#pragma unroll
+                for (int dp = 0; dp < HD / 16; ++dp) {
+                    unsigned vf[4];
+                    ldmatrix_x4_trans(vf, (va ^ (unsigned)(((dp * 2) & 7) << 4)) + (dp / 4) * HALF_BYTES);
+                    mma_bf16(o[2 * dp], ph, vf[0], vf[1]);
+                    mma_bf16(o[2 * dp + 1], ph, vf[2], vf[3]);
+                    mma_bf16(o[2 * dp], pl, vf[0], vf[1]);
+                    mma_bf16(o[2 * dp + 1], pl, vf[2], vf[3]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[s]);     // this warp is done with the stage
+        }
+        if (!__all_sync(0xffffffffu, ok) && lane == 0) {
+            failed_flag = 1;
+            atomicExch(p.status, ERR_CONSUMER_WAIT);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+            l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+        }
+    }
+
+    // ---- merge the four warps' partials through shared memory (the stages are done with)
+    __syncthreads();
+    if (failed_flag) return;
+    float* Om = reinterpret_cast<float*>(tiles);          // [NCW][16][HD]
+    float* Mm = Om + NCW * 16 * HD;                       // [NCW][16]
+    float* Lm = Mm + NCW * 16;                            // [NCW][16]
+    if (warp < NCW) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int rr = g + 8 * i;
+#pragma unroll
+            for (int nt = 0; nt < HD / 8; ++nt) {
+                Om[(warp * 16 + rr) * HD + nt * 8 + 2 * t] = o[nt][2 * i];
+                Om[(warp * 16 + rr) * HD + nt * 8 + 2 * t + 1] = o[nt][2 * i + 1];
+            }
+            if (t == 0) {
+                Mm[warp * 16 + rr] = m[i];
+                Lm[warp * 16 + rr] = l[i];
+            }
+        }
+    }
+    __syncthreads();
+    const int n_rows = min(p.tpw, ql - tok0) * ng;
+    for (int idx = tid; idx < n_rows * HD; idx += NTHREADS) {
+        const int rr = idx / HD, d = idx - rr * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NCW; ++w) M = fmaxf(M, Mm[w * 16 + rr]);
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int w = 0; w < NCW; ++w) {
+            const float mw = Mm[w * 16 + rr];
+            if (mw == -INFINITY) continue;
+            const float f = exp2f(mw - M);
+            num = fmaf(f, Om[(w * 16 + rr) * HD + d], num);
+            den = fmaf(f, Lm[w * 16 + rr], den);
+        }
+        const int tok = qs + tok0 + rr / ng;
+        const int head = kvh * p.group + g0 + rr % ng;
+        const size_t row = (size_t)tok * p.n_heads + head;
+        if (p.n_splits == 1) {
+            p.out[row * HD + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+        } else {
+            p.part_o[(row * p.n_splits + split) * HD + d] = num;
+            if (d == 0) {
+                p.part_ml[(row * p.n_splits + split) * 2] = (M == -INFINITY) ? -INFINITY : M * LN2;   // natural-log scale
+                p.part_ml[(row * p.n_splits + split) * 2 + 1] = den;
+            }
+        }
+    }
+}
+
+// out[row, d] = sum_i e^{m_i - M} o_i[d] / sum_i e^{m_i - M} l_i,  M = max_i m_i: the weights are
+// computed once per row (lanes over splits), then every thread sums its lanes over the splits in order
+__global__ void merge_partials_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                      __nv_bfloat16* __restrict__ out, int n_splits, int head_dim) {
+    __shared__ float wgt[MERGE_MAX_SPLITS];
+    __shared__ float red;
+    const size_t row = blockIdx.x;
+    const float* ml = part_ml + row * n_splits * 2;
+    if (threadIdx.x < 32) {
+        float M = -INFINITY;
+        for (int i = threadIdx.x; i < n_splits; i += 32) M = fmaxf(M, ml[2 * i]);
+        M = warp_max(M);
+        float den = 0.f;
+        for (int i = threadIdx.x; i < n_splits; i += 32) {
+            const float mi = ml[2 * i];
+            const float w = (mi == -INFINITY) ? 0.f : __expf(mi - M);
+            wgt[i] = w;
+            den = fmaf(w, ml[2 * i + 1], den);
+        }
+        den = warp_sum(den);
+        if (threadIdx.x == 0) red = den;
+    }
+    __syncthreads();
+    const float inv = red > 0.f ? 1.f / red : 0.f;
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float num = 0.f;
+        for (int i = 0; i < n_splits; ++i) num = fmaf(wgt[i], part_o[(row * n_splits + i) * head_dim + d], num);
+        out[row * head_dim + d] = __float2bfloat16_rn(num * inv);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// the page tensor as rows of head_dim elements; box = box_rows x 64 elements, 128-byte swizzle.
+// Maps are kept per (pointer, rows, head_dim, box): the page tensors live as long as the engine.
+int page_map(CUtensorMap* out, const void* base, long long rows, int head_dim, int box_rows) {
+    static std::map<std::tuple<const void*, long long, int, int>, CUtensorMap> cache;
+    static std::mutex lock;
+    std::lock_guard<std::mutex> guard(lock);
+    auto key = std::make_tuple(base, rows, head_dim, box_rows);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return TL_OK;
+    }
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr) return TL_BAD_SIZE;
+    cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUtensorMap m;
+    CUresult rc = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return TL_BAD_SIZE;
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = m;
+    *out = m;
+    return TL_OK;
+}
+
+template <int HD> constexpr int stages_for() { return HD == 128 ? 2 : 3; }
+template <int HD> constexpr size_t smem_for() {
+    return (size_t)stages_for<HD>() * 2 * (HD / 64) * BN * 128 + 16 * (HD + 8) * 2 + 1024;
+}
+
+struct Plan {
+    int ng, n_gchunks, tpw, n_q_tiles, n_splits;
+};
+
+bool takes(int n_heads, int n_kv_heads, int head_dim, int page_size, int max_q_len) {
+    if (head_dim != 64 && head_dim != 128) return false;
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return false;
+    if (page_size < 1 || (page_size & (page_size - 1)) != 0) return false;           // a power of two
+    const int group = n_heads / n_kv_heads;
+    const int ng = group < 16 ? group : 16;
+    return max_q_len >= 1 && max_q_len <= 16 / ng;
+}
+
+Plan make_plan(int n_seqs, int n_heads, int n_kv_heads, int head_dim, int max_q_len, int max_kv_len, int allow_split) {
+    Plan pl;
+    const int group = n_heads / n_kv_heads;
+    pl.ng = group < 16 ? group : 16;
+    pl.n_gchunks = (group + pl.ng - 1) / pl.ng;
+    pl.tpw = 16 / pl.ng;
+    pl.n_q_tiles = (max_q_len + pl.tpw - 1) / pl.tpw;
+    pl.n_splits = 1;
+    if (allow_split && max_kv_len >= 2 * MIN_SPLIT) {
+        // CTAs run in waves; with s splits a CTA does 1/s of the keys.  Pick the s that makes
+        // (waves / s), the time in units of one unsplit CTA, smallest, charging each split a
+        // little for its partial results and the merge.
+        const size_t per_cta = head_dim == 128 ? smem_for<128>() : smem_for<64>();
+        int per_sm = (int)((size_t)224 * 1024 / (per_cta + 1024));
+        if (per_sm > 6) per_sm = 6;
+        const long long slots = 148LL * per_sm;
+        const long long base = (long long)pl.n_q_tiles * n_kv_heads * pl.n_gchunks * n_seqs;
+        int most = max_kv_len / MIN_SPLIT;
+        if (most > MERGE_MAX_SPLITS) most = MERGE_MAX_SPLITS;
+        double best = 1e30;
+        for (int sp = 1; sp <= most; ++sp) {
+            const long long waves = (base * sp + slots - 1) / slots;
+            const double cost = (double)waves / sp + 0.01 * sp;
+            if (cost < best - 1e-9) {
+                best = cost;
+                pl.n_splits = sp;
+            }
+        }
+    }
+    return pl;
+}
+
+template <int HD>
+int launch(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParams& p, dim3 grid, cudaStream_t s) {
+    constexpr size_t smem = smem_for<HD>();
+    auto kern = attention_decode_kernel<HD, stages_for<HD>()>;
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        raised = true;
+    }
+    kern<<<grid, NTHREADS, smem, s>>>(mk, mv, p);
+    TL_LAUNCH_CHECK();
+    return TL_OK;
+}
+
+}  // namespace
+
+// 1 if this kernel takes the step: head_dim 64 or 128, a page size that is a power of two, and
+// every request's rows (tokens x heads of a kv group) within one 16-row tile.
+extern "C" int tl_attention_decode_supports(int n_heads, int n_kv_heads, int head_dim, int page_size, int max_q_len) {
+    return takes(n_heads, n_kv_heads, head_dim, page_size, max_q_len) ? 1 : 0;
+}
+
+extern "C" int tl_attention_decode_plan(int n_tokens, int n_seqs, int n_heads, int n_kv_heads, int head_dim,
+                                        int max_q_len, int max_kv_len, int allow_split,
+                                        int* n_splits, long long* workspace_floats) {
+    if (!takes(n_heads, n_kv_heads, head_dim, 16, max_q_len)) return TL_BAD_SIZE;
+    const Plan pl = make_plan(n_seqs, n_heads, n_kv_heads, head_dim, max_q_len, max_kv_len, allow_split);
+    *n_splits = pl.n_splits;
+    *workspace_floats = pl.n_splits > 1 ? (long long)n_tokens * n_heads * pl.n_splits * (head_dim + 2) : 0;
+    return TL_OK;
+}
+
+// Same arguments as tl_paged_attention_mma; n_pages is the first extent of the page tensors.
+extern "C" int tl_paged_attention_decode(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                         const int* block_table, int table_stride, const int* q_start,
+                                         const int* kv_len, float* workspace, int* status, int n_tokens, int n_seqs,
+                                         int n_heads, int n_kv_heads, int head_dim, int page_size, long long n_pages,
+                                         int max_q_len, int max_kv_len, int window, float scale, int allow_split,
+                                         void* stream) {
+    if (n_tokens <= 0 || n_seqs <= 0) return TL_OK;
+    if (!takes(n_heads, n_kv_heads, head_dim, page_size, max_q_len) || max_kv_len <= 0 || n_pages <= 0) return TL_BAD_SIZE;
+    if (n_pages * n_kv_heads * page_size >= (1LL << 31)) return TL_BAD_SIZE;
+    if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(out) || status == nullptr) return TL_BAD_ALIGN;
+    const Plan pl = make_plan(n_seqs, n_heads, n_kv_heads, head_dim, max_q_len, max_kv_len, allow_split);
+    if (pl.n_splits > 1 && workspace == nullptr) return TL_BAD_SIZE;
+    if (n_seqs > 65535 || (long long)n_kv_heads * pl.n_gchunks > 65535) return TL_BAD_SIZE;
+
+    DecodeParams p;
+    p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out;
+    p.block_table = block_table; p.q_start = q_start; p.kv_len = kv_len; p.table_stride = table_stride;
+    p.status = status;
+    p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page_size) ++p.page_shift;
+    p.box_rows = page_size < BN ? page_size : BN;
+    p.total_rows = (int)(n_pages * n_kv_heads * page_size);
+    p.group = n_heads / n_kv_heads; p.ng = pl.ng; p.n_gchunks = pl.n_gchunks; p.tpw = pl.tpw;
+    p.window = window > 0 ? window : 0;
+    p.n_splits = pl.n_splits;
+    p.scale_log2 = scale * LOG2E;
+    p.part_o = workspace;
+    p.part_ml = workspace ? workspace + (size_t)n_tokens * n_heads * pl.n_splits * head_dim : nullptr;
+
+    const long long rows = n_pages * n_kv_heads * page_size;
+    CUtensorMap mk, mv;
+    int rc = page_map(&mk, k_pages, rows, head_dim, p.box_rows);
+    if (rc != TL_OK) return rc;
+    rc = page_map(&mv, v_pages, rows, head_dim, p.box_rows);
+    if (rc != TL_OK) return rc;
+
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(pl.n_q_tiles * pl.n_splits, n_kv_heads * pl.n_gchunks, n_seqs);
+    rc = head_dim == 128 ? launch<128>(mk, mv, p, grid, s) : launch<64>(mk, mv, p, grid, s);
+    if (rc != TL_OK) return rc;
+    if (pl.n_splits > 1) {
+        merge_partials_kernel<<<dim3((unsigned)n_tokens * (unsigned)n_heads), dim3(head_dim >= 128 ? 128u : 64u), 0, s>>>(
+            p.part_o, p.part_ml, p.out, pl.n_splits, head_dim);
+        TL_LAUNCH_CHECK();
+    }
+    return TL_OK;
+}

@@ -70,6 +70,11 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float ex2(float x) {     // 2^x, one instruction; 2^-inf = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -222,22 +227,12 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
                     mma_bf16(s[2 * np + 1], qf[kd], kf[2], kf[3]);
                 }
             }
-            // ---- mask, streaming softmax (base 2)
+            // ---- mask, streaming softmax (base 2; the scale is folded into the exponent)
             float mx[2] = {-INFINITY, -INFINITY};
             const int share_lo = k0 + key_off, share_hi = share_lo + 16 * KG;   // this warp's keys of the tile
             const bool all_visible = share_hi <= k_hi && share_hi - 1 <= warp_qmin &&
                                      (p.window <= 0 || share_lo > warp_qmax - p.window);
-            if (all_visible) {       // every key counts for every row: no per-element tests
-#pragma unroll
-                for (int nt = 0; nt < 2 * KG; ++nt) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float v = s[nt][e] * p.scale_log2;
-                        s[nt][e] = v;
-                        mx[e >> 1] = fmaxf(mx[e >> 1], v);
-                    }
-                }
-            } else {
+            if (!all_visible) {      // else every key counts for every row: no per-element tests
 #pragma unroll
                 for (int nt = 0; nt < 2 * KG; ++nt) {
 #pragma unroll
@@ -245,19 +240,22 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
                         const int i = e >> 1;
                         const int kpos = share_lo + nt * 8 + 2 * t + (e & 1);
                         const bool ok = kpos <= qpos[i] && kpos < k_hi && (p.window <= 0 || kpos > qpos[i] - p.window);
-                        const float v = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
-                        s[nt][e] = v;
-                        mx[i] = fmaxf(mx[i], v);
+                        if (!ok) s[nt][e] = -INFINITY;
                     }
                 }
             }
-            float alpha[2];
+#pragma unroll
+            for (int nt = 0; nt < 2 * KG; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+            float alpha[2], m_safe[2];
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
                 mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-                const float m_new = fmaxf(m[i], mx[i]);
-                alpha[i] = (m_new == -INFINITY) ? 1.f : exp2f(m[i] - m_new);
+                const float m_new = fmaxf(m[i], mx[i] * p.scale_log2);       // maxima live on the base-2 scale
+                m_safe[i] = (m_new == -INFINITY) ? 0.f : m_new;                // no key seen yet: keep exponents finite
+                alpha[i] = ex2(m[i] - m_safe[i]);
                 m[i] = m_new;
                 l[i] *= alpha[i];
             }
@@ -265,16 +263,17 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
             for (int nt = 0; nt < 2 * KG; ++nt) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int i = e >> 1;
-                    const float pv = (m[i] == -INFINITY) ? 0.f : exp2f(s[nt][e] - m[i]);
+                    const float pv = ex2(fmaf(s[nt][e], p.scale_log2, -m_safe[e >> 1]));
                     s[nt][e] = pv;
-                    l[i] += pv;
+                    l[e >> 1] += pv;
                 }
             }
+            if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {   // the maximum moved for some row
 #pragma unroll
-            for (int i = 0; i < HD / 8; ++i) {
-                o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-                o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+                for (int i = 0; i < HD / 8; ++i) {
+                    o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+                    o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+                }
             }
             // ---- accumulate probabilities times values.  A probability is split into two bfloat16
             // numbers (value and remainder) and multiplied twice, so the product keeps 16 bits of

@@ -105,7 +105,7 @@ class NativeOps:
         """Compile, side by side, what a model of this dtype will call."""
         names = ["elementwise", "rope", "attention", "gemm_simt"]
         if dtype == torch.bfloat16:
-            names += ["attention_mma", "gemm_tcgen05"]
+            names += ["attention_mma", "attention_decode", "gemm_tcgen05"]
         if sampling:
             names.append("sampling")
         build_libraries(names)
@@ -341,7 +341,9 @@ class NativeOps:
                         window: Optional[int], page_size: int, allow_split: bool = True,
                         impl: str = "auto") -> torch.Tensor:
         """``impl``: ``"general"`` (CUDA cores, any supported size, both dtypes), ``"mma"`` (tensor
-        cores, bfloat16, head_dim 16/32/64/128) or ``"auto"`` (mma where it applies)."""
+        cores, bfloat16, head_dim 16/32/64/128), ``"decode"`` (tensor cores fed by TMA, bfloat16,
+        head_dim 64/128, steps whose requests bring one token or very few) or ``"auto"``
+        (the most specialised kernel that applies)."""
         _cuda_contig(q, "q")
         _cuda_contig(k_pages, "k_pages", q.dtype)
         _cuda_contig(v_pages, "v_pages", q.dtype)
@@ -357,14 +359,31 @@ class NativeOps:
         _need(block_table.shape[0] >= n_seqs and q_start.numel() >= n_seqs + 1 and kv_len.numel() >= n_seqs,
               "block_table, q_start and kv_len must cover every request of the step")
         _need(block_table.shape[1] * page_size >= max_kv_len, "block_table is too narrow for max_kv_len")
-        _need(impl in ("auto", "general", "mma"), f"unknown attention implementation {impl!r}")
+        _need(impl in ("auto", "general", "mma", "decode"), f"unknown attention implementation {impl!r}")
         mma_ok = q.dtype == torch.bfloat16 and head_dim in (16, 32, 64, 128)
         _need(impl != "mma" or mma_ok, "the tensor-core attention kernel takes bfloat16 and head_dim 16, 32, 64 or 128")
-        use_mma = mma_ok and impl != "general"
+        use_mma = mma_ok and impl in ("auto", "mma")
+        decode_ok = (q.dtype == torch.bfloat16 and impl in ("auto", "decode") and head_dim in (64, 128) and
+                     self._lib("attention_decode").tl_attention_decode_supports(n_heads, n_kv_heads, head_dim,
+                                                                                 page_size, max_q_len) == 1)
+        _need(impl != "decode" or decode_ok, "the decode attention kernel takes bfloat16, head_dim 64 or 128, a "
+              "power-of-two page size and requests whose rows fit one 16-row tile")
         n_splits = ctypes.c_int(0)
         floats = ctypes.c_longlong(0)
         out = torch.empty_like(q)
-        if use_mma:
+        if decode_ok:
+            lib = self._lib("attention_decode")
+            rc = lib.tl_attention_decode_plan(T, n_seqs, n_heads, n_kv_heads, head_dim, max_q_len, max_kv_len,
+                                              1 if allow_split else 0, ctypes.byref(n_splits), ctypes.byref(floats))
+            _check(rc, "attention_decode_plan")
+            ws = self._scratch(q.device, floats.value)
+            rc = lib.tl_paged_attention_decode(
+                _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
+                _ptr(q_start), _ptr(kv_len), _ptr(ws), ctypes.c_void_p(self._status.data_ptr()), T, n_seqs,
+                n_heads, n_kv_heads, head_dim, page_size, ctypes.c_longlong(k_pages.shape[0]), max_q_len, max_kv_len,
+                int(window or 0), ctypes.c_float(scale), 1 if allow_split else 0, _stream())
+            _check(rc, "paged_attention_decode")
+        elif use_mma:
             lib = self._lib("attention_mma")
             rc = lib.tl_attention_mma_plan(T, n_seqs, n_heads, n_kv_heads, head_dim, max_q_len, max_kv_len,
                                            1 if allow_split else 0, ctypes.byref(n_splits), ctypes.byref(floats))
