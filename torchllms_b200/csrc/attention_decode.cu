@@ -128,6 +128,8 @@ __global__ void __launch_bounds__(NTHREADS, 3) attention_decode_kernel(const __g
     __shared__ __align__(8) unsigned long long empty_bar[STAGES];
     __shared__ int failed_flag;
 
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int b = blockIdx.z;
     const int qs = p.q_start[b];
     const int ql = p.q_start[b + 1] - qs;
@@ -400,6 +402,8 @@ __global__ void merge_partials_kernel(const float* __restrict__ part_o, const fl
                                       __nv_bfloat16* __restrict__ out, int n_splits, int head_dim) {
     __shared__ float wgt[MERGE_MAX_SPLITS];
     __shared__ float red;
+    grid_launch_dependents();
+    grid_dependency_wait();
     const size_t row = blockIdx.x;
     const float* ml = part_ml + row * n_splits * 2;
     if (threadIdx.x < 32) {
@@ -532,9 +536,7 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParams& p, 
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
-    kern<<<grid, NTHREADS, smem, s>>>(mk, mv, p);
-    TL_LAUNCH_CHECK();
-    return TL_OK;
+    return (int)tl_launch(kern, grid, dim3(NTHREADS), smem, s, mk, mv, p);
 }
 
 }  // namespace
@@ -598,9 +600,10 @@ extern "C" int tl_paged_attention_decode(const void* q, const void* k_pages, con
     rc = head_dim == 128 ? launch<128>(mk, mv, p, grid, s) : launch<64>(mk, mv, p, grid, s);
     if (rc != TL_OK) return rc;
     if (pl.n_splits > 1) {
-        merge_partials_kernel<<<dim3((unsigned)n_tokens * (unsigned)n_heads), dim3(head_dim >= 128 ? 128u : 64u), 0, s>>>(
-            p.part_o, p.part_ml, p.out, pl.n_splits, head_dim);
-        TL_LAUNCH_CHECK();
+        cudaError_t e = tl_launch(merge_partials_kernel, dim3((unsigned)n_tokens * (unsigned)n_heads),
+                                  dim3(head_dim >= 128 ? 128u : 64u), 0, s, (const float*)p.part_o, (const float*)p.part_ml,
+                                  p.out, pl.n_splits, head_dim);
+        if (e != cudaSuccess) return (int)e;
     }
     return TL_OK;
 }

@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 enum TlStatus : int {
     TL_OK = 0,
@@ -66,6 +67,40 @@ __device__ __forceinline__ float warp_max(float x) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
     return x;
+}
+
+// ---- programmatic dependent launch: a kernel may start while its predecessor in the stream is
+// still running, do what does not depend on it (set-up, prefetching weights), and must call
+// grid_dependency_wait() before it touches anything the predecessor writes or reads.  Every
+// kernel launched through tl_launch calls it, so completion of a kernel still implies completion
+// of everything before it.  grid_launch_dependents() lets the successor be scheduled early.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* off = getenv("TORCHLLMS_B200_NO_PDL");
+        on = (off != nullptr && off[0] == '1') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+// Launch with the programmatic-stream-serialization attribute (works in stream capture too).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t tl_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

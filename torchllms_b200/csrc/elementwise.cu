@@ -11,6 +11,8 @@
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                              float* __restrict__ out, int dim, int vocab) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // the host rejects such ids; stay in bounds anyway
@@ -45,6 +47,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
                                const int* __restrict__ rows, int dim, float eps, int write_back) {
     extern __shared__ __align__(16) float row_buf[];  // the summed row, kept for the second pass
     __shared__ float warp_part[32];
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int o = blockIdx.x;
     const int r = rows ? rows[o] : o;
     float* hr = h + (size_t)r * dim;
@@ -108,6 +112,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
 template <typename TI, typename T>
 __global__ void swiglu_kernel(const TI* __restrict__ in, int splits, long long plane, T* __restrict__ out,
                               int hidden, long long total) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (; i < total; i += stride) {
@@ -128,14 +134,14 @@ extern "C" int tl_embed(const int* ids, const void* table, int table_dtype, floa
     if (dim <= 0 || vocab <= 0) return TL_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = dim >= 1024 ? 256 : 128;
+    cudaError_t e;
     if (table_dtype == TL_F32)
-        embed_kernel<float><<<n_tokens, threads, 0, s>>>(ids, (const float*)table, out, dim, vocab);
+        e = tl_launch(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, ids, (const float*)table, out, dim, vocab);
     else if (table_dtype == TL_BF16)
-        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(ids, (const __nv_bfloat16*)table, out, dim, vocab);
+        e = tl_launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, ids, (const __nv_bfloat16*)table, out, dim, vocab);
     else
         return TL_BAD_DTYPE;
-    TL_LAUNCH_CHECK();
-    return TL_OK;
+    return (int)e;
 }
 
 template <typename TD, typename TO>
@@ -153,9 +159,8 @@ static int launch_rmsnorm(float* h, const void* delta, int splits, long long pla
     const int per_thread = vec ? 4 : 1;
     int threads = (dim / per_thread + 31) / 32 * 32;
     threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
-    kern<<<n_out, threads, smem, s>>>(h, (const TD*)delta, splits, plane, w, (TO*)out, rows, dim, eps, write_back);
-    TL_LAUNCH_CHECK();
-    return TL_OK;
+    return (int)tl_launch(kern, dim3(n_out), dim3(threads), smem, s, h, (const TD*)delta, splits, plane, w, (TO*)out, rows,
+                          dim, eps, write_back);
 }
 
 // delta may be null (then nothing is added); it may hold `delta_splits` planes of [rows of h, dim],
@@ -188,14 +193,14 @@ extern "C" int tl_swiglu(const void* in, int in_dtype, int splits, void* out, in
     long long blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 32) blocks = 148 * 32;
     const long long plane = 2 * total;
+    const dim3 grid((unsigned)blocks), block(threads);
     if (in_dtype == TL_F32 && dtype == TL_F32)
-        swiglu_kernel<float, float><<<(int)blocks, threads, 0, s>>>((const float*)in, splits, plane, (float*)out, hidden, total);
-    else if (in_dtype == TL_BF16 && dtype == TL_BF16)
-        swiglu_kernel<__nv_bfloat16, __nv_bfloat16><<<(int)blocks, threads, 0, s>>>((const __nv_bfloat16*)in, splits, plane, (__nv_bfloat16*)out, hidden, total);
-    else if (in_dtype == TL_F32 && dtype == TL_BF16)
-        swiglu_kernel<float, __nv_bfloat16><<<(int)blocks, threads, 0, s>>>((const float*)in, splits, plane, (__nv_bfloat16*)out, hidden, total);
-    else
-        return TL_BAD_DTYPE;
-    TL_LAUNCH_CHECK();
-    return TL_OK;
+        return (int)tl_launch(swiglu_kernel<float, float>, grid, block, 0, s, (const float*)in, splits, plane, (float*)out, hidden, total);
+    if (in_dtype == TL_BF16 && dtype == TL_BF16)
+        return (int)tl_launch(swiglu_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)in, splits, plane,
+                              (__nv_bfloat16*)out, hidden, total);
+    if (in_dtype == TL_F32 && dtype == TL_BF16)
+        return (int)tl_launch(swiglu_kernel<float, __nv_bfloat16>, grid, block, 0, s, (const float*)in, splits, plane,
+                              (__nv_bfloat16*)out, hidden, total);
+    return TL_BAD_DTYPE;
 }

@@ -155,13 +155,23 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_d = tmem_base_slot;
     volatile int* aborted = &abort_flag;
+    grid_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
-            // ---- producer
-            for (int i = 0; i < n_kb; ++i) {
+            // ---- producer.  The weights depend on no earlier kernel: their first tiles are fetched
+            // before the dependency on the predecessor is resolved, the activations after it.
+            const int pre = n_kb < STAGES ? n_kb : STAGES;
+            for (int i = 0; i < pre; ++i) {
+                mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+                tma_load_2d(tiles + i * STAGE_BYTES, &map_w, &full_bar[i], (kb0 + i) * BK, slab * BP);
+            }
+            grid_dependency_wait();
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(tiles + i * STAGE_BYTES + W_BYTES, &map_a, &full_bar[i], (kb0 + i) * BK, 0);
+            for (int i = pre; i < n_kb; ++i) {
                 const int s = i % STAGES;
-                if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, aborted)) {
+                if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, aborted)) {
                     abort_flag = 1;
                     atomicExch(p.status, ERR_TMA_WAIT);
                     break;
@@ -287,9 +297,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, in
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
-    kern<<<dim3(slabs, splits), NTHREADS, smem, s>>>(mw, ma, p);
-    TL_LAUNCH_CHECK();
-    return TL_OK;
+    return (int)tl_launch(kern, dim3(slabs, splits), dim3(NTHREADS), smem, s, mw, ma, p);
 }
 
 }  // namespace

@@ -17,6 +17,8 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int splits, lon
                                      T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                      int n_heads, int n_kv_heads, int head_dim, int page_size,
                                      int table_rows, int interleaved) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int t = blockIdx.x;
     const int half = head_dim >> 1;
     const int heads_per_cta = (n_heads + 2 * n_kv_heads + gridDim.y - 1) / gridDim.y;
@@ -89,14 +91,12 @@ extern "C" int tl_rope_kv_write(const void* qkv, int in_dtype, int splits, const
     const int threads = pairs >= 1024 ? 256 : 128;
     const long long plane = (long long)n_tokens * (n_heads + 2 * n_kv_heads) * head_dim;
 #define TL_ROPE_LAUNCH(TI, T)                                                                                   \
-    rope_kv_write_kernel<TI, T><<<dim3(n_tokens, chunks), threads, 0, s>>>(                                                   \
-        (const TI*)qkv, splits, plane, positions, table, slot_mapping, (T*)q_out, (T*)k_pages, (T*)v_pages,     \
-        n_heads, n_kv_heads, head_dim, page_size, table_rows, interleaved)
-    if (in_dtype == TL_F32 && dtype == TL_F32) TL_ROPE_LAUNCH(float, float);
-    else if (in_dtype == TL_BF16 && dtype == TL_BF16) TL_ROPE_LAUNCH(__nv_bfloat16, __nv_bfloat16);
-    else if (in_dtype == TL_F32 && dtype == TL_BF16) TL_ROPE_LAUNCH(float, __nv_bfloat16);
-    else return TL_BAD_DTYPE;
+    tl_launch(rope_kv_write_kernel<TI, T>, dim3(n_tokens, chunks), dim3(threads), 0, s,                         \
+              (const TI*)qkv, splits, plane, positions, table, slot_mapping, (T*)q_out, (T*)k_pages, (T*)v_pages, \
+              n_heads, n_kv_heads, head_dim, page_size, table_rows, interleaved)
+    if (in_dtype == TL_F32 && dtype == TL_F32) return (int)TL_ROPE_LAUNCH(float, float);
+    if (in_dtype == TL_BF16 && dtype == TL_BF16) return (int)TL_ROPE_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    if (in_dtype == TL_F32 && dtype == TL_BF16) return (int)TL_ROPE_LAUNCH(float, __nv_bfloat16);
 #undef TL_ROPE_LAUNCH
-    TL_LAUNCH_CHECK();
-    return TL_OK;
+    return TL_BAD_DTYPE;
 }

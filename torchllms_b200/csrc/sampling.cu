@@ -141,6 +141,8 @@ __global__ void __launch_bounds__(NT1) sample_stage1_kernel(const float* __restr
                                                             float* __restrict__ part_v, int* __restrict__ part_i) {
     __shared__ float best_v[NT1 / 32];
     __shared__ int best_i[NT1 / 32];
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int r = blockIdx.y, chunk = blockIdx.x;
     const float* row = logits + (size_t)r * row_stride;
     const float temp = temperature ? temperature[r] : 0.f;
@@ -176,6 +178,8 @@ __global__ void __launch_bounds__(NT1) sample_stage1_kernel(const float* __restr
 
 __global__ void sample_stage2_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
                                      int n_chunks, int V, int* __restrict__ out) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int r = blockIdx.x, lane = threadIdx.x;
     float bv = -INFINITY;
     int bi = V;
@@ -205,11 +209,11 @@ extern "C" int tl_sample_wide(const float* logits, long long row_stride, int n_r
     float* part_v = (float*)scratch;
     int* part_i = (int*)scratch + (size_t)chunks * n_rows;
     cudaStream_t s = (cudaStream_t)stream;
-    sample_stage1_kernel<<<dim3(chunks, n_rows), NT1, 0, s>>>(logits, row_stride, vocab, temperature, row_keys, part_v, part_i);
-    TL_LAUNCH_CHECK();
-    sample_stage2_kernel<<<n_rows, 32, 0, s>>>(part_v, part_i, chunks, vocab, out);
-    TL_LAUNCH_CHECK();
-    return TL_OK;
+    cudaError_t e = tl_launch(sample_stage1_kernel, dim3(chunks, n_rows), dim3(NT1), 0, s, logits, row_stride, vocab,
+                              temperature, row_keys, part_v, part_i);
+    if (e != cudaSuccess) return (int)e;
+    return (int)tl_launch(sample_stage2_kernel, dim3(n_rows), dim3(32), 0, s, (const float*)part_v, (const int*)part_i,
+                          chunks, vocab, out);
 }
 
 // temperature, top_k and row_keys may be null: then every row is greedy / unfiltered.  A row
