@@ -305,10 +305,13 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, in
 // How many K splits the kernel would use for a [N, K] weight: a function of the weight's shape
 // only, so a token's result does not depend on what else is in the batch.
 extern "C" int tl_gemm_tcgen05_splits(int N, int K) {
+    // Two CTAs fit an SM; all CTAs of a launch should be resident at once (one wave), because a
+    // second, partly filled wave streams at a fraction of the bandwidth.  So: as many splits as
+    // keep slabs * splits within 2 * 148, each with at least four stages of work.
     const int slabs = (N + BP - 1) / BP;
     const int k_blocks = (K + BK - 1) / BK;
-    int splits = (2 * 148 + slabs - 1) / slabs;
-    const int most = k_blocks / 4 > 0 ? k_blocks / 4 : 1;      // at least four stages of work per CTA
+    int splits = (2 * 148) / slabs;
+    const int most = k_blocks / 4 > 0 ? k_blocks / 4 : 1;
     if (splits > most) splits = most;
     if (splits < 1) splits = 1;
     const int per = (k_blocks + splits - 1) / splits;
