@@ -265,6 +265,7 @@ def main():
 
     # ------------------------------------------------------------------ end to end through LLM.generate
     n_new = args.warmup + args.steps
+    llm.warmup(range(1, args.batch + 1))                                            # decode graphs, as at server start
     llm.generate(prompt_token_ids=prompts(args.batch, 64), max_new_tokens=4)        # warm the path
     llm.generate(prompt_token_ids=prompts(args.batch), max_new_tokens=n_new)
     st = llm.last_stats

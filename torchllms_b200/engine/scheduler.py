@@ -47,6 +47,15 @@ class Request:
     def tokens(self) -> List[int]:
         return self.prompt + self.generated
 
+    def span(self, start: int, n: int) -> List[int]:
+        """Tokens ``start .. start + n`` of prompt followed by generated, without joining the two."""
+        lp = len(self.prompt)
+        if start + n <= lp:
+            return self.prompt[start:start + n]
+        if start >= lp:
+            return self.generated[start - lp:start - lp + n]
+        return self.prompt[start:] + self.generated[:start + n - lp]
+
     def n_pending(self) -> int:
         return len(self.prompt) + len(self.generated) - self.n_fed
 
@@ -189,7 +198,7 @@ class Scheduler:
             return finished_now
         entries, samplers = [], []
         for r, n in planned:
-            toks = r.tokens()[r.n_fed:r.n_fed + n]
+            toks = r.span(r.n_fed, n)
             completes = r.n_fed + n == len(r.prompt) + len(r.generated)
             entries.append(StepEntry(r.handle, toks, [n - 1] if completes else []))
             if completes:

@@ -184,6 +184,29 @@ class Engine:
             self.model.ops.launches += entry[2]
         return entry[1]
 
+    def capture_decode_graphs(self, batch_sizes: Sequence[int]) -> int:
+        """Record the decode-step graphs for these numbers of requests ahead of time, with
+        throw-away requests (the cache must have room for one page each).  Returns how many
+        graphs exist afterwards.  Without this a shape is recorded the second time it occurs."""
+        if not self.use_graphs:
+            return 0
+        for b in sorted(set(int(x) for x in batch_sizes)):
+            if b < 1 or b > self.cache.max_num_seqs or (b, b) in self._graphs:
+                continue
+            if self.cache.n_live() + b > self.cache.max_num_seqs:
+                continue
+            handles = [self.claim() for _ in range(b)]
+            try:
+                for _ in range(3):          # one token each: eager, eager (first sight), recorded
+                    self.step([StepEntry(h, [0]) for h in handles])
+            except OutOfPages:
+                pass
+            finally:
+                for h in handles:
+                    self.release(h)
+        torch.cuda.synchronize()
+        return len(self._graphs)
+
     # --------------------------------------------------------------------- step
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run the entries' tokens as one batch.  Returns float32 logits
@@ -220,29 +243,34 @@ class Engine:
         starts = cache.extend_many([(e.handle, n) for e, n in zip(entries, q_lens)])  # may raise OutOfPages
         buf = self._buf
         buf.wait_host_free()
+        lens = np.asarray(q_lens, dtype=np.int64)
+        first = np.asarray(starts, dtype=np.int64)
         q_start = np.zeros(B + 1, dtype=np.int64)
-        np.cumsum(q_lens, out=q_start[1:])
-        kv_lens = [s + n for s, n in zip(starts, q_lens)]
+        np.cumsum(lens, out=q_start[1:])
+        kv_lens = (first + lens).tolist()
         slots = [cache.slot(e.handle) for e in entries]
+        slots_np = np.asarray(slots, dtype=np.int64)
+        # per token: which request it belongs to and its absolute position (no loop over requests)
+        seq_of = np.repeat(np.arange(B, dtype=np.int64), lens)
+        pos_all = np.arange(T, dtype=np.int64) - q_start[seq_of] + first[seq_of]
         buf.host_view("token_ids")[:T] = flat
-        pos = buf.host_view("positions")
-        sot = buf.host_view("seq_of_token")
-        for i, (s, n) in enumerate(zip(starts, q_lens)):
-            a = q_start[i]
-            pos[a:a + n] = np.arange(s, s + n)
-            sot[a:a + n] = i
+        buf.host_view("positions")[:T] = pos_all
+        buf.host_view("seq_of_token")[:T] = seq_of
         buf.host_view("q_start")[:B + 1] = q_start
         buf.host_view("kv_len")[:B] = kv_lens
         buf.host_view("state_slot")[:B] = slots
-        buf.host_view("fresh")[:B] = [1 if s == 0 else 0 for s in starts]
+        buf.host_view("fresh")[:B] = first == 0
         buf.host_view("want_rows")[:len(want_rows)] = want_rows
+        page = cache.page_size
         for g in range(len(cache.groups)):
-            sm = buf.host_view(f"slot_mapping{g}")
-            for i, (e, s, n) in enumerate(zip(entries, starts, q_lens)):
-                a = q_start[i]
-                sm[a:a + n] = cache.slot_mapping(g, e.handle, s, n)
-            bt = buf.host_view(f"block_table{g}")[:B * buf.NB].reshape(B, buf.NB)
-            bt[:] = cache.block_table_rows(g, slots)
+            rows = cache.block_table_rows(g, slots)                       # [B, max_blocks]
+            pages = rows[seq_of, pos_all // page]
+            if (pages < 0).any():
+                for e, s0 in zip(entries, starts):
+                    cache.truncate(e.handle, s0)
+                raise StepError("a token of this step falls on a page that was already given back")
+            buf.host_view(f"slot_mapping{g}")[:T] = pages * page + pos_all % page
+            buf.host_view(f"block_table{g}")[:B * buf.NB].reshape(B, buf.NB)[:] = rows
         buf.upload(B)
 
         decode_only = max(q_lens) == 1

@@ -112,6 +112,12 @@ class LLM:
         self.eos_set = set(self.eos_ids)
         self.last_stats = None
 
+    def warmup(self, batch_sizes: Optional[Sequence[int]] = None) -> int:
+        """Record the CUDA graphs of decode steps for these numbers of running requests (default:
+        every number up to ``max_bsz``) before the first request arrives; returns how many exist."""
+        sizes = list(batch_sizes) if batch_sizes is not None else list(range(1, self.max_bsz + 1))
+        return self.engine.capture_decode_graphs(sizes)
+
     def _kv_layout(self):
         needs: Dict[Any, int] = {}
         for need, _state, cache_of in self.model.run_needs():
