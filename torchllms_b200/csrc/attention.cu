@@ -345,3 +345,71 @@ extern "C" int tl_paged_attention(const void* q, const void* k_pages, const void
     }
     return TL_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same attention for callers that may not allocate: the split-KV partials live in a fixed
+// array inside this library instead of a workspace the caller brings.  See
+// attention_static_scratch.h for who needs this and for the rules of use.
+#include "attention_static_scratch.h"
+
+namespace {
+
+// Part of the library image: present on every device that loads it, until the process ends.
+static __device__ __align__(256) float tl_static_scratch[TL_STATIC_SCRATCH_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+float* static_scratch_address[MAX_DEVICES] = {};   // per device, asked for once
+
+// In host code the array's name is only a handle for the runtime, not a pointer a kernel could
+// use; the device address has to be asked for, with the right device current.
+int static_scratch_for_current_device(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= MAX_DEVICES) return TL_STATIC_SCRATCH_NO_ADDRESS;
+    if (static_scratch_address[dev] == nullptr) {
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, tl_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (ptr == nullptr) return TL_STATIC_SCRATCH_NO_ADDRESS;
+        static_scratch_address[dev] = ptr;
+    }
+    *out = static_scratch_address[dev];
+    return TL_OK;
+}
+
+}  // namespace
+
+extern "C" int tl_paged_attention_static_scratch(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                                 const int* block_table, int table_stride, const int* q_start,
+                                                 const int* kv_len, int dtype, int n_tokens, int n_seqs, int n_heads,
+                                                 int n_kv_heads, int head_dim, int page_size, int max_q_len,
+                                                 int max_kv_len, int window, float scale, int allow_split, void* stream) {
+    if (n_tokens <= 0 || n_seqs <= 0) return TL_OK;
+    int n_splits = 0;
+    long long floats = 0;
+    int rc = tl_attention_plan(n_tokens, n_seqs, n_heads, n_kv_heads, head_dim, max_q_len, max_kv_len, allow_split,
+                               &n_splits, &floats);
+    if (rc != TL_OK) return rc;
+    if (floats > (long long)TL_STATIC_SCRATCH_FLOATS) return TL_STATIC_SCRATCH_TOO_SMALL;   // nothing was launched
+    float* scratch = nullptr;
+    rc = static_scratch_for_current_device(&scratch);
+    if (rc != TL_OK) return rc;
+    // Every (row, split) cell that the merge reads is written by the attention kernel of this same
+    // call first, so what an earlier call left in the array does not matter and nothing is cleared.
+    return tl_paged_attention(q, k_pages, v_pages, out, block_table, table_stride, q_start, kv_len, scratch, dtype,
+                              n_tokens, n_seqs, n_heads, n_kv_heads, head_dim, page_size, max_q_len, max_kv_len,
+                              window, scale, allow_split, stream);
+}
+
+extern "C" const char* tl_static_scratch_strerror(int code) {
+    switch (code) {
+        case TL_OK: return "ok";
+        case TL_STATIC_SCRATCH_TOO_SMALL:
+            return "this step needs more split-KV scratch than the 8 MiB array built into the library holds; "
+                   "use fewer tokens, heads or splits per call, or tl_paged_attention with a workspace of your own";
+        case TL_STATIC_SCRATCH_NO_ADDRESS:
+            return "the runtime gave no device address for the built-in scratch array on the current device";
+        default: return "see the status codes of tl_paged_attention";
+    }
+}
