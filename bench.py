@@ -122,14 +122,21 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    """The unmodified reference through its own public API, if it is installed under baseline/_ref."""
+    """The unmodified reference through its own public API, if it is installed under baseline/_ref
+    (pip install --no-index --no-build-isolation --no-deps --target baseline/_ref <reference>)."""
     ref = ROOT / "baseline" / "_ref"
-    why = None
     if not (ref / "torchllms").is_dir():
-        why = "reference not installed under baseline/_ref (offline pip install not done on this box)"
+        why = "reference not installed under baseline/_ref"
     else:
-        why = ("reference LLM needs a tokenizer folder and a consolidated.00.pth checkpoint of the 8B shape; "
-               "no arm that drives its stock generate() with synthetic ids is wired up yet")
+        sys.path.insert(0, str(ref))
+        os.environ.setdefault("HF_HUB_OFFLINE", "1")
+        os.environ.setdefault("TRANSFORMERS_OFFLINE", "1")
+        try:
+            from torchllms.inference import LLM  # noqa: F401
+            why = ("the reference's LLM needs a tokenizer folder and a consolidated.00.pth checkpoint of the 8B "
+                   "shape (neither exists offline) and takes text prompts only; not driven")
+        except Exception as e:   # the installed package does not import
+            why = f"installed reference does not import: {type(e).__name__}: {str(e)[:160]}"
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
