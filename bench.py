@@ -269,6 +269,7 @@ def main():
         table(f"decode step, batch {args.batch}, context 2,048", prof)
         for x in [h] + hs:
             engine.release(x)
+        engine.use_graphs = True
 
     # ------------------------------------------------------------------ end to end through LLM.generate
     n_new = args.warmup + args.steps

@@ -108,23 +108,37 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
     }
 }
 
-// `in` holds `splits` planes of [tokens, 2 * hidden] (partial sums of a split-K product), summed first
-template <typename TI, typename T>
+// `in` holds `splits` planes of [tokens, 2 * hidden] (partial sums of a split-K product), summed first.
+// VEC = 4: hidden is a multiple of 4 and rows are 16-byte aligned: four gates and four ups per thread.
+template <typename TI, typename T, int VEC>
 __global__ void swiglu_kernel(const TI* __restrict__ in, int splits, long long plane, T* __restrict__ out,
-                              int hidden, long long total) {
+                              int hidden, int n_tokens) {
     grid_launch_dependents();
     grid_dependency_wait();
-    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long stride = (long long)gridDim.x * blockDim.x;
-    for (; i < total; i += stride) {
-        const long long t = i / hidden;
-        const int f = (int)(i - t * hidden);
-        float g = 0.f, u = 0.f;
-        for (int sp = 0; sp < splits; ++sp) {
-            g += to_float(in[sp * plane + t * 2 * hidden + f]);
-            u += to_float(in[sp * plane + t * 2 * hidden + hidden + f]);
+    const int per_row = hidden / VEC;
+    for (int t = blockIdx.y; t < n_tokens; t += gridDim.y) {
+        const TI* row = in + (size_t)t * 2 * hidden;
+        T* orow = out + (size_t)t * hidden;
+        for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < per_row; c += gridDim.x * blockDim.x) {
+            const int f = c * VEC;
+            if (VEC == 4) {
+                float4 g = load4(row + f), u = load4(row + hidden + f);
+                for (int sp = 1; sp < splits; ++sp) {
+                    const float4 g2 = load4(row + sp * plane + f), u2 = load4(row + sp * plane + hidden + f);
+                    g.x += g2.x; g.y += g2.y; g.z += g2.z; g.w += g2.w;
+                    u.x += u2.x; u.y += u2.y; u.z += u2.z; u.w += u2.w;
+                }
+                store4(orow + f, make_float4(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y,
+                                             g.z / (1.f + expf(-g.z)) * u.z, g.w / (1.f + expf(-g.w)) * u.w));
+            } else {
+                float g = 0.f, u = 0.f;
+                for (int sp = 0; sp < splits; ++sp) {
+                    g += to_float(row[sp * plane + f]);
+                    u += to_float(row[sp * plane + hidden + f]);
+                }
+                orow[f] = from_float<T>(g / (1.f + expf(-g)) * u);
+            }
         }
-        out[i] = from_float<T>(g / (1.f + expf(-g)) * u);
     }
 }
 
@@ -159,6 +173,7 @@ static int launch_rmsnorm(float* h, const void* delta, int splits, long long pla
     const int per_thread = vec ? 4 : 1;
     int threads = (dim / per_thread + 31) / 32 * 32;
     threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
+    if (n_out >= 512 && threads > 256) threads = 256;   // many rows: smaller CTAs, more of them resident
     return (int)tl_launch(kern, dim3(n_out), dim3(threads), smem, s, h, (const TD*)delta, splits, plane, w, (TO*)out, rows,
                           dim, eps, write_back);
 }
@@ -182,25 +197,29 @@ extern "C" int tl_rmsnorm(float* h, const void* delta, int delta_dtype, int delt
     return TL_BAD_DTYPE;
 }
 
+template <typename TI, typename T>
+static int launch_swiglu(const void* in, int splits, void* out, int n_tokens, int hidden, cudaStream_t s) {
+    const long long plane = 2LL * n_tokens * hidden;
+    const bool vec = hidden % 4 == 0 && aligned16(in) && aligned16(out) && sizeof(T) * hidden % 8 == 0;
+    const int per_row = vec ? hidden / 4 : hidden;
+    const int threads = 256;
+    int bx = (per_row + threads - 1) / threads;
+    if (bx > 64) bx = 64;
+    int by = n_tokens < 4096 ? n_tokens : 4096;
+    const dim3 grid(bx, by), block(threads);
+    if (vec)
+        return (int)tl_launch(swiglu_kernel<TI, T, 4>, grid, block, 0, s, (const TI*)in, splits, plane, (T*)out, hidden, n_tokens);
+    return (int)tl_launch(swiglu_kernel<TI, T, 1>, grid, block, 0, s, (const TI*)in, splits, plane, (T*)out, hidden, n_tokens);
+}
+
 // in: [splits, n_tokens, 2 * hidden] of in_dtype (splits > 1 only for float32 partial sums); out: [n_tokens, hidden]
 extern "C" int tl_swiglu(const void* in, int in_dtype, int splits, void* out, int dtype, int n_tokens, int hidden,
                          void* stream) {
-    const long long total = (long long)n_tokens * hidden;
-    if (total <= 0) return TL_OK;
+    if ((long long)n_tokens * hidden <= 0) return TL_OK;
     if (splits < 1) return TL_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = 256;
-    long long blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 32) blocks = 148 * 32;
-    const long long plane = 2 * total;
-    const dim3 grid((unsigned)blocks), block(threads);
-    if (in_dtype == TL_F32 && dtype == TL_F32)
-        return (int)tl_launch(swiglu_kernel<float, float>, grid, block, 0, s, (const float*)in, splits, plane, (float*)out, hidden, total);
-    if (in_dtype == TL_BF16 && dtype == TL_BF16)
-        return (int)tl_launch(swiglu_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)in, splits, plane,
-                              (__nv_bfloat16*)out, hidden, total);
-    if (in_dtype == TL_F32 && dtype == TL_BF16)
-        return (int)tl_launch(swiglu_kernel<float, __nv_bfloat16>, grid, block, 0, s, (const float*)in, splits, plane,
-                              (__nv_bfloat16*)out, hidden, total);
+    if (in_dtype == TL_F32 && dtype == TL_F32) return launch_swiglu<float, float>(in, splits, out, n_tokens, hidden, s);
+    if (in_dtype == TL_BF16 && dtype == TL_BF16) return launch_swiglu<__nv_bfloat16, __nv_bfloat16>(in, splits, out, n_tokens, hidden, s);
+    if (in_dtype == TL_F32 && dtype == TL_BF16) return launch_swiglu<float, __nv_bfloat16>(in, splits, out, n_tokens, hidden, s);
     return TL_BAD_DTYPE;
 }

@@ -71,6 +71,89 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int splits, lon
     }
 }
 
+// eight consecutive elements as floats
+__device__ __forceinline__ void load8(const float* p, float (&x)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&x)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        x[2 * i] = f.x;
+        x[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void store8(float* p, const float (&x)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(x[4], x[5], x[6], x[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&x)[8]) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+
+// The adjacent-lane pairing with 16-byte accesses: a thread takes eight consecutive lanes (four
+// pairs) of one head.  Same arithmetic as the kernel above.
+template <typename TI, typename T>
+__global__ void rope_kv_write_vec_kernel(const TI* __restrict__ qkv, int splits, long long plane,
+                                         const int* __restrict__ positions, const float* __restrict__ table,
+                                         const int* __restrict__ slot_mapping, T* __restrict__ q_out,
+                                         T* __restrict__ k_pages, T* __restrict__ v_pages, int n_heads, int n_kv_heads,
+                                         int head_dim, int page_size, int table_rows) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int t = blockIdx.x;
+    const int heads = n_heads + 2 * n_kv_heads;
+    const int per_head = head_dim >> 3;
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= table_rows ? table_rows - 1 : pos);
+    const float* cs = table + (size_t)pos * head_dim;
+    const TI* src = qkv + (size_t)t * heads * head_dim;
+    const bool write = k_pages != nullptr;
+    int page = 0, slot = 0;
+    if (write) {
+        const int sm = slot_mapping[t];
+        page = sm / page_size;
+        slot = sm - page * page_size;
+    }
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < heads * per_head; c += gridDim.y * blockDim.x) {
+        const int head = c / per_head;
+        const int off = (c - head * per_head) << 3;
+        float x[8];
+        load8(src + head * head_dim + off, x);
+        for (int sp = 1; sp < splits; ++sp) {
+            float y[8];
+            load8(src + sp * plane + head * head_dim + off, y);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] += y[i];
+        }
+        if (head < n_heads + n_kv_heads) {
+            float r[8];
+            load8(cs + off, r);          // (cos, sin) of the four pairs
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float a = x[2 * i], b = x[2 * i + 1], co = r[2 * i], si = r[2 * i + 1];
+                x[2 * i] = a * co - b * si;
+                x[2 * i + 1] = b * co + a * si;
+            }
+        }
+        if (head < n_heads) {
+            store8(q_out + ((size_t)t * n_heads + head) * head_dim + off, x);
+        } else if (write) {
+            const bool is_k = head < n_heads + n_kv_heads;
+            const int kvh = is_k ? head - n_heads : head - n_heads - n_kv_heads;
+            T* base = is_k ? k_pages : v_pages;
+            store8(base + (((size_t)page * n_kv_heads + kvh) * page_size + slot) * head_dim + off, x);
+        }
+    }
+}
+
 // k_pages / v_pages may both be null: then only q is produced (a run that reads another run's cache).
 // qkv: [splits, n_tokens, row] of in_dtype (splits > 1 only for float32 partial sums); q, pages: dtype.
 extern "C" int tl_rope_kv_write(const void* qkv, int in_dtype, int splits, const int* positions, const float* table,
@@ -90,6 +173,22 @@ extern "C" int tl_rope_kv_write(const void* qkv, int in_dtype, int splits, const
     const int pairs = per_cta * (head_dim / 2);
     const int threads = pairs >= 1024 ? 256 : 128;
     const long long plane = (long long)n_tokens * (n_heads + 2 * n_kv_heads) * head_dim;
+    if (interleaved && head_dim % 8 == 0 && aligned16(qkv) && aligned16(q_out) && aligned16(table) &&
+        (k_pages == nullptr || (aligned16(k_pages) && aligned16(v_pages)))) {
+        const int chunks8 = heads * (head_dim / 8);
+        const int vthreads = 128;
+        int by = (chunks8 + vthreads - 1) / vthreads;
+        if (n_tokens >= 256 && by > 2) by = 2;        // many tokens: fewer, fatter CTAs
+#define TL_ROPE_VEC(TI, T)                                                                                      \
+    tl_launch(rope_kv_write_vec_kernel<TI, T>, dim3(n_tokens, by), dim3(vthreads), 0, s,                        \
+              (const TI*)qkv, splits, plane, positions, table, slot_mapping, (T*)q_out, (T*)k_pages, (T*)v_pages, \
+              n_heads, n_kv_heads, head_dim, page_size, table_rows)
+        if (in_dtype == TL_F32 && dtype == TL_F32) return (int)TL_ROPE_VEC(float, float);
+        if (in_dtype == TL_BF16 && dtype == TL_BF16) return (int)TL_ROPE_VEC(__nv_bfloat16, __nv_bfloat16);
+        if (in_dtype == TL_F32 && dtype == TL_BF16) return (int)TL_ROPE_VEC(float, __nv_bfloat16);
+#undef TL_ROPE_VEC
+        return TL_BAD_DTYPE;
+    }
 #define TL_ROPE_LAUNCH(TI, T)                                                                                   \
     tl_launch(rope_kv_write_kernel<TI, T>, dim3(n_tokens, chunks), dim3(threads), 0, s,                         \
               (const TI*)qkv, splits, plane, positions, table, slot_mapping, (T*)q_out, (T*)k_pages, (T*)v_pages, \
