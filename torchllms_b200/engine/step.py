@@ -133,16 +133,20 @@ class Engine:
                                   max_num_seqs=max_num_seqs, max_len=self.max_len, dtype=model.dtype,
                                   device=self.device, max_step_tokens=self.max_step_tokens)
         self._buf = _StepBuffers(self.cache, self.max_step_tokens, self.device)
+        self._has_window = any(g.need.kind == "window" for g in self.cache.groups)
         self.vocab_size = model.spec.vocab_size
         self.steps_run = 0
         self.tokens_run = 0
-        # Steps that hold one token per request have the same launch shapes whenever the number of
-        # requests is the same, so they are recorded once into a CUDA graph and replayed.
+        # A step's launch shapes depend only on (tokens, requests, wanted rows, longest portion), never
+        # on how long the requests have grown: the kernels read lengths and tables from the uploaded
+        # buffers.  So a shape that keeps coming back (every decode step with the same number of
+        # requests; every full prompt chunk) is recorded once into a CUDA graph and replayed.
         ops = model.ops
         self.use_graphs = bool(use_graphs and self.device.type == "cuda" and model.graph_safe
                                and getattr(ops, "graph_capturable", lambda d: False)(model.dtype))
-        self._graphs = {}          # (n_requests, n_wanted) -> (graph, logits buffer, launches)
+        self._graphs = {}          # shape key -> (graph, logits buffer, launches)
         self._graph_seen = {}
+        self.max_prompt_graphs = 16   # recorded shapes other than decode steps (each keeps its activations)
         self._graph_pool = None
         self.graph_replays = 0
 
@@ -157,15 +161,18 @@ class Engine:
         return self.cache.can_extend(wants)
 
     def _forward_graphed(self, ctx: StepContext, views) -> Optional[torch.Tensor]:
-        """Decode steps: the second step of a shape records a CUDA graph, later ones replay it.
-        The logits buffer of a shape is reused: its contents hold until the next step."""
-        key = (ctx.n_seqs, ctx.n_want)
+        """A decode shape is recorded the second time it occurs, any other shape the third time
+        (while fewer than ``max_prompt_graphs`` of those exist); later steps replay.  The logits
+        buffer of a shape is reused: its contents hold until the next step of that shape."""
+        key = self._shape_key(ctx.n_tokens, ctx.n_seqs, ctx.n_want, ctx.max_q_len)
         entry = self._graphs.get(key)
         if entry is None:
             seen = self._graph_seen.get(key, 0)
             self._graph_seen[key] = seen + 1
-            if seen == 0:
-                return self.model.forward(ctx, views)          # first time eager: loads libraries, sizes scratch
+            decode = ctx.max_q_len == 1
+            full = (not decode) and sum(1 for k in self._graphs if k[3] != 1) >= self.max_prompt_graphs
+            if seen < (1 if decode else 2) or full:
+                return self.model.forward(ctx, views)          # eager: loads libraries, sizes scratch
             ops = self.model.ops
             before = getattr(ops, "launches", 0)
             torch.cuda.synchronize()
@@ -178,6 +185,13 @@ class Engine:
             self._graphs[key] = entry
             if hasattr(ops, "launches"):
                 ops.launches = before
+        return self._replay(entry)
+
+    @staticmethod
+    def _shape_key(n_tokens: int, n_seqs: int, n_want: int, max_q_len: int):
+        return (n_tokens, n_seqs, n_want, max_q_len)
+
+    def _replay(self, entry) -> Optional[torch.Tensor]:
         entry[0].replay()
         self.graph_replays += 1
         if hasattr(self.model.ops, "launches"):
@@ -191,7 +205,7 @@ class Engine:
         if not self.use_graphs:
             return 0
         for b in sorted(set(int(x) for x in batch_sizes)):
-            if b < 1 or b > self.cache.max_num_seqs or (b, b) in self._graphs:
+            if b < 1 or b > self.cache.max_num_seqs or self._shape_key(b, b, b, 1) in self._graphs:
                 continue
             if self.cache.n_live() + b > self.cache.max_num_seqs:
                 continue
@@ -249,7 +263,6 @@ class Engine:
         np.cumsum(lens, out=q_start[1:])
         kv_lens = (first + lens).tolist()
         slots = [cache.slot(e.handle) for e in entries]
-        slots_np = np.asarray(slots, dtype=np.int64)
         # per token: which request it belongs to and its absolute position (no loop over requests)
         seq_of = np.repeat(np.arange(B, dtype=np.int64), lens)
         pos_all = np.arange(T, dtype=np.int64) - q_start[seq_of] + first[seq_of]
@@ -274,29 +287,37 @@ class Engine:
         buf.upload(B)
 
         decode_only = max(q_lens) == 1
-        ctx = StepContext(
-            n_tokens=T, n_seqs=B, n_want=len(want_rows), max_q_len=max(q_lens),
-            # decode steps plan for the longest sequence there can be, so their shape depends on B alone
-            max_kv_len=self.max_len if decode_only else max(kv_lens),
-            token_ids=buf.dev_view("token_ids", T), positions=buf.dev_view("positions", T),
-            seq_of_token=buf.dev_view("seq_of_token", T), q_start=buf.dev_view("q_start", B + 1),
-            kv_len=buf.dev_view("kv_len", B), state_slot=buf.dev_view("state_slot", B),
-            fresh=buf.dev_view("fresh", B), want_rows=buf.dev_view("want_rows", len(want_rows)),
-            q_lens=q_lens, kv_lens=kv_lens, slots=slots)
-        block_tables = [buf.dev_view(f"block_table{g}", B * buf.NB).view(B, buf.NB) for g in range(len(cache.groups))]
-        slot_maps = [buf.dev_view(f"slot_mapping{g}", T) for g in range(len(cache.groups))]
-        views = [cache.run_view(i, block_tables, slot_maps) for i in range(cache.n_runs)]
+        n_want = len(want_rows)
         try:
-            if decode_only and self.use_graphs:
-                logits = self._forward_graphed(ctx, views)
+            recorded = self._graphs.get(self._shape_key(T, B, n_want, max(q_lens))) if self.use_graphs else None
+            if recorded is not None:
+                # the graph reads the buffers uploaded above at their fixed addresses: nothing else to build
+                logits = self._replay(recorded)
             else:
-                logits = self.model.forward(ctx, views)
+                ctx = StepContext(
+                    n_tokens=T, n_seqs=B, n_want=n_want, max_q_len=max(q_lens),
+                    # steps of short portions (where keys may be split over CTAs) plan for the longest
+                    # sequence there can be, so that their launch shapes do not depend on the lengths
+                    max_kv_len=self.max_len if max(q_lens) <= 16 else max(kv_lens),
+                    token_ids=buf.dev_view("token_ids", T), positions=buf.dev_view("positions", T),
+                    seq_of_token=buf.dev_view("seq_of_token", T), q_start=buf.dev_view("q_start", B + 1),
+                    kv_len=buf.dev_view("kv_len", B), state_slot=buf.dev_view("state_slot", B),
+                    fresh=buf.dev_view("fresh", B), want_rows=buf.dev_view("want_rows", n_want),
+                    q_lens=q_lens, kv_lens=kv_lens, slots=slots)
+                block_tables = [buf.dev_view(f"block_table{g}", B * buf.NB).view(B, buf.NB) for g in range(len(cache.groups))]
+                slot_maps = [buf.dev_view(f"slot_mapping{g}", T) for g in range(len(cache.groups))]
+                views = [cache.run_view(i, block_tables, slot_maps) for i in range(cache.n_runs)]
+                if self.use_graphs:
+                    logits = self._forward_graphed(ctx, views)
+                else:
+                    logits = self.model.forward(ctx, views)
         except BaseException:
             for e, s in zip(entries, starts):  # leave the cache as the step found it
                 cache.truncate(e.handle, s)
             raise
-        for e in entries:
-            cache.pass_window(e.handle)
+        if self._has_window:
+            for e in entries:
+                cache.pass_window(e.handle)
         self.steps_run += 1
         self.tokens_run += T
         return logits
