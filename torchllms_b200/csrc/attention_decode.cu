@@ -144,27 +144,6 @@ __global__ void __launch_bounds__(NTHREADS, 3) attention_decode_kernel(const __g
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     volatile int* failed = &failed_flag;
 
-    if (tid == 0) {
-        failed_flag = 0;
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], NCW);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    // queries (zero rows where the tile has none)
-    for (int c = tid; c < 16 * (HD / 8); c += NTHREADS) {
-        const int rr = c / (HD / 8), part = c - rr * (HD / 8);
-        const int tok = tok0 + rr / ng;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (rr < p.tpw * ng && tok < ql) {
-            const int head = kvh * p.group + g0 + rr % ng;
-            v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + tok) * p.n_heads + head) * HD + part * 8);
-        }
-        *reinterpret_cast<uint4*>(Qs + rr * QPITCH + part * 8) = v;
-    }
-    __syncthreads();
-
     // ---- which keys this CTA walks: its share of the request's visible keys, in whole tiles
     const int cta_tok_hi = min(ql, tok0 + p.tpw);
     const int qpos_base = kl - ql;
@@ -179,6 +158,55 @@ __global__ void __launch_bounds__(NTHREADS, 3) attention_decode_kernel(const __g
     }
     const int k_start = k_lo & ~(p.box_rows - 1);      // copies start on a box (page) boundary; keys below k_lo are masked
     const int n_tiles = k_hi > k_start ? (k_hi - k_start + BN - 1) / BN : 0;
+    const int* table = p.block_table + (size_t)b * p.table_stride;
+
+    // one tile: a box per page (or per 64 rows of a larger page) and 64-element column block, K and V
+    auto issue_tile = [&](int it) {
+        const int s = it % STAGES;
+        const int k0 = k_start + it * BN;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        unsigned char* kt = tiles + s * STAGE_BYTES;
+        for (int c = 0; c < BN / p.box_rows; ++c) {
+            const int kpos = k0 + c * p.box_rows;
+            // boxes past the last key start outside the tensor: the copy writes the zero fill, so
+            // that what is multiplied by probability 0 there is finite
+            int row = p.total_rows;
+            if (kpos < k_hi) {
+                const int page = table[kpos >> p.page_shift];
+                row = (page * p.n_kv_heads + kvh) * p.page_size + (kpos & (p.page_size - 1));
+            }
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) {
+                unsigned char* dst = kt + h * HALF_BYTES + c * p.box_rows * 128;
+                tma_load_2d(dst, &map_k, &full_bar[s], h * 64, row);
+                tma_load_2d(dst + KV_BYTES, &map_v, &full_bar[s], h * 64, row);
+            }
+        }
+    };
+
+    if (tid == NCW * 32) {
+        // the producer lane sets the barriers up and sends the first tiles on their way while the
+        // other warps are still fetching the queries
+        failed_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], NCW);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        for (int it = 0; it < STAGES && it < n_tiles; ++it) issue_tile(it);
+    }
+    // queries (zero rows where the tile has none)
+    for (int c = tid; c < 16 * (HD / 8); c += NTHREADS) {
+        const int rr = c / (HD / 8), part = c - rr * (HD / 8);
+        const int tok = tok0 + rr / ng;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (rr < p.tpw * ng && tok < ql) {
+            const int head = kvh * p.group + g0 + rr % ng;
+            v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + tok) * p.n_heads + head) * HD + part * 8);
+        }
+        *reinterpret_cast<uint4*>(Qs + rr * QPITCH + part * 8) = v;
+    }
+    __syncthreads();
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[HD / 8][4];
@@ -187,35 +215,15 @@ __global__ void __launch_bounds__(NTHREADS, 3) attention_decode_kernel(const __g
     const int g = lane >> 2, t = lane & 3;
 
     if (warp == NCW) {
-        // ---- producer
+        // ---- producer: the first tiles are on their way; keep the ring full
         if (lane == 0) {
-            const int* table = p.block_table + (size_t)b * p.table_stride;
-            for (int it = 0; it < n_tiles; ++it) {
-                const int s = it % STAGES;
-                if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1, failed)) {
+            for (int it = STAGES; it < n_tiles; ++it) {
+                if (!mbar_wait(&empty_bar[it % STAGES], ((it / STAGES) - 1) & 1, failed)) {
                     failed_flag = 1;
                     atomicExch(p.status, ERR_PRODUCER_WAIT);
                     break;
                 }
-                const int k0 = k_start + it * BN;
-                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-                unsigned char* kt = tiles + s * STAGE_BYTES;
-                for (int c = 0; c < BN / p.box_rows; ++c) {
-                    const int kpos = k0 + c * p.box_rows;
-                    // boxes past the last key start outside the tensor: the copy writes the zero fill, so
-                    // that what is multiplied by probability 0 there is finite
-                    int row = p.total_rows;
-                    if (kpos < k_hi) {
-                        const int page = table[kpos >> p.page_shift];
-                        row = (page * p.n_kv_heads + kvh) * p.page_size + (kpos & (p.page_size - 1));
-                    }
-#pragma unroll
-                    for (int h = 0; h < HALVES; ++h) {
-                        unsigned char* dst = kt + h * HALF_BYTES + c * p.box_rows * 128;
-                        tma_load_2d(dst, &map_k, &full_bar[s], h * 64, row);
-                        tma_load_2d(dst + KV_BYTES, &map_v, &full_bar[s], h * 64, row);
-                    }
-                }
+                issue_tile(it);
             }
         }
     } else {
