@@ -153,3 +153,144 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
         engine.cache.check_invariants()
     finally:
         MIXERS.unregister("toy_running_mean")
+
+
+# --------------------------------------------------------------------------------------------------
+# A feed-forward with routing and another position encoding, both defined here.
+
+from torchllms_b200.parts.base import (FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, PositionEncoding,  # noqa: E402
+                                       register_feed_forward, register_position_encoding)
+
+
+class RoutedFFN(FeedForward):
+    """Top-1 routing over small experts: out = gate * W_out[e] relu(W_in[e] x), e = argmax(router x).
+    Router logits and the softmax over them are float32."""
+
+    def __init__(self, env, *, dim, hidden, n_experts):
+        self.env, self.dim, self.hidden, self.n_experts = env, dim, hidden, n_experts
+
+    def expected_tensors(self):
+        out = {"router.weight": ExpectedTensor((self.n_experts, self.dim))}
+        for e in range(self.n_experts):
+            out[f"experts.{e}.w_in.weight"] = ExpectedTensor((self.hidden, self.dim))
+            out[f"experts.{e}.w_out.weight"] = ExpectedTensor((self.dim, self.hidden))
+        return out
+
+    def load(self, tensors):
+        self.router = tensors["router.weight"].to(self.env.device, torch.float32)
+        self.w_in = [as_compute(tensors[f"experts.{e}.w_in.weight"], self.env) for e in range(self.n_experts)]
+        self.w_out = [as_compute(tensors[f"experts.{e}.w_out.weight"], self.env) for e in range(self.n_experts)]
+
+    def forward(self, x, ctx):
+        probs = torch.softmax(x.float() @ self.router.t(), -1)
+        gate, choice = probs.max(-1)
+        out = torch.zeros_like(x)
+        for e in range(self.n_experts):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel():
+                h = torch.relu(self.env.ops.linear(x[rows].contiguous(), self.w_in[e]))
+                out[rows] = (self.env.ops.linear(h, self.w_out[e]).float() * gate[rows, None]).to(x.dtype)
+        return out
+
+
+class LearnedOffsets(PositionEncoding):
+    """No rotation: a learned vector per position is added to q and k (float32 sum), v is stored as it is."""
+
+    def __init__(self, env, *, head_dim, max_positions):
+        self.env, self.head_dim, self.max_positions = env, head_dim, max_positions
+
+    def expected_tensors(self):
+        return {"offsets.weight": ExpectedTensor((self.max_positions, self.head_dim))}
+
+    def load(self, tensors):
+        self.offsets = tensors["offsets.weight"].to(self.env.device, torch.float32)
+        # an identity table lets the fused kernel do the split and the cache write without rotating
+        ident = torch.zeros(self.max_positions, self.head_dim // 2, 2)
+        ident[..., 0] = 1.0
+        self.identity = ident.to(self.env.device)
+
+    def encode_and_store(self, qkv, ctx, cache, n_heads, n_kv_heads, head_dim):
+        T = qkv.shape[0]
+        x = qkv.float().view(T, n_heads + 2 * n_kv_heads, head_dim).clone()
+        x[:, : n_heads + n_kv_heads] += self.offsets[ctx.positions.long()][:, None, :]
+        shifted = x.view(T, -1).to(qkv.dtype)
+        return self.env.ops.rope_kv_write(
+            shifted, ctx.positions, self.identity, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim,
+            interleaved=True, k_pages=cache.k_pages if cache.writes else None,
+            v_pages=cache.v_pages if cache.writes else None, slot_mapping=cache.slot_mapping, page_size=cache.page_size)
+
+
+def test_toy_routed_feed_forward_and_other_position_encodings():
+    from torchllms_b200.kernels import get_ops
+    register_feed_forward("toy_routed")(RoutedFFN)
+    register_position_encoding("toy_learned_offsets")(LearnedOffsets)
+    try:
+        dim, H, KV, hd, vocab, E = 64, 4, 2, 16, 97, 3
+        norm = part("rmsnorm", dim=dim, eps=1e-5)
+        blk = part("prenorm", mixer_prefix="mixer", ffn_prefix="ffn", mixer_norm_prefix="norm1", ffn_norm_prefix="norm2")
+        attn_learned = part("attention", dim=dim, n_heads=H, n_kv_heads=KV, head_dim=hd, scale=hd ** -0.5, window=None,
+                            position=part("toy_learned_offsets", head_dim=hd, max_positions=128))
+        attn_half = part("attention", dim=dim, n_heads=H, n_kv_heads=KV, head_dim=hd, scale=hd ** -0.5, window=None,
+                         position=part("rope", head_dim=hd, theta=100.0, scaling=None, pairing="half"))
+        routed = part("toy_routed", dim=dim, hidden=40, n_experts=E)
+        dense = part("swiglu", dim=dim, hidden=72)
+        spec = ModelSpec(dim=dim, vocab_size=vocab, max_positions=128, embedding_tensor="embed.weight",
+                         layers=(LayerSpec("l0", blk, attn_learned, routed, norm, norm),
+                                 LayerSpec("l1", blk, attn_half, dense, norm, norm)),
+                         run_order=(RunEntry(0), RunEntry(1)), final_norm=norm, final_norm_prefix="final_norm",
+                         head_tensor="head.weight")
+        model = Model(spec, dtype=torch.float32, device="cuda", ops=get_ops())
+        assert not model.graph_safe          # parts that read back on the host keep the engine off CUDA graphs
+        g = torch.Generator().manual_seed(11)
+        w = {n: (1 + 0.1 * torch.randn(e.shape, generator=g) if "norm" in n else torch.randn(e.shape, generator=g) * 0.15)
+             for n, e in model.expected_tensors().items()}
+        # a position encoding's tensors live under the mixer that owns it
+        assert "l0.mixer.position.offsets.weight" in w and "l0.ffn.experts.2.w_out.weight" in w
+        model.load(w)
+        engine = Engine(model, page_size=8, pool_tokens=128, max_num_seqs=2, max_len=128, max_step_tokens=64)
+        toks = torch.randint(0, vocab, (50,), generator=g).tolist()
+
+        # ---- the same model written out plainly, whole sequence, no cache
+        S = len(toks)
+        x = w["embed.weight"][torch.tensor(toks)]
+        offsets = w["l0.mixer.position.offsets.weight"]
+
+        def attend(x, p, encode):
+            n = plain_llama.rms_norm(x, w[f"{p}.norm1.weight"], 1e-5)
+            q = (n @ w[f"{p}.mixer.wq.weight"].T).view(S, H, hd)
+            k = (n @ w[f"{p}.mixer.wk.weight"].T).view(S, KV, hd)
+            v = (n @ w[f"{p}.mixer.wv.weight"].T).view(S, KV, hd)
+            q, k = encode(q), encode(k)
+            return x + plain_llama.causal_attention(q, k, v) @ w[f"{p}.mixer.wo.weight"].T
+
+        def half_rope(t):
+            inv = plain_llama.rope_frequencies(hd, 100.0, None)
+            cos, sin = plain_llama.rope_angles(inv, torch.arange(S))
+            a, b = t[..., : hd // 2], t[..., hd // 2:]
+            c, s_ = cos[:, None, :], sin[:, None, :]
+            return torch.cat([a * c - b * s_, b * c + a * s_], -1)
+
+        h = attend(x, "l0", lambda t: t + offsets[:S, None, :])
+        n = plain_llama.rms_norm(h, w["l0.norm2.weight"], 1e-5)
+        probs = torch.softmax(n @ w["l0.ffn.router.weight"].T, -1)
+        gate, choice = probs.max(-1)
+        ff = torch.zeros_like(n)
+        for t in range(S):
+            e = int(choice[t])
+            ff[t] = gate[t] * (torch.relu(n[t] @ w[f"l0.ffn.experts.{e}.w_in.weight"].T) @ w[f"l0.ffn.experts.{e}.w_out.weight"].T)
+        h = h + ff
+        h = attend(h, "l1", half_rope)
+        m = plain_llama.rms_norm(h, w["l1.norm2.weight"], 1e-5)
+        h = h + plain_llama.swiglu_ffn(m, w["l1.ffn.w1.weight"], w["l1.ffn.w2.weight"], w["l1.ffn.w3.weight"])
+        want = plain_llama.rms_norm(h, w["final_norm.weight"], 1e-5) @ w["head.weight"].T
+
+        handle = engine.claim()
+        got, fed = [], 0
+        for n_tok in (7, 2, 20, 1, 1, 19):
+            got.append(engine.step([StepEntry(handle, toks[fed:fed + n_tok], list(range(n_tok)))]).cpu())
+            fed += n_tok
+        err = (torch.cat(got) - want).abs().max().item()
+        assert err < 1e-4, err
+    finally:
+        FEED_FORWARDS.unregister("toy_routed")
+        POSITION_ENCODINGS.unregister("toy_learned_offsets")

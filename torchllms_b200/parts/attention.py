@@ -44,17 +44,22 @@ class PagedAttention(Mixer):
 
     def expected_tensors(self) -> Dict[str, ExpectedTensor]:
         q, kv = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
-        return {
+        out = {
             "wq.weight": ExpectedTensor((q, self.dim)),
             "wk.weight": ExpectedTensor((kv, self.dim)),
             "wv.weight": ExpectedTensor((kv, self.dim)),
             "wo.weight": ExpectedTensor((self.dim, q)),
         }
+        # a position encoding with tensors of its own (none for rope) keeps them under "position."
+        for name, e in self.position.expected_tensors().items():
+            out[f"position.{name}"] = e
+        return out
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         # One projection for q, k and v: rows [wq; wk; wv].
         self.wqkv = torch.cat([as_compute(tensors[n], self.env) for n in ("wq.weight", "wk.weight", "wv.weight")])
         self.wo = as_compute(tensors["wo.weight"], self.env)
+        self.position.load({name: tensors[f"position.{name}"] for name in self.position.expected_tensors()})
 
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         ops = self.env.ops
