@@ -41,7 +41,7 @@ def ctx_for(portions, starts, page_size, n_pages, device="cuda"):
     slots = [int(table[i, p // page_size]) * page_size + p % page_size for i, p in zip(seq, pos)]
     t = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
     kv = [s + n for s, n in zip(starts, portions)]
-    ctx = StepContext(n_tokens=len(pos), n_seqs=B, n_want=0, max_q_len=max(portions), max_kv_len=max(kv),
+    ctx = StepContext(n_tokens=len(pos), n_seqs=B, n_want=0, max_q_len=max(portions), max_kv_len=max(kv), n_decode=0,
                       token_ids=t([0] * len(pos)), positions=t(pos), seq_of_token=t(seq), q_start=t(q_start),
                       kv_len=t(kv), state_slot=t(list(range(B))), fresh=t([int(s == 0) for s in starts]),
                       want_rows=t([]), q_lens=list(portions), kv_lens=kv, slots=list(range(B)))

@@ -118,11 +118,11 @@ class TorchOps:
         return q
 
     def paged_attention(self, q, k_pages, v_pages, block_table, q_start, kv_len, *, n_seqs, max_q_len,
-                        max_kv_len, scale, window, page_size, allow_split=True, impl="auto"):
+                        max_kv_len, scale, window, page_size, allow_split=True, impl="auto", n_tokens=None, out=None):
         T, H, hd = q.shape
         KV = k_pages.shape[1]
         group = H // KV
-        out = torch.zeros_like(q)
+        out = torch.zeros_like(q) if out is None else out
         qs = q_start.tolist()
         kl = kv_len.tolist()
         for b in range(n_seqs):

@@ -52,6 +52,7 @@ class StepContext:
     n_want: int
     max_q_len: int
     max_kv_len: int
+    n_decode: int                # how many requests at the head of the batch bring exactly one token
     token_ids: torch.Tensor      # [T] int32
     positions: torch.Tensor      # [T] int32, absolute position of each token in its request
     seq_of_token: torch.Tensor   # [T] int32, index into the step's requests
@@ -164,7 +165,7 @@ class Engine:
         """A decode shape is recorded the second time it occurs, any other shape the third time
         (while fewer than ``max_prompt_graphs`` of those exist); later steps replay.  The logits
         buffer of a shape is reused: its contents hold until the next step of that shape."""
-        key = self._shape_key(ctx.n_tokens, ctx.n_seqs, ctx.n_want, ctx.max_q_len)
+        key = self._shape_key(ctx.n_tokens, ctx.n_seqs, ctx.n_want, ctx.max_q_len, ctx.n_decode)
         entry = self._graphs.get(key)
         if entry is None:
             seen = self._graph_seen.get(key, 0)
@@ -188,8 +189,8 @@ class Engine:
         return self._replay(entry)
 
     @staticmethod
-    def _shape_key(n_tokens: int, n_seqs: int, n_want: int, max_q_len: int):
-        return (n_tokens, n_seqs, n_want, max_q_len)
+    def _shape_key(n_tokens: int, n_seqs: int, n_want: int, max_q_len: int, n_decode: int):
+        return (n_tokens, n_seqs, n_want, max_q_len, n_decode)
 
     def _replay(self, entry) -> Optional[torch.Tensor]:
         entry[0].replay()
@@ -205,7 +206,7 @@ class Engine:
         if not self.use_graphs:
             return 0
         for b in sorted(set(int(x) for x in batch_sizes)):
-            if b < 1 or b > self.cache.max_num_seqs or self._shape_key(b, b, b, 1) in self._graphs:
+            if b < 1 or b > self.cache.max_num_seqs or self._shape_key(b, b, b, 1, b) in self._graphs:
                 continue
             if self.cache.n_live() + b > self.cache.max_num_seqs:
                 continue
@@ -288,14 +289,17 @@ class Engine:
 
         decode_only = max(q_lens) == 1
         n_want = len(want_rows)
+        n_decode = 0
+        while n_decode < B and q_lens[n_decode] == 1:
+            n_decode += 1
         try:
-            recorded = self._graphs.get(self._shape_key(T, B, n_want, max(q_lens))) if self.use_graphs else None
+            recorded = self._graphs.get(self._shape_key(T, B, n_want, max(q_lens), n_decode)) if self.use_graphs else None
             if recorded is not None:
                 # the graph reads the buffers uploaded above at their fixed addresses: nothing else to build
                 logits = self._replay(recorded)
             else:
                 ctx = StepContext(
-                    n_tokens=T, n_seqs=B, n_want=n_want, max_q_len=max(q_lens),
+                    n_tokens=T, n_seqs=B, n_want=n_want, max_q_len=max(q_lens), n_decode=n_decode,
                     # steps of short portions (where keys may be split over CTAs) plan for the longest
                     # sequence there can be, so that their launch shapes do not depend on the lengths
                     max_kv_len=self.max_len if max(q_lens) <= 16 else max(kv_lens),

@@ -339,11 +339,17 @@ class NativeOps:
                         block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor, *,
                         n_seqs: int, max_q_len: int, max_kv_len: int, scale: float,
                         window: Optional[int], page_size: int, allow_split: bool = True,
-                        impl: str = "auto") -> torch.Tensor:
+                        impl: str = "auto", n_tokens: Optional[int] = None,
+                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``impl``: ``"general"`` (CUDA cores, any supported size, both dtypes), ``"mma"`` (tensor
         cores, bfloat16, head_dim 16/32/64/128), ``"decode"`` (tensor cores fed by TMA, bfloat16,
         head_dim 64/128, steps whose requests bring one token or very few) or ``"auto"``
-        (the most specialised kernel that applies)."""
+        (the most specialised kernel that applies).
+
+        ``block_table``, ``q_start`` and ``kv_len`` may be slices that cover only some requests of
+        the step (``q_start`` keeps counting tokens from the start of ``q``); ``n_tokens`` then
+        bounds the rows those requests own (default: all of ``q``), and ``out`` lets several such
+        calls fill one tensor."""
         _cuda_contig(q, "q")
         _cuda_contig(k_pages, "k_pages", q.dtype)
         _cuda_contig(v_pages, "v_pages", q.dtype)
@@ -352,6 +358,12 @@ class NativeOps:
         _need(block_table.is_cuda and block_table.dtype == torch.int32 and block_table.dim() == 2
               and block_table.stride(1) == 1, "block_table must be an int32 matrix with unit column stride")
         T, n_heads, head_dim = q.shape
+        if n_tokens is not None:
+            _need(0 < n_tokens <= T, "n_tokens must lie within q")
+            T = int(n_tokens)
+        if out is not None:
+            _cuda_contig(out, "out", q.dtype)
+            _need(out.shape == q.shape, "out must have q's shape")
         n_kv_heads = k_pages.shape[1]
         self.check_attention_sizes(n_heads, n_kv_heads, head_dim, q.dtype)
         _need(k_pages.shape[2] == page_size and k_pages.shape[3] == head_dim and v_pages.shape == k_pages.shape,
@@ -370,7 +382,8 @@ class NativeOps:
               "power-of-two page size and requests whose rows fit one 16-row tile")
         n_splits = ctypes.c_int(0)
         floats = ctypes.c_longlong(0)
-        out = torch.empty_like(q)
+        if out is None:
+            out = torch.empty_like(q)
         if decode_ok:
             lib = self._lib("attention_decode")
             rc = lib.tl_attention_decode_plan(T, n_seqs, n_heads, n_kv_heads, head_dim, max_q_len, max_kv_len,

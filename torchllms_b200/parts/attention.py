@@ -65,9 +65,22 @@ class PagedAttention(Mixer):
         ops = self.env.ops
         qkv = ops.linear(x, self.wqkv, partials_ok=True)   # rope adds up split-K partial sums
         q = self.position.encode_and_store(qkv, ctx, cache, self.n_heads, self.n_kv_heads, self.head_dim)
-        o = ops.paged_attention(
-            q, cache.k_pages, cache.v_pages, cache.block_table, ctx.q_start, ctx.kv_len,
-            n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, max_kv_len=ctx.max_kv_len,
-            scale=self.scale, window=self.window, page_size=cache.page_size)
+        common = dict(scale=self.scale, window=self.window, page_size=cache.page_size)
+        nd, B = getattr(ctx, "n_decode", 0), ctx.n_seqs
+        if 0 < nd < B and ctx.max_q_len > 1:
+            # decoded tokens beside prompt portions: the requests at the head of the batch bring one
+            # token each and long histories, the rest bring portions; each kind goes to the kernel
+            # shape made for it, both writing into one output
+            o = torch.empty_like(q)
+            ops.paged_attention(q, cache.k_pages, cache.v_pages, cache.block_table[:nd], ctx.q_start[:nd + 1],
+                                ctx.kv_len[:nd], n_seqs=nd, max_q_len=1, max_kv_len=self.env.max_positions,
+                                n_tokens=nd, out=o, **common)
+            ops.paged_attention(q, cache.k_pages, cache.v_pages, cache.block_table[nd:], ctx.q_start[nd:],
+                                ctx.kv_len[nd:], n_seqs=B - nd, max_q_len=ctx.max_q_len, max_kv_len=ctx.max_kv_len,
+                                out=o, allow_split=False, **common)   # (a merge pass would run over the first call's rows too)
+        else:
+            o = ops.paged_attention(
+                q, cache.k_pages, cache.v_pages, cache.block_table, ctx.q_start, ctx.kv_len,
+                n_seqs=B, max_q_len=ctx.max_q_len, max_kv_len=ctx.max_kv_len, **common)
         # the caller's norm adds up split-K partial sums together with the residual
         return ops.linear(o.view(o.shape[0], self.n_heads * self.head_dim), self.wo, partials_ok=True)
