@@ -143,12 +143,17 @@ def test_gemm_tcgen05_few_rows(ops, M, N, K):
 
 
 def test_gemm_tcgen05_rows_do_not_depend_on_the_batch(ops):
-    """A token's product is the same bits alone, padded to 16, or among 64 rows."""
+    """A token's product is the same bits whatever else shares its bucket of rows (1-16, 17-32,
+    33-64: the buckets split K differently, so across them results agree to float32 rounding)."""
     x, w = rand((64, 4096), torch.bfloat16, 50), rand((512, 4096), torch.bfloat16, 51, 0.3)
-    full = ops.gemm_tcgen05(x, w, torch.float32)
+    sixteen = ops.gemm_tcgen05(x[:16].contiguous(), w, torch.float32)
     one = ops.gemm_tcgen05(x[5:6].contiguous(), w, torch.float32)
-    some = ops.gemm_tcgen05(x[:20].contiguous(), w, torch.float32)
-    assert torch.equal(full[..., 5, :], one[..., 0, :]) and torch.equal(full[..., :20, :], some)
+    assert torch.equal(sixteen[..., 5, :], one[..., 0, :])
+    full = ops.gemm_tcgen05(x, w, torch.float32)
+    some = ops.gemm_tcgen05(x[:40].contiguous(), w, torch.float32)
+    assert torch.equal(full[..., :40, :], some)
+    total = lambda t: t.sum(0) if t.dim() == 3 else t
+    torch.testing.assert_close(total(full)[5], total(one)[0], atol=1e-4, rtol=1e-5)
 
 
 # ------------------------------------------------------------------------------------ rope

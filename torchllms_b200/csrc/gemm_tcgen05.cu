@@ -302,17 +302,19 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, in
 
 }  // namespace
 
-// How many K splits the kernel would use for a [N, K] weight: a function of the weight's shape
-// only, so a token's result does not depend on what else is in the batch.
-extern "C" int tl_gemm_tcgen05_splits(int N, int K) {
+// How many K splits the kernel uses for M rows against a [N, K] weight.
+extern "C" int tl_gemm_tcgen05_splits(int M, int N, int K) {
     // Two CTAs fit an SM; all CTAs of a launch should be resident at once (one wave), because a
     // second, partly filled wave streams at a fraction of the bandwidth.  So: as many splits as
-    // keep slabs * splits within 2 * 148, each with at least four stages of work.
+    // keep slabs * splits within 2 * 148, each with at least four stages of work.  (Fewer splits
+    // for the wider token buckets, to save the float32 partial sums' traffic, measured slower: the
+    // CTAs they would save are what keeps the stream busy.)  M is taken so that this can change.
     const int slabs = (N + BP - 1) / BP;
     const int k_blocks = (K + BK - 1) / BK;
     int splits = (2 * 148) / slabs;
     const int most = k_blocks / 4 > 0 ? k_blocks / 4 : 1;
     if (splits > most) splits = most;
+    (void)M;
     if (splits < 1) splits = 1;
     const int per = (k_blocks + splits - 1) / splits;
     return (k_blocks + per - 1) / per;                          // no empty split
@@ -324,7 +326,7 @@ extern "C" int tl_gemm_tcgen05_supports(int M, int N, int K) {
     return (M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0) ? 1 : 0;
 }
 
-// A: [M, K] bf16, W: [N, K] bf16, out: [splits, M, N] with splits = tl_gemm_tcgen05_splits(N, K);
+// A: [M, K] bf16, W: [N, K] bf16, out: [splits, M, N] with splits = tl_gemm_tcgen05_splits(M, N, K);
 // float32 when out_is_f32, else bfloat16 (then splits must be 1).  status: one int the kernel sets
 // to a non-zero code if a wait ran out (it then leaves its output unwritten).
 extern "C" int tl_gemm_tcgen05(const void* A, const void* W, void* out, int out_is_f32, int M, int N, int K,
@@ -332,7 +334,7 @@ extern "C" int tl_gemm_tcgen05(const void* A, const void* W, void* out, int out_
     if (M <= 0 || N <= 0) return TL_OK;
     if (!tl_gemm_tcgen05_supports(M, N, K)) return TL_BAD_SIZE;
     if (!aligned16(A) || !aligned16(W) || !aligned16(out) || status == nullptr) return TL_BAD_ALIGN;
-    if (splits != tl_gemm_tcgen05_splits(N, K)) return TL_BAD_SIZE;
+    if (splits != tl_gemm_tcgen05_splits(M, N, K)) return TL_BAD_SIZE;
     if (!out_is_f32 && splits != 1) return TL_BAD_SIZE;
     const int slabs = (N + BP - 1) / BP;
     const int k_blocks = (K + BK - 1) / BK;

@@ -253,7 +253,7 @@ class NativeOps:
         _need(1 <= M <= 64 and K % 8 == 0 and K >= 8, "gemm_tcgen05 takes 1..64 rows and K a multiple of 8")
         _need(out_dtype in _DT, f"gemm_tcgen05: output dtype {out_dtype} unsupported")
         lib = self._lib("gemm_tcgen05")
-        splits = lib.tl_gemm_tcgen05_splits(N, K)
+        splits = lib.tl_gemm_tcgen05_splits(M, N, K)
         f32 = out_dtype == torch.float32 or splits > 1
         out = torch.empty((splits, M, N), dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
         rc = lib.tl_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(out), 1 if f32 else 0, M, N, K, splits,
