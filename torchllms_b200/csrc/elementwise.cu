@@ -197,6 +197,30 @@ extern "C" int tl_rmsnorm(float* h, const void* delta, int delta_dtype, int delt
     return TL_BAD_DTYPE;
 }
 
+// bfloat16 in and out, hidden a multiple of 8, one plane: eight gates and eight ups per thread (16-byte accesses)
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                     int hidden, long long n_chunks) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int per_row = hidden >> 3;
+    for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < n_chunks; c += (long long)gridDim.x * blockDim.x) {
+        const long long t = c / per_row;
+        const int f = (int)(c - t * per_row) << 3;
+        const uint4 graw = *reinterpret_cast<const uint4*>(in + t * 2 * hidden + f);
+        const uint4 uraw = *reinterpret_cast<const uint4*>(in + t * 2 * hidden + hidden + f);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+        uint4 oraw;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&oraw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 g = __bfloat1622float2(g2[i]), u = __bfloat1622float2(u2[i]);
+            o2[i] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+        }
+        *reinterpret_cast<uint4*>(out + t * hidden + f) = oraw;
+    }
+}
+
 template <typename TI, typename T>
 static int launch_swiglu(const void* in, int splits, void* out, int n_tokens, int hidden, cudaStream_t s) {
     const long long plane = 2LL * n_tokens * hidden;
@@ -219,7 +243,16 @@ extern "C" int tl_swiglu(const void* in, int in_dtype, int splits, void* out, in
     if (splits < 1) return TL_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (in_dtype == TL_F32 && dtype == TL_F32) return launch_swiglu<float, float>(in, splits, out, n_tokens, hidden, s);
-    if (in_dtype == TL_BF16 && dtype == TL_BF16) return launch_swiglu<__nv_bfloat16, __nv_bfloat16>(in, splits, out, n_tokens, hidden, s);
+    if (in_dtype == TL_BF16 && dtype == TL_BF16) {
+        if (splits == 1 && hidden % 8 == 0 && aligned16(in) && aligned16(out)) {
+            const long long n_chunks = (long long)n_tokens * (hidden / 8);
+            long long blocks = (n_chunks + 255) / 256;
+            if (blocks > 148 * 16) blocks = 148 * 16;
+            return (int)tl_launch(swiglu_bf16x8_kernel, dim3((unsigned)blocks), dim3(256), 0, s, (const __nv_bfloat16*)in,
+                                  (__nv_bfloat16*)out, hidden, n_chunks);
+        }
+        return launch_swiglu<__nv_bfloat16, __nv_bfloat16>(in, splits, out, n_tokens, hidden, s);
+    }
     if (in_dtype == TL_F32 && dtype == TL_BF16) return launch_swiglu<float, __nv_bfloat16>(in, splits, out, n_tokens, hidden, s);
     return TL_BAD_DTYPE;
 }
