@@ -77,3 +77,27 @@ def test_temperature_sampling_is_reproducible_and_seeded(tmp_path):
     top1 = a.generate(prompt_token_ids=PROMPTS["A"], max_new_tokens=10, temperature=1.5, top_k=1)
     greedy = a.generate(prompt_token_ids=PROMPTS["A"], max_new_tokens=10)
     assert [r.token_ids for r in top1] == [r.token_ids for r in greedy]
+
+
+@pytest.mark.parametrize("precision", ["float32", "bfloat16"])
+def test_launching_ahead_gives_the_same_tokens_on_the_device(tmp_path, precision):
+    """The scheduler feeds a decode step from the sampler's output on the device before the host
+    has read it.  Same tokens as the step-by-step way, greedy and with a temperature, when requests
+    of different budgets leave one by one (the device-side gather) and when one stops on a token."""
+    from torchllms_b200.inference import LLM
+    cfg, _, page = TINY["B"]
+    folder = tiny_folder(tmp_path, "B")
+    prompts = PROMPTS["B"]
+    kw = dict(precision=precision, max_len=256, max_bsz=4, page_size=page, max_num_batched_tokens=64, prefill_chunk=24)
+    plain_way = LLM(folder, look_ahead=False, **kw)
+    for sampling in (dict(), dict(temperature=0.9, top_k=12, seed=5), dict(temperature=0.7, seed=6)):
+        want = plain_way.generate(prompt_token_ids=prompts, max_new_tokens=40, **sampling)
+        stop = want[0].token_ids[17]
+        ahead = LLM(folder, look_ahead=True, eos_ids=[stop], **kw)
+        stepwise = LLM(folder, look_ahead=False, eos_ids=[stop], **kw)
+        got, ref = (x.generate(prompt_token_ids=prompts, max_new_tokens=40, **sampling) for x in (ahead, stepwise))
+        assert [r.token_ids for r in got] == [r.token_ids for r in ref]
+        assert [r.stop_reason for r in got] == [r.stop_reason for r in ref] and got[0].stop_reason == stop
+        assert ahead.last_stats.launched_ahead > 10 and stepwise.last_stats.launched_ahead == 0
+        ahead.engine.cache.check_invariants()
+        assert ahead.engine.cache.n_live() == 0

@@ -155,6 +155,41 @@ def test_preemption_when_pages_run_out_changes_no_token(folder, plain):
     assert outs[0] == outs[1] and b.stats.preemptions > 0
 
 
+def test_launching_the_next_step_ahead_changes_no_token(folder, plain):
+    """The scheduler launches the next decode step before it has read this one's tokens.  Same
+    tokens as without, through a stop token (a row computed in vain), a budget's end, a late
+    arrival and a full pool; the cache is none the worse at any step."""
+    prompts = [[7] * 30, [9, 8] * 14, [11] * 25, [5, 6, 7]]
+    budgets = [24, 9, 17, 24]
+    free = plain.greedy(prompts[1], 9)
+    eos = (free[4],)                                                  # request 1 stops early on this
+    runs = {}
+    for ahead in (True, False):
+        for pool in (512, 112):
+            s = make_scheduler(folder, pool_tokens=pool, eos=eos, look_ahead=ahead)
+            reqs = [Request(i, list(p), b, SamplingParams(0.7, 20, 3)) for i, (p, b) in enumerate(zip(prompts, budgets))]
+            for r in reqs[:3]:
+                s.add(r)
+            for _ in range(6):
+                s.step()
+                s.engine.cache.check_invariants()
+            s.add(reqs[3])                                            # arrives while the others decode
+            while s.has_work():
+                s.step()
+                s.engine.cache.check_invariants()
+            assert all(r.error is None and r.finished for r in reqs)
+            assert s.engine.cache.n_live() == 0
+            assert s.engine.cache.free_pages() == s.engine.cache.groups[0].allocator.n_pages
+            runs[ahead, pool] = ([r.generated for r in reqs], s.trace, s.stats)
+    for pool in (512, 112):
+        assert runs[True, pool][0] == runs[False, pool][0]
+        assert runs[True, pool][2].launched_ahead > 0 and runs[False, pool][2].launched_ahead == 0
+        # the lost bets are the only extra work: one row for each request that stopped on a token
+        assert runs[False, pool][2].tokens <= runs[True, pool][2].tokens <= runs[False, pool][2].tokens + len(prompts)
+    assert runs[True, 112][2].preemptions > 0
+    assert runs[True, 512][0] == runs[True, 112][0]
+
+
 def test_a_request_that_can_never_fit_gets_an_error_not_a_hang(folder):
     s = make_scheduler(folder, pool_tokens=32)
     reqs = [Request(0, [1] * 40, 5), Request(1, [2] * 10, 5), Request(2, [3] * 20, 30)]

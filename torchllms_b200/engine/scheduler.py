@@ -25,6 +25,8 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, Iterable, List, Optional, Sequence, Set, Tuple
 
+import torch
+
 from ..cache.manager import OutOfPages
 from ..sampling.sampler import Sampler, SamplingParams
 from .step import Engine, StepEntry
@@ -71,13 +73,28 @@ class SchedulerStats:
     decode_steps: int = 0            # steps that held decode tokens only
     decode_step_tokens: int = 0
     decode_seconds: float = 0.0      # wall time of those steps, sampling and its read-back included
+    launched_ahead: int = 0          # decode steps put on the device before the step before them was read
+
+
+@dataclass
+class _Launched:
+    """A step that is on the device."""
+
+    planned: List[Tuple[Request, int]]
+    samplers: List[Request]               # the requests that get a token from it, in row order
+    on_device: Optional[torch.Tensor]     # their tokens, on the device
+    tokens: object                        # the same on their way to the host (None: nobody samples)
+    pure_decode: bool
 
 
 class Scheduler:
     def __init__(self, engine: Engine, sampler: Sampler, *, max_num_seqs: Optional[int] = None,
                  max_num_batched_tokens: int = 2048, prefill_chunk: Optional[int] = None,
-                 eos_ids: Iterable[int] = ()):
+                 eos_ids: Iterable[int] = (), look_ahead: bool = True):
         self.engine = engine
+        self.look_ahead = bool(look_ahead)
+        self._in_flight: Optional[_Launched] = None   # a step on the device whose tokens are not read yet
+        self._last_read = 0.0                          # when the last step's tokens reached the host
         self.sampler = sampler
         self.max_num_seqs = min(int(max_num_seqs or engine.cache.max_num_seqs), engine.cache.max_num_seqs)
         self.max_num_batched_tokens = min(int(max_num_batched_tokens), engine.max_step_tokens)
@@ -185,40 +202,40 @@ class Scheduler:
         return planned
 
     def step(self) -> List[Request]:
-        """Plan, run and sample one step; returns the requests that finished in it."""
-        before = [r for r in self.running]
-        planned = self.plan()
-        finished_now = [r for r in before if r.finished and r not in self.running]
-        if not planned:
-            if not finished_now and self.has_work() and not self.running:
-                # nothing running and the head of the queue cannot start: it can never fit
-                r = self.waiting.popleft()
-                r.finished, r.error = True, "request does not fit the cache pool"
-                finished_now.append(r)
-            return finished_now
-        entries, samplers = [], []
-        for r, n in planned:
-            toks = r.span(r.n_fed, n)
-            completes = r.n_fed + n == len(r.prompt) + len(r.generated)
-            entries.append(StepEntry(r.handle, toks, [n - 1] if completes else []))
-            if completes:
-                samplers.append(r)
-        pure_decode = all(n == 1 and r.n_fed > 0 and r.generated for r, n in planned)
-        t0 = time.perf_counter()
-        logits = self.engine.step(entries)
-        self.trace.append([(r.index, n) for r, n in planned])
-        self.stats.steps += 1
-        for r, n in planned:
-            self.stats.tokens += n
-            if n == 1 and r.n_fed > 0 and r.n_fed + 1 == len(r.prompt) + len(r.generated) and r.generated:
-                self.stats.decode_tokens += 1
-            else:
-                self.stats.prefill_tokens += n
-            r.n_fed += n
-        if samplers:
-            new = self.sampler.sample(logits, [r.sampling for r in samplers], [r.index for r in samplers],
-                                      [len(r.generated) for r in samplers])
-            for r, tok in zip(samplers, new):
+        """Complete one step (plan, run, sample, read back) and return the requests that finished
+        in it.
+
+        With ``look_ahead``, the next decode step is put on the device before this step's tokens
+        are read: its token ids go from the sampler's output to the model's input on the device,
+        so the device does not wait while the host reads tokens and books them.  That next step is
+        a bet that no request ends on a stop token: a request that does has one row computed in
+        vain (its pages are freed as usual; no other row depends on it).  Ending on the budget is
+        known beforehand and is no bet.  A call still completes exactly one step."""
+        # a step's time runs from this call's start, or, if it was launched during the call before,
+        # from the moment that call had its tokens (the device went straight on to this one)
+        started = self._last_read if self._in_flight is not None else time.perf_counter()
+        finished_now: List[Request] = []
+        current, self._in_flight = self._in_flight, None
+        if current is None:
+            before = [r for r in self.running]
+            planned = self.plan()
+            finished_now = [r for r in before if r.finished and r not in self.running]
+            if not planned:
+                if not finished_now and self.has_work() and not self.running:
+                    # nothing running and the head of the queue cannot start: it can never fit
+                    r = self.waiting.popleft()
+                    r.finished, r.error = True, "request does not fit the cache pool"
+                    finished_now.append(r)
+                return finished_now
+            current = self._launch(planned)
+        if self.look_ahead and current.tokens is not None:
+            self._in_flight = self._launch_ahead(current)
+        if current.tokens is not None:
+            new = self.sampler.finish(current.tokens)
+            self._last_read = time.perf_counter()
+            for r, tok in zip(current.samplers, new):
+                if r.finished:
+                    continue                    # it ended a step ago; this row was the lost bet
                 r.generated.append(int(tok))
                 if int(tok) in self.eos_set:
                     r.stop_reason = int(tok)
@@ -230,11 +247,69 @@ class Scheduler:
                     r.handle = None
                     self.running.remove(r)
                     finished_now.append(r)
-        if pure_decode:
+        if self._in_flight is not None and all(r.finished for r in self._in_flight.samplers):
+            self._in_flight = None              # nobody is left to read it
+        if current.pure_decode:
             self.stats.decode_steps += 1
-            self.stats.decode_step_tokens += len(planned)
-            self.stats.decode_seconds += time.perf_counter() - t0
+            self.stats.decode_step_tokens += len(current.planned)
+            self.stats.decode_seconds += time.perf_counter() - started
         return finished_now
+
+    def _launch(self, planned: List[Tuple[Request, int]], device_tokens=None, rows=None, ahead: int = 0) -> "_Launched":
+        """Put a planned step and its sampling on the device; nothing here waits for the device.
+        ``ahead`` is 1 when the requests' last tokens are not on the host yet: they are rows
+        ``rows`` of ``device_tokens``."""
+        shape, tokens, samplers = [], [], []
+        for r, n in planned:
+            completes = r.n_fed + n == len(r.prompt) + len(r.generated) + ahead
+            shape.append((r.handle, n, [n - 1] if completes else []))
+            if completes:
+                samplers.append(r)
+            if device_tokens is None:
+                tokens.extend(r.span(r.n_fed, n))
+        pure_decode = all(n == 1 and r.n_fed > 0 and (r.generated or ahead) for r, n in planned)
+        prepared = self.engine.prepare(shape)       # OutOfPages leaves everything as it was
+        if device_tokens is None:
+            logits = self.engine.run_prepared(prepared, tokens)
+        else:
+            logits = self.engine.run_prepared(prepared, device_tokens, rows)
+        self.trace.append([(r.index, n) for r, n in planned])
+        self.stats.steps += 1
+        for r, n in planned:
+            self.stats.tokens += n
+            if (n == 1 and r.n_fed > 0 and r.n_fed + 1 == len(r.prompt) + len(r.generated) + ahead
+                    and (r.generated or ahead)):
+                self.stats.decode_tokens += 1
+            else:
+                self.stats.prefill_tokens += n
+            r.n_fed += n
+        pending = on_device = None
+        if samplers:
+            on_device = self.sampler.launch(logits, [r.sampling for r in samplers], [r.index for r in samplers],
+                                            [len(r.generated) + ahead for r in samplers])
+            pending = self.sampler.read_back(on_device)
+        return _Launched(planned, samplers, on_device, pending, pure_decode)
+
+    def _launch_ahead(self, current: "_Launched") -> Optional["_Launched"]:
+        """The decode step after ``current`` for the requests that will still run if none of them
+        stops on a token, launched before ``current``'s tokens are known; ``None`` when the next step
+        needs a fresh plan (somebody waits for admission, a prompt is still being fed, pages ran out)."""
+        if self.waiting and len(self.running) < self.max_num_seqs:
+            return None
+        place = {id(r): i for i, r in enumerate(current.samplers)}
+        if any(id(r) not in place for r in self.running):
+            return None
+        # whoever has room for another token after the one being sampled now
+        stay = [r for r in self.running if len(r.generated) + 1 < r.budget]
+        if not stay or len(stay) > self.max_num_batched_tokens:
+            return None
+        try:
+            launched = self._launch([(r, 1) for r in stay], device_tokens=current.on_device,
+                                    rows=[place[id(r)] for r in stay], ahead=1)
+        except OutOfPages:
+            return None                         # the ordinary plan decides whom to pre-empt
+        self.stats.launched_ahead += 1
+        return launched
 
     def run(self, requests: Sequence[Request]) -> Sequence[Request]:
         """Run the requests to completion; they are finished in place."""

@@ -44,6 +44,18 @@ class StepEntry:
 
 
 @dataclass
+class PreparedStep:
+    """What :meth:`Engine.prepare` decided: everything of a step but the token values."""
+
+    handles: List[int]
+    q_lens: List[int]
+    starts: List[int]        # each request's length before the step
+    kv_lens: List[int]
+    slots: List[int]
+    n_want: int
+
+
+@dataclass
 class StepContext:
     """What the parts see of a step (device tensors are views of one uploaded buffer)."""
 
@@ -68,30 +80,45 @@ class StepContext:
 
 
 class _StepBuffers:
-    """Fixed-layout pinned host buffer and its device twin."""
+    """A pinned host buffer and its device twin.  A step's index data lie back to back, so that
+    one copy of just the used part uploads them.  Where a section lies depends only on the step's
+    numbers of tokens and requests: a recorded graph (there is one per such pair at least) finds
+    its inputs at fixed addresses."""
+
+    PER_TOKEN = ("token_ids", "positions", "seq_of_token", "want_rows", "token_src")   # token_ids stays first
+    PER_SEQ = ("kv_len", "state_slot", "fresh")
 
     def __init__(self, cache: CacheManager, max_tokens: int, device: torch.device):
         B, T, NB, G = cache.max_num_seqs, max_tokens, cache.max_blocks, len(cache.groups)
         self.T, self.B, self.NB, self.G = T, B, NB, G
-        off = 0
-        self.sections = {}
-        for name, n in (("token_ids", T), ("positions", T), ("seq_of_token", T), ("want_rows", T),
-                        ("q_start", B + 1), ("kv_len", B), ("state_slot", B), ("fresh", B)):
-            self.sections[name] = (off, n)
-            off += n
-        for g in range(G):
-            self.sections[f"slot_mapping{g}"] = (off, T)
-            off += T
-        for g in range(G):
-            self.sections[f"block_table{g}"] = (off, B * NB)
-            off += B * NB
-        self.total = off
+        self._layouts = {}
+        self.sections, self.used = self._layout(T, B)
+        self.total = self.used
         pin = device.type == "cuda"
         self.host = torch.zeros(self.total, dtype=torch.int32, pin_memory=pin)
         self.host_np = self.host.numpy()
         self.dev = torch.zeros(self.total, dtype=torch.int32, device=device)
         self.copied = torch.cuda.Event() if pin else None
         self._pending = False
+        self.uploaded_bytes = 0
+
+    def _layout(self, n_tokens: int, n_seqs: int):
+        got = self._layouts.get((n_tokens, n_seqs))
+        if got is None:
+            sections, off = {}, 0
+            sizes = [(name, n_tokens) for name in self.PER_TOKEN]
+            sizes += [(f"slot_mapping{g}", n_tokens) for g in range(self.G)]
+            sizes += [("q_start", n_seqs + 1)] + [(name, n_seqs) for name in self.PER_SEQ]
+            sizes += [(f"block_table{g}", n_seqs * self.NB) for g in range(self.G)]
+            for name, n in sizes:
+                sections[name] = (off, n)
+                off += -(-n // 4) * 4                     # every section starts on 16 bytes
+            got = self._layouts[n_tokens, n_seqs] = (sections, off)
+        return got
+
+    def lay_out(self, n_tokens: int, n_seqs: int) -> None:
+        """Place the sections for a step of this many tokens and requests."""
+        self.sections, self.used = self._layout(n_tokens, n_seqs)
 
     def host_view(self, name: str) -> np.ndarray:
         off, n = self.sections[name]
@@ -106,14 +133,12 @@ class _StepBuffers:
             self.copied.synchronize()
         self._pending = False
 
-    def upload(self, n_seqs: int) -> None:
-        # everything up to the last block-table row in use, in one copy
-        if self.G:
-            off, _ = self.sections[f"block_table{self.G - 1}"]
-            end = off + n_seqs * self.NB
-        else:
-            end = self.sections["fresh"][0] + self.B
-        self.dev[:end].copy_(self.host[:end], non_blocking=True)
+    def upload(self, skip_tokens: bool = False) -> None:
+        # the sections in use, in one copy; the token ids (the first section) stay behind when the
+        # device has them already
+        start, end = (self.sections["positions"][0] if skip_tokens else 0), self.used
+        self.uploaded_bytes = 4 * (end - start)
+        self.dev[start:end].copy_(self.host[start:end], non_blocking=True)
         if self.copied is not None:
             self.copied.record()
             self._pending = True
@@ -226,48 +251,55 @@ class Engine:
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run the entries' tokens as one batch.  Returns float32 logits
         ``[n_wanted, vocab]`` on the device, rows in the order of the entries and
-        of each entry's ``want``; ``None`` when nothing was wanted.
+        of each entry's ``want``; ``None`` when nothing was wanted.  (With CUDA graphs
+        on, the tensor is a buffer the next step of the same shape writes again.)
 
         Raises :class:`~torchllms_b200.cache.manager.OutOfPages` (nothing changed)
         when the pool cannot hold the new tokens."""
         if not entries:
             return None
-        q_lens = [len(e.tokens) for e in entries]
-        T, B = sum(q_lens), len(entries)
-        if min(q_lens) <= 0:
+        prepared = self.prepare([(e.handle, len(e.tokens), e.want) for e in entries])
+        return self.run_prepared(prepared, [t for e in entries for t in e.tokens])
+
+    def prepare(self, shape: Sequence[Tuple[int, int, Optional[Sequence[int]]]]) -> "PreparedStep":
+        """The host half of a step that does not need the token values: ``shape`` holds
+        ``(handle, n_tokens, want)`` per request.  Grows the cache and packs positions, cache
+        slots, block tables and wanted rows into the pinned buffer.  A scheduler may call this for
+        the next step while the device still runs the current one, then :meth:`run_prepared` once
+        the tokens are known, or :meth:`discard` if the step will not happen after all.  Only one
+        prepared step can exist at a time."""
+        handles = [h for h, _n, _w in shape]
+        q_lens = [int(n) for _h, n, _w in shape]
+        T, B = sum(q_lens), len(shape)
+        if B == 0 or min(q_lens) <= 0:
             raise StepError("every entry of a step must bring at least one token")
         if T > self.max_step_tokens:
             raise StepError(f"a step may bring at most {self.max_step_tokens} tokens, got {T}")
         if B > self.cache.max_num_seqs:
             raise StepError(f"a step may hold at most {self.cache.max_num_seqs} requests, got {B}")
-        flat = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=T)
-        if flat.min() < 0 or flat.max() >= self.vocab_size:
-            bad = int(flat[(flat < 0) | (flat >= self.vocab_size)][0])
-            raise StepError(f"token id {bad} is outside the vocabulary (0..{self.vocab_size - 1})")
         want_rows: List[int] = []
         base = 0
-        for e, n in zip(entries, q_lens):
-            want = [n - 1] if e.want is None else list(e.want)
-            for w in want:
+        for (h, _n, want), n in zip(shape, q_lens):
+            for w in ([n - 1] if want is None else want):
                 if not 0 <= w < n:
-                    raise StepError(f"request {e.handle}: wanted place {w} is outside its {n} tokens")
+                    raise StepError(f"request {h}: wanted place {w} is outside its {n} tokens")
                 want_rows.append(base + w)
             base += n
 
         cache = self.cache
-        starts = cache.extend_many([(e.handle, n) for e, n in zip(entries, q_lens)])  # may raise OutOfPages
+        starts = cache.extend_many(list(zip(handles, q_lens)))  # may raise OutOfPages
         buf = self._buf
         buf.wait_host_free()
+        buf.lay_out(T, B)
         lens = np.asarray(q_lens, dtype=np.int64)
         first = np.asarray(starts, dtype=np.int64)
         q_start = np.zeros(B + 1, dtype=np.int64)
         np.cumsum(lens, out=q_start[1:])
         kv_lens = (first + lens).tolist()
-        slots = [cache.slot(e.handle) for e in entries]
+        slots = [cache.slot(h) for h in handles]
         # per token: which request it belongs to and its absolute position (no loop over requests)
         seq_of = np.repeat(np.arange(B, dtype=np.int64), lens)
         pos_all = np.arange(T, dtype=np.int64) - q_start[seq_of] + first[seq_of]
-        buf.host_view("token_ids")[:T] = flat
         buf.host_view("positions")[:T] = pos_all
         buf.host_view("seq_of_token")[:T] = seq_of
         buf.host_view("q_start")[:B + 1] = q_start
@@ -280,29 +312,63 @@ class Engine:
             rows = cache.block_table_rows(g, slots)                       # [B, max_blocks]
             pages = rows[seq_of, pos_all // page]
             if (pages < 0).any():
-                for e, s0 in zip(entries, starts):
-                    cache.truncate(e.handle, s0)
+                for h, s0 in zip(handles, starts):
+                    cache.truncate(h, s0)
                 raise StepError("a token of this step falls on a page that was already given back")
             buf.host_view(f"slot_mapping{g}")[:T] = pages * page + pos_all % page
             buf.host_view(f"block_table{g}")[:B * buf.NB].reshape(B, buf.NB)[:] = rows
-        buf.upload(B)
+        return PreparedStep(handles, q_lens, starts, kv_lens, slots, len(want_rows))
 
-        decode_only = max(q_lens) == 1
-        n_want = len(want_rows)
-        n_decode = 0
-        while n_decode < B and q_lens[n_decode] == 1:
-            n_decode += 1
+    def discard(self, prepared: "PreparedStep") -> None:
+        """Undo :meth:`prepare`: the cache is as it was before (requests released meanwhile are skipped)."""
+        live = set(self.cache.live_handles())
+        for h, s0 in zip(prepared.handles, prepared.starts):
+            if h in live:
+                self.cache.truncate(h, s0)
+
+    def run_prepared(self, prepared: "PreparedStep", tokens, rows: Optional[Sequence[int]] = None) -> Optional[torch.Tensor]:
+        """The device half: upload the packed buffer with these token ids and run the model.
+        ``tokens`` is a list of ids, or an int32 tensor on the device (ids the sampler has just
+        written and the host has not seen yet: they are taken as they are); with ``rows``, the
+        step's ids are ``tokens[rows]``, gathered on the device.  Nothing here waits for the device."""
+        q_lens, starts, kv_lens, slots = prepared.q_lens, prepared.starts, prepared.kv_lens, prepared.slots
+        handles = prepared.handles
+        T, B, n_want = sum(q_lens), len(q_lens), prepared.n_want
+        cache, buf = self.cache, self._buf
+        buf.lay_out(T, B)
         try:
-            recorded = self._graphs.get(self._shape_key(T, B, n_want, max(q_lens), n_decode)) if self.use_graphs else None
+            if isinstance(tokens, torch.Tensor):
+                if tokens.dtype != torch.int32 or tokens.device != buf.dev.device or tokens.dim() != 1:
+                    raise StepError("token ids on the device must be an int32 vector on the engine's device")
+                rows = list(range(T)) if rows is None else list(rows)
+                if len(rows) != T or min(rows) < 0 or max(rows) >= tokens.shape[0]:
+                    raise StepError(f"the prepared step holds {T} tokens; rows {rows} of {tokens.shape[0]} ids do not give them")
+                buf.host_view("token_src")[:T] = rows      # the gather's index rides in the step's one upload
+                buf.upload(skip_tokens=True)
+                torch.index_select(tokens, 0, buf.dev_view("token_src", T), out=buf.dev_view("token_ids", T))
+            elif len(tokens) != T:
+                raise StepError(f"the prepared step holds {T} tokens, got {len(tokens)}")
+            else:
+                flat = np.asarray(tokens, dtype=np.int64)
+                if flat.min() < 0 or flat.max() >= self.vocab_size:
+                    bad = int(flat[(flat < 0) | (flat >= self.vocab_size)][0])
+                    raise StepError(f"token id {bad} is outside the vocabulary (0..{self.vocab_size - 1})")
+                buf.host_view("token_ids")[:T] = flat
+                buf.upload()
+            max_q = max(q_lens)
+            n_decode = 0
+            while n_decode < B and q_lens[n_decode] == 1:
+                n_decode += 1
+            recorded = self._graphs.get(self._shape_key(T, B, n_want, max_q, n_decode)) if self.use_graphs else None
             if recorded is not None:
                 # the graph reads the buffers uploaded above at their fixed addresses: nothing else to build
                 logits = self._replay(recorded)
             else:
                 ctx = StepContext(
-                    n_tokens=T, n_seqs=B, n_want=n_want, max_q_len=max(q_lens), n_decode=n_decode,
+                    n_tokens=T, n_seqs=B, n_want=n_want, max_q_len=max_q, n_decode=n_decode,
                     # steps of short portions (where keys may be split over CTAs) plan for the longest
                     # sequence there can be, so that their launch shapes do not depend on the lengths
-                    max_kv_len=self.max_len if max(q_lens) <= 16 else max(kv_lens),
+                    max_kv_len=self.max_len if max_q <= 16 else max(kv_lens),
                     token_ids=buf.dev_view("token_ids", T), positions=buf.dev_view("positions", T),
                     seq_of_token=buf.dev_view("seq_of_token", T), q_start=buf.dev_view("q_start", B + 1),
                     kv_len=buf.dev_view("kv_len", B), state_slot=buf.dev_view("state_slot", B),
@@ -316,12 +382,12 @@ class Engine:
                 else:
                     logits = self.model.forward(ctx, views)
         except BaseException:
-            for e, s in zip(entries, starts):  # leave the cache as the step found it
-                cache.truncate(e.handle, s)
+            for h, s0 in zip(handles, starts):  # leave the cache as the step found it
+                cache.truncate(h, s0)
             raise
         if self._has_window:
-            for e in entries:
-                cache.pass_window(e.handle)
+            for h in handles:
+                cache.pass_window(h)
         self.steps_run += 1
         self.tokens_run += T
         return logits

@@ -58,6 +58,7 @@ class LLM:
         max_num_batched_tokens: int = 2048,
         prefill_chunk: Optional[int] = None,
         seed: int = 0,
+        look_ahead: bool = True,
         config=None,
         random_seed: Optional[int] = None,
         ops=None,
@@ -99,6 +100,7 @@ class LLM:
                              max_len=self.max_len, max_step_tokens=max(max_num_batched_tokens, 1))
         self.sampler = Sampler(ops, self.model.device)
         self.max_num_batched_tokens = max_num_batched_tokens
+        self.look_ahead = bool(look_ahead)      # launch a decode step before the one before it is read back
         self.prefill_chunk = prefill_chunk
 
         self.template: Optional[ChatTemplate] = get_template(template_config) if template_config else None
@@ -179,7 +181,7 @@ class LLM:
         scheduler = Scheduler(self.engine, self.sampler,
                               max_num_seqs=min(batch_size, self.max_bsz) if batch_size else self.max_bsz,
                               max_num_batched_tokens=self.max_num_batched_tokens,
-                              prefill_chunk=self.prefill_chunk, eos_ids=self.eos_set)
+                              prefill_chunk=self.prefill_chunk, eos_ids=self.eos_set, look_ahead=self.look_ahead)
         try:
             scheduler.run(requests)
         finally:

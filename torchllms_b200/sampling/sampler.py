@@ -43,6 +43,15 @@ class SamplingParams:
     seed: int = 0
 
 
+class PendingTokens:
+    """Sampled tokens on their way to the host."""
+
+    __slots__ = ("host", "done")
+
+    def __init__(self, host: torch.Tensor, done):
+        self.host, self.done = host, done
+
+
 class Sampler:
     def __init__(self, ops, device):
         self.ops = ops
@@ -51,23 +60,51 @@ class Sampler:
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], requests: Sequence[int],
                token_indices: Sequence[int]) -> List[int]:
         """One token per row of ``logits`` ``[n, vocab]`` (float32, on the device)."""
+        return self.finish(self.launch(logits, params, requests, token_indices))
+
+    def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], requests: Sequence[int],
+               token_indices: Sequence[int]) -> torch.Tensor:
+        """Start sampling and return the tokens as a device tensor without waiting for them:
+        the caller may do host work before :meth:`finish` reads them back."""
         n = logits.shape[0]
         assert n == len(params) == len(requests) == len(token_indices)
         if all(not p.temperature > 0 for p in params):
-            return self._checked(self.ops.sample(logits).tolist())
+            return self.ops.sample(logits)
         packed = np.zeros((n, 4), dtype=np.int32)  # temperature bits | top_k | key low | key high
         packed[:, 0] = np.asarray([p.temperature for p in params], dtype=np.float32).view(np.int32)
         packed[:, 1] = [int(p.top_k or 0) for p in params]
         keys = np.asarray([row_key(p.seed, r, t) for p, r, t in zip(params, requests, token_indices)], dtype=np.uint64)
         packed[:, 2:4] = keys.view(np.int32).reshape(n, 2)
-        dev = torch.from_numpy(packed).to(self.device)
+        host = torch.from_numpy(packed)
+        if self.device.type == "cuda":
+            host = host.pin_memory()        # a copy from pageable memory would wait for the device
+        dev = host.to(self.device, non_blocking=True)
         temperature = dev[:, 0].contiguous().view(torch.float32)
         top_k = dev[:, 1].contiguous()
         row_keys = dev[:, 2:4].contiguous().view(torch.int64).reshape(n)
-        return self._checked(self.ops.sample(logits, temperature, top_k, row_keys).tolist())
+        return self.ops.sample(logits, temperature, top_k, row_keys)
+
+    def read_back(self, tokens: torch.Tensor) -> "PendingTokens":
+        """Start copying the tokens of :meth:`launch` to the host.  Work queued on the device after
+        this call does not delay :meth:`finish`, which waits for this copy alone."""
+        if tokens.device.type != "cuda":
+            return PendingTokens(tokens, None)
+        host = torch.empty(tokens.shape, dtype=tokens.dtype, pin_memory=True)
+        host.copy_(tokens, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return PendingTokens(host, done)
+
+    def finish(self, tokens) -> List[int]:
+        """The tokens of :meth:`launch` (or of :meth:`read_back`) on the host; this waits for them."""
+        if isinstance(tokens, PendingTokens):
+            if tokens.done is not None:
+                tokens.done.synchronize()
+            return self._checked(tokens.host.tolist())
+        return self._checked(tokens.tolist())
 
     def _checked(self, tokens: List[int]) -> List[int]:
-        # the read-back above synchronised the stream: a kernel that gave up a wait has said so by now
+        # the device has finished everything up to the read-back: a kernel that gave up a wait has said so by now
         check = getattr(self.ops, "check_status", None)
         if check is not None:
             check()
