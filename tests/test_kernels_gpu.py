@@ -239,6 +239,9 @@ ATTN_CASES = [
     ([900, 130], [2, 1], 16, 2, 64, 32, 77),              # two tokens of a group of 8 behind a window, pages of 32
     ([300, 5], [1, 1], 4, 4, 128, 128, None),             # pages larger than a tile
     ([1500, 1499, 3], [1, 1, 1], 32, 8, 128, 16, 512),    # the 8B layout decoding behind a window
+    ([700, 45], [3, 4], 32, 8, 128, 16, None),            # 16 rows to a tile (four tokens of a group of four), head_dim 128
+    ([400, 33, 130], [1, 1, 1], 16, 1, 128, 16, None),    # decoding with a group of 16, head_dim 128
+    ([260, 19], [2, 1], 12, 2, 64, 8, 50),                # group of 6: two tokens make 12 rows, behind a window
 ]
 
 

@@ -10,9 +10,16 @@
 // A CTA serves one (request, kv head, key split).  Warp 4 is the producer: for every 64-key tile it
 // looks up the pages, and issues cp.async.bulk.tensor copies (no multicast) of [page rows x 64
 // elements] boxes into 128-byte-swizzled shared memory, completing on an mbarrier per stage.
-// Warps 0-3 share the 16 rows and each takes 16 keys of every tile; they hand a stage back through a
+// Warps 0-3 share the rows and each takes 16 keys of every tile; they hand a stage back through a
 // second mbarrier.  No CTA-wide barrier is used until the four partial results are merged.  Key
 // splits over CTAs write float32 partials that merge_partials_kernel combines.
+//
+// The products are taken transposed: scores^T = K Q^T and out^T = V^T P^T, so that the 16 rows of
+// a tensor-core tile are keys (or value columns), all of them real, and the few query rows (four
+// for a group of four heads) sit in the 8-wide direction.  With the queries as the 16 rows, three
+// quarters of every product were padding, and instruction issue, not memory, set the pace.  The
+// probabilities change sides between the two products (result columns -> operand columns),
+// which is one movmatrix per 8 x 8 block.
 // Every mbarrier wait is bounded in time; on a time-out the CTA records a code in the status
 // word, writes nothing and returns.
 #include "common.cuh"
@@ -111,16 +118,25 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 // byte offset of (row, 16-byte chunk c of a 128-byte row) inside a 128-byte-swizzled [rows x 128 B] tile
 __device__ __forceinline__ unsigned swz(int row, int c) { return (unsigned)(row * 128 + ((c ^ (row & 7)) << 4)); }
 
-template <int HD, int STAGES>
-__global__ void __launch_bounds__(NTHREADS, 3) attention_decode_kernel(const __grid_constant__ CUtensorMap map_k,
-                                                                    const __grid_constant__ CUtensorMap map_v,
-                                                                    const DecodeParams p) {
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {     // 8 x 8 bfloat16 block, transposed across the warp
+    unsigned d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+// NT: 8-row blocks of query rows (1: up to 8 rows, 2: up to 16)
+template <int HD, int STAGES, int NT>
+__global__ void __launch_bounds__(NTHREADS, NT == 1 ? 3 : 2) attention_decode_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                                  const __grid_constant__ CUtensorMap map_v,
+                                                                                  const DecodeParams p) {
     constexpr int HALVES = HD / 64;                     // 64-element (128-byte) column blocks of a row
     constexpr unsigned HALF_BYTES = BN * 128;           // one [64 keys x 128 B] block
     constexpr unsigned KV_BYTES = HALVES * HALF_BYTES;  // K (or V) of a tile
     constexpr unsigned STAGE_BYTES = 2 * KV_BYTES;
     constexpr int QPITCH = HD + 8;
     constexpr int KSTEPS = HD / 16;
+    constexpr int NROWS = 8 * NT;
+    constexpr int OPITCH = HD + 4;                      // of the merge buffer: rows two apart fall on different banks
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(tiles + STAGES * STAGE_BYTES);   // [16][QPITCH]
@@ -208,10 +224,17 @@ __global__ void __launch_bounds__(NTHREADS, 3) attention_decode_kernel(const __g
     }
     __syncthreads();
 
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    float o[HD / 8][4];
+    // this thread's two query rows of every 8-row block are 2t and 2t + 1: of the scores^T tile it
+    // holds keys g and g + 8 for them, of the out^T tile value columns g and g + 8
+    float m[NT][2], l[NT][2];
+    float o[NT][KSTEPS][4];
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int nt = 0; nt < NT; ++nt) {
+        m[nt][0] = m[nt][1] = -INFINITY;
+        l[nt][0] = l[nt][1] = 0.f;
+#pragma unroll
+        for (int i = 0; i < KSTEPS; ++i) o[nt][i][0] = o[nt][i][1] = o[nt][i][2] = o[nt][i][3] = 0.f;
+    }
     const int g = lane >> 2, t = lane & 3;
 
     if (warp == NCW) {
@@ -227,29 +250,41 @@ __global__ void __launch_bounds__(NTHREADS, 3) attention_decode_kernel(const __g
             }
         }
     } else {
-        // ---- consumers: the same 16 rows, 16 keys of every tile each
-        int qpos[2];
+        // ---- consumers: the same rows, 16 keys of every tile each
+        int qpos[NT][2];
+        int qmax = -1, qmin = INT_MAX;
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int rr = g + 8 * i;
-            const int tok = tok0 + rr / ng;
-            qpos[i] = (rr < p.tpw * ng && tok < ql) ? qpos_base + tok : -1;
-        }
-        const int warp_qmax = __reduce_max_sync(0xffffffffu, max(qpos[0], qpos[1]));
-        const int warp_qmin = __reduce_min_sync(0xffffffffu, min(qpos[0] < 0 ? INT_MAX : qpos[0], qpos[1] < 0 ? INT_MAX : qpos[1]));
-        unsigned qf[KSTEPS][4];
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int rr = nt * 8 + 2 * t + j;
+                const int tok = tok0 + rr / ng;
+                const int qp = (rr < p.tpw * ng && tok < ql) ? qpos_base + tok : -1;
+                qpos[nt][j] = qp;
+                qmax = max(qmax, qp);
+                if (qp >= 0) qmin = min(qmin, qp);
+            }
+        const int warp_qmax = __reduce_max_sync(0xffffffffu, qmax);
+        const int warp_qmin = __reduce_min_sync(0xffffffffu, qmin);
+        // Q^T as the 8-wide operand: this thread holds columns 2t, 2t + 1 (and + 8) of row g
+        unsigned qf[NT][KSTEPS][2];
         const int mi = lane >> 3;
 #pragma unroll
-        for (int kd = 0; kd < KSTEPS; ++kd) {
-            const int row = (lane & 7) + ((mi & 1) ? 8 : 0);
-            ldmatrix_x4(qf[kd], smem_u32(Qs + row * QPITCH + kd * 16 + ((mi & 2) ? 8 : 0)));
-        }
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int kd2 = 0; kd2 < KSTEPS / 2; ++kd2) {
+                unsigned r[4];
+                ldmatrix_x4(r, smem_u32(Qs + (nt * 8 + (lane & 7)) * QPITCH + (kd2 * 4 + mi) * 8));
+                qf[nt][2 * kd2][0] = r[0]; qf[nt][2 * kd2][1] = r[1];
+                qf[nt][2 * kd2 + 1][0] = r[2]; qf[nt][2 * kd2 + 1][1] = r[3];
+            }
         const int key_off = warp * 16;
-        // this lane's row and first chunk inside a tile, for the K fragments and for the V fragments
-        const int k_row = key_off + (lane & 7) + ((mi & 2) ? 8 : 0);
-        const int v_row = key_off + (lane & 7) + ((mi & 1) ? 8 : 0);
-        const unsigned k_lane_off = swz(k_row, mi & 1);
-        const unsigned v_lane_off = swz(v_row, (mi & 2) ? 1 : 0);
+        // this lane's row and first chunk inside a tile: K as the 16-row operand [keys x 16 columns],
+        // V through a transposing load as [16 columns x keys]
+        const int k_row = key_off + (lane & 7) + ((mi & 1) ? 8 : 0);
+        const int v_row = key_off + (lane & 7) + ((mi & 2) ? 8 : 0);
+        const unsigned k_lane_off = swz(k_row, (mi & 2) ? 1 : 0);
+        const unsigned v_lane_off = swz(v_row, mi & 1);
         bool ok = true;
         for (int it = 0; it < n_tiles; ++it) {
             const int s = it % STAGES;
@@ -261,81 +296,80 @@ __global__ void __launch_bounds__(NTHREADS, 3) attention_decode_kernel(const __g
             if (share_lo <= warp_qmax && share_lo + 16 > k_lo) {
                 const unsigned kt = smem_u32(tiles + s * STAGE_BYTES);
                 // rows are 128 bytes and tiles 1024-byte aligned, so bits 4-6 of a row's address are the
-                // swizzled chunk: xor-ing a constant chunk number in is all it takes to move along K
+                // swizzled chunk: xor-ing a constant chunk number in is all it takes to move along a row
                 const unsigned ka = kt + k_lane_off, va = kt + KV_BYTES + v_lane_off;
-                float sc[2][4];
+                float sc[NT][4];
 #pragma unroll
-                for (int i = 0; i < 2; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+                for (int nt = 0; nt < NT; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
 #pragma unroll
                 for (int kd = 0; kd < KSTEPS; ++kd) {
                     unsigned kf[4];
                     ldmatrix_x4(kf, (ka ^ (unsigned)(((kd * 2) & 7) << 4)) + (kd / 4) * HALF_BYTES);
-                    mma_bf16(sc[0], qf[kd], kf[0], kf[1]);
-                    mma_bf16(sc[1], qf[kd], kf[2], kf[3]);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) mma_bf16(sc[nt], kf, qf[nt][kd][0], qf[nt][kd][1]);
                 }
-                float mx[2] = {-INFINITY, -INFINITY};
                 const bool all_visible = share_lo >= k_lo && share_lo + 16 <= k_hi && share_lo + 15 <= warp_qmin &&
                                          (p.window <= 0 || share_lo > warp_qmax - p.window);
                 if (!all_visible) {
 #pragma unroll
-                    for (int nt = 0; nt < 2; ++nt)
+                    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const int i = e >> 1;
-                            const int kpos = share_lo + nt * 8 + 2 * t + (e & 1);
-                            const bool vis = kpos >= k_lo && kpos < k_hi && kpos <= qpos[i] &&
-                                             (p.window <= 0 || kpos > qpos[i] - p.window);
+                            const int qp = qpos[nt][e & 1];
+                            const int kpos = share_lo + g + 8 * (e >> 1);
+                            const bool vis = kpos >= k_lo && kpos < k_hi && kpos <= qp && (p.window <= 0 || kpos > qp - p.window);
                             if (!vis) sc[nt][e] = -INFINITY;
                         }
                 }
+                unsigned ph[NT][2], pl[NT][2];
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
+                for (int nt = 0; nt < NT; ++nt) {
+                    float m_safe[2], alpha[2];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], sc[nt][e]);
-                float alpha[2], m_safe[2];
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
-                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-                    const float m_new = fmaxf(m[i], mx[i] * p.scale_log2);      // maxima live on the base-2 scale
-                    m_safe[i] = (m_new == -INFINITY) ? 0.f : m_new;               // no key seen yet: keep exponents finite
-                    alpha[i] = ex2(m[i] - m_safe[i]);
-                    m[i] = m_new;
-                    l[i] *= alpha[i];
-                }
-#pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
+                    for (int j = 0; j < 2; ++j) {
+                        float mx = fmaxf(sc[nt][j], sc[nt][j + 2]);            // over the 16 keys: the lanes that share t
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                        const float m_new = fmaxf(m[nt][j], mx * p.scale_log2);   // maxima live on the base-2 scale
+                        m_safe[j] = (m_new == -INFINITY) ? 0.f : m_new;           // no key seen yet: keep exponents finite
+                        alpha[j] = ex2(m[nt][j] - m_safe[j]);
+                        m[nt][j] = m_new;
+                        l[nt][j] *= alpha[j];
+                    }
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float pv = ex2(fmaf(sc[nt][e], p.scale_log2, -m_safe[e >> 1]));
+                        const float pv = ex2(fmaf(sc[nt][e], p.scale_log2, -m_safe[e & 1]));
                         sc[nt][e] = pv;
-                        l[e >> 1] += pv;
+                        l[nt][e & 1] += pv;
                     }
-                if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+                    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-                    for (int i = 0; i < HD / 8; ++i) {
-                        o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-                        o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+                        for (int i = 0; i < KSTEPS; ++i) {
+                            o[nt][i][0] *= alpha[0]; o[nt][i][1] *= alpha[1];
+                            o[nt][i][2] *= alpha[0]; o[nt][i][3] *= alpha[1];
+                        }
+                    }
+                    // probabilities as value + remainder in bfloat16 (the product keeps 16 bits of them),
+                    // moved from result layout [key g][rows 2t, 2t+1] to operand layout [keys 2t, 2t+1][row g]
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const float a = sc[nt][2 * h], c = sc[nt][2 * h + 1];
+                        const __nv_bfloat162 hi = __floats2bfloat162_rn(a, c);
+                        const float2 back = __bfloat1622float2(hi);
+                        ph[nt][h] = movmatrix_trans(*reinterpret_cast<const unsigned*>(&hi));
+                        pl[nt][h] = movmatrix_trans(pack_bf16(a - back.x, c - back.y));
                     }
                 }
-                // probabilities as value + remainder in bfloat16: the product keeps 16 bits of them
-                unsigned ph[4], pl[4];
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const float a = sc[r >> 1][(r & 1) * 2], c = sc[r >> 1][(r & 1) * 2 + 1];
-                    const __nv_bfloat162 hi = __floats2bfloat162_rn(a, c);
-                    const float2 back = __bfloat1622float2(hi);
-                    ph[r] = *reinterpret_cast<const unsigned*>(&hi);
-                    pl[r] = pack_bf16(a - back.x, c - back.y);
-                }
-#pragma unroll
-                for (int dp = 0; dp < HD / 16; ++dp) {
+                for (int dp = 0; dp < KSTEPS; ++dp) {
                     unsigned vf[4];
                     ldmatrix_x4_trans(vf, (va ^ (unsigned)(((dp * 2) & 7) << 4)) + (dp / 4) * HALF_BYTES);
-                    mma_bf16(o[2 * dp], ph, vf[0], vf[1]);
-                    mma_bf16(o[2 * dp + 1], ph, vf[2], vf[3]);
-                    mma_bf16(o[2 * dp], pl, vf[0], vf[1]);
-                    mma_bf16(o[2 * dp + 1], pl, vf[2], vf[3]);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        mma_bf16(o[nt][dp], vf, ph[nt][0], ph[nt][1]);
+                        mma_bf16(o[nt][dp], vf, pl[nt][0], pl[nt][1]);
+                    }
                 }
             }
             __syncwarp();
@@ -346,30 +380,35 @@ __global__ void __launch_bounds__(NTHREADS, 3) attention_decode_kernel(const __g
             atomicExch(p.status, ERR_CONSUMER_WAIT);
         }
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
-            l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
-        }
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                l[nt][j] += __shfl_xor_sync(0xffffffffu, l[nt][j], 4);
+                l[nt][j] += __shfl_xor_sync(0xffffffffu, l[nt][j], 8);
+                l[nt][j] += __shfl_xor_sync(0xffffffffu, l[nt][j], 16);
+            }
     }
 
     // ---- merge the four warps' partials through shared memory (the stages are done with)
     __syncthreads();
     if (failed_flag) return;
-    float* Om = reinterpret_cast<float*>(tiles);          // [NCW][16][HD]
-    float* Mm = Om + NCW * 16 * HD;                       // [NCW][16]
-    float* Lm = Mm + NCW * 16;                            // [NCW][16]
+    float* Om = reinterpret_cast<float*>(tiles);          // [NCW][NROWS][OPITCH]
+    float* Mm = Om + NCW * NROWS * OPITCH;                // [NCW][NROWS]
+    float* Lm = Mm + NCW * NROWS;                         // [NCW][NROWS]
     if (warp < NCW) {
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int rr = g + 8 * i;
+        for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
-            for (int nt = 0; nt < HD / 8; ++nt) {
-                Om[(warp * 16 + rr) * HD + nt * 8 + 2 * t] = o[nt][2 * i];
-                Om[(warp * 16 + rr) * HD + nt * 8 + 2 * t + 1] = o[nt][2 * i + 1];
-            }
-            if (t == 0) {
-                Mm[warp * 16 + rr] = m[i];
-                Lm[warp * 16 + rr] = l[i];
+            for (int dp = 0; dp < KSTEPS; ++dp)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    Om[(warp * NROWS + nt * 8 + 2 * t + (e & 1)) * OPITCH + dp * 16 + g + 8 * (e >> 1)] = o[nt][dp][e];
+            if (g == 0) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    Mm[warp * NROWS + nt * 8 + 2 * t + j] = m[nt][j];
+                    Lm[warp * NROWS + nt * 8 + 2 * t + j] = l[nt][j];
+                }
             }
         }
     }
@@ -379,15 +418,15 @@ __global__ void __launch_bounds__(NTHREADS, 3) attention_decode_kernel(const __g
         const int rr = idx / HD, d = idx - rr * HD;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < NCW; ++w) M = fmaxf(M, Mm[w * 16 + rr]);
+        for (int w = 0; w < NCW; ++w) M = fmaxf(M, Mm[w * NROWS + rr]);
         float num = 0.f, den = 0.f;
 #pragma unroll
         for (int w = 0; w < NCW; ++w) {
-            const float mw = Mm[w * 16 + rr];
+            const float mw = Mm[w * NROWS + rr];
             if (mw == -INFINITY) continue;
             const float f = exp2f(mw - M);
-            num = fmaf(f, Om[(w * 16 + rr) * HD + d], num);
-            den = fmaf(f, Lm[w * 16 + rr], den);
+            num = fmaf(f, Om[(w * NROWS + rr) * OPITCH + d], num);
+            den = fmaf(f, Lm[w * NROWS + rr], den);
         }
         const int tok = qs + tok0 + rr / ng;
         const int head = kvh * p.group + g0 + rr % ng;
@@ -534,10 +573,10 @@ Plan make_plan(int n_seqs, int n_heads, int n_kv_heads, int head_dim, int max_q_
     return pl;
 }
 
-template <int HD>
+template <int HD, int NT>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParams& p, dim3 grid, cudaStream_t s) {
     constexpr size_t smem = smem_for<HD>();
-    auto kern = attention_decode_kernel<HD, stages_for<HD>()>;
+    auto kern = attention_decode_kernel<HD, stages_for<HD>(), NT>;
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -605,7 +644,12 @@ extern "C" int tl_paged_attention_decode(const void* q, const void* k_pages, con
 
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(pl.n_q_tiles * pl.n_splits, n_kv_heads * pl.n_gchunks, n_seqs);
-    rc = head_dim == 128 ? launch<128>(mk, mv, p, grid, s) : launch<64>(mk, mv, p, grid, s);
+    // query rows a CTA can meet: one 8-row block is enough for them, or two
+    const int rows_used = (max_q_len < pl.tpw ? max_q_len : pl.tpw) * pl.ng;
+    if (rows_used <= 8)
+        rc = head_dim == 128 ? launch<128, 1>(mk, mv, p, grid, s) : launch<64, 1>(mk, mv, p, grid, s);
+    else
+        rc = head_dim == 128 ? launch<128, 2>(mk, mv, p, grid, s) : launch<64, 2>(mk, mv, p, grid, s);
     if (rc != TL_OK) return rc;
     if (pl.n_splits > 1) {
         cudaError_t e = tl_launch(merge_partials_kernel, dim3((unsigned)n_tokens * (unsigned)n_heads),
