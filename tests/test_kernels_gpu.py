@@ -242,14 +242,22 @@ ATTN_CASES = [
     ([700, 45], [3, 4], 32, 8, 128, 16, None),            # 16 rows to a tile (four tokens of a group of four), head_dim 128
     ([400, 33, 130], [1, 1, 1], 16, 1, 128, 16, None),    # decoding with a group of 16, head_dim 128
     ([260, 19], [2, 1], 12, 2, 64, 8, 50),                # group of 6: two tokens make 12 rows, behind a window
+    ([3000, 700], [400, 700], 8, 2, 128, 16, None),       # a portion late in a long context beside a whole prompt
+    ([1000], [1000], 4, 2, 64, 32, 300),                  # a window that spans several key tiles
+    ([600, 130], [600, 129], 4, 4, 128, 256, None),       # pages larger than a key tile of any kernel
 ]
 
 
-IMPLS = [(torch.float32, "general"), (torch.bfloat16, "general"), (torch.bfloat16, "mma"), (torch.bfloat16, "decode")]
+IMPLS = [(torch.float32, "general"), (torch.bfloat16, "general"), (torch.bfloat16, "mma"), (torch.bfloat16, "decode"),
+         (torch.bfloat16, "prefill")]
 
 
 def mma_takes(hd):
     return hd in (16, 32, 64, 128)
+
+
+def prefill_takes(hd, P):
+    return hd in (64, 128) and P & (P - 1) == 0
 
 
 def decode_takes(q_lens, H, KV, hd, P):
@@ -265,6 +273,8 @@ def test_paged_attention_matches_twin(ops, dtype, impl, case):
         pytest.skip("the tensor-core kernel does not take this head size")
     if impl == "decode" and not decode_takes(q_lens, H, KV, hd, P):
         pytest.skip("the decode kernel does not take this step")
+    if impl == "prefill" and not prefill_takes(hd, P):
+        pytest.skip("the tcgen05 prefill kernel does not take this head size or page size")
     a = build_paged(seq_lens, q_lens, H, KV, hd, P, dtype, seed=len(seq_lens) * 100 + hd)
     scale = hd ** -0.5
     got = ops.paged_attention(**a, scale=scale, window=window, impl=impl)
@@ -292,7 +302,7 @@ def test_decode_attention_split_over_keys(ops, dtype, impl, B, L):
 def test_attention_finds_one_far_key_among_hundreds(ops, dtype, impl, key_pos):
     """Random scores hide a dropped key; here one key takes nearly all the weight, so the output
     must equal that key's value."""
-    L, H, KV, hd, P = 700, 4, 2, (64 if impl == "decode" else 32), 16
+    L, H, KV, hd, P = 700, 4, 2, (64 if impl in ("decode", "prefill") else 32), 16
     a = build_paged([L, 40], [1, 1], H, KV, hd, P, dtype, seed=key_pos, peak=(0, key_pos, 10.0))
     got = ops.paged_attention(**a, scale=hd ** -0.5, window=None, impl=impl).float()
     page, slot = a["block_table"][0, key_pos // P].item(), key_pos % P
@@ -308,7 +318,7 @@ def test_attention_finds_one_far_key_among_hundreds(ops, dtype, impl, key_pos):
 def test_window_edge_is_exact(ops, dtype, impl):
     """The key just outside the window gets a huge score: if the edge were off by one it would
     take over the output."""
-    L, H, KV, hd, P, w = 100, 2, 1, (64 if impl == "decode" else 16), 8, 24
+    L, H, KV, hd, P, w = 100, 2, 1, (64 if impl in ("decode", "prefill") else 16), 8, 24
     for edge_inside in (False, True):
         key_pos = (L - 1) - w + (1 if edge_inside else 0)   # last query sits at L - 1
         a = build_paged([L], [1], H, KV, hd, P, dtype, seed=3, peak=(0, key_pos, 12.0))

@@ -33,7 +33,7 @@ NVCC_FLAGS = [
 # libraries that need more than the CUDA runtime
 EXTRA_LINK: Dict[str, List[str]] = {}
 
-ALL_LIBRARIES = ("elementwise", "rope", "attention", "attention_mma", "attention_decode", "gemm_simt", "gemm_tcgen05", "sampling")
+ALL_LIBRARIES = ("elementwise", "rope", "attention", "attention_mma", "attention_decode", "attention_prefill", "gemm_simt", "gemm_tcgen05", "sampling")
 
 
 class KernelBuildError(RuntimeError):

@@ -80,6 +80,8 @@ def _timed(fn):
 class NativeOps:
     """The kernels as methods.  Libraries are compiled and loaded on first use."""
 
+    PREFILL_MIN_Q = 96      # portions at least this long go to the tcgen05 prefill attention kernel
+
     name = "native-sm100a"
 
     def __init__(self):
@@ -343,8 +345,9 @@ class NativeOps:
                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``impl``: ``"general"`` (CUDA cores, any supported size, both dtypes), ``"mma"`` (tensor
         cores, bfloat16, head_dim 16/32/64/128), ``"decode"`` (tensor cores fed by TMA, bfloat16,
-        head_dim 64/128, steps whose requests bring one token or very few) or ``"auto"``
-        (the most specialised kernel that applies).
+        head_dim 64/128, steps whose requests bring one token or very few), ``"prefill"``
+        (tcgen05 tensor cores with accumulators in tensor memory, bfloat16, head_dim 64/128, made
+        for long portions) or ``"auto"`` (the most specialised kernel that applies).
 
         ``block_table``, ``q_start`` and ``kv_len`` may be slices that cover only some requests of
         the step (``q_start`` keeps counting tokens from the start of ``q``); ``n_tokens`` then
@@ -371,7 +374,7 @@ class NativeOps:
         _need(block_table.shape[0] >= n_seqs and q_start.numel() >= n_seqs + 1 and kv_len.numel() >= n_seqs,
               "block_table, q_start and kv_len must cover every request of the step")
         _need(block_table.shape[1] * page_size >= max_kv_len, "block_table is too narrow for max_kv_len")
-        _need(impl in ("auto", "general", "mma", "decode"), f"unknown attention implementation {impl!r}")
+        _need(impl in ("auto", "general", "mma", "decode", "prefill"), f"unknown attention implementation {impl!r}")
         mma_ok = q.dtype == torch.bfloat16 and head_dim in (16, 32, 64, 128)
         _need(impl != "mma" or mma_ok, "the tensor-core attention kernel takes bfloat16 and head_dim 16, 32, 64 or 128")
         use_mma = mma_ok and impl in ("auto", "mma")
@@ -384,6 +387,21 @@ class NativeOps:
         floats = ctypes.c_longlong(0)
         if out is None:
             out = torch.empty_like(q)
+        prefill_ok = (q.dtype == torch.bfloat16 and impl in ("auto", "prefill") and head_dim in (64, 128) and not decode_ok
+                      and (impl == "prefill" or max_q_len >= self.PREFILL_MIN_Q) and
+                      self._lib("attention_prefill").tl_attention_prefill_supports(n_heads, n_kv_heads, head_dim, page_size) == 1)
+        _need(impl != "prefill" or prefill_ok, "the tcgen05 prefill attention kernel takes bfloat16, head_dim 64 or 128 "
+              "and a power-of-two page size")
+        if prefill_ok:
+            lib = self._lib("attention_prefill")
+            rc = lib.tl_paged_attention_prefill(
+                _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
+                _ptr(q_start), _ptr(kv_len), ctypes.c_void_p(self._status.data_ptr()), ctypes.c_longlong(q.shape[0]),
+                T, n_seqs, n_heads, n_kv_heads, head_dim, page_size, ctypes.c_longlong(k_pages.shape[0]), max_q_len,
+                int(window or 0), ctypes.c_float(scale), _stream())
+            _check(rc, "paged_attention_prefill")
+            self.launches += 1
+            return out
         if decode_ok:
             lib = self._lib("attention_decode")
             rc = lib.tl_attention_decode_plan(T, n_seqs, n_heads, n_kv_heads, head_dim, max_q_len, max_kv_len,
