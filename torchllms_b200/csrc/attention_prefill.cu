@@ -7,21 +7,27 @@
 // a whole query row, so the softmax needs no exchange between threads.
 //
 // A CTA serves 128 consecutive tokens of one request and one query head (M = 128), walking the
-// visible keys in tiles of 128.  192 threads:
-//   warps 0-3      : softmax.  Thread r owns row r = TMEM lane r: reads its 128 scores
-//                    (tcgen05.ld), masks, keeps the running maximum and sum, writes the
-//                    probabilities into shared memory in the operand layout, rescales
-//                    its accumulator row in TMEM when the maximum has grown, and at the end
-//                    divides the row by the sum and stores it.
-//   warp 4, lane 0 : issues the products.  S_j = Q K_j^T into one of two score buffers in TMEM
-//                    (so that S_{j+1} is computed while the softmax works on S_j), then
-//                    O += P_j V_j once the probabilities are in place.
-//   warp 5, lane 0 : TMA producer: the Q tile once, then per key tile one box per page (or per
-//                    128 rows of a larger page) and 64-element column block of K and of V into
-//                    128-byte-swizzled shared memory; no multicast.
-// Q and K are K-major operands (rows of 128 bytes, swizzled); V is used as stored, keys x
-// columns, as an MN-major operand.  Probabilities are multiplied as value + remainder, both
-// bfloat16 (two products), so that the product keeps 16 bits of them, as in the other kernels.
+// visible keys in tiles of 128.  320 threads:
+//   warps 0-7      : softmax.  Row r = TMEM lane r belongs to two threads, one in warp r / 32 for
+//                    the tile's first 64 keys and one in warp 4 + r / 32 for the other 64 (a warp
+//                    reaches the lanes 32 (w mod 4) .. + 31 only).  At the start each puts its half
+//                    of the query row into tensor memory.  Per tile each reads its scores
+//                    (tcgen05.ld), masks, and the two swap their maxima through shared memory;
+//                    both then keep the same running maximum, a sum of their own, write their
+//                    probabilities back into tensor memory where the scores were (tcgen05.st),
+//                    rescale their half of the accumulator row when the maximum has grown, and at
+//                    the end divide it by the sum and store it.  No other exchange between threads.
+//   warp 8, lane 0 : issues the products.  S_j = Q K_j^T into one of two score buffers (so that
+//                    S_{j+1} is computed while the softmax works on S_j), then O += P_j V_j once
+//                    the probabilities are in place.  The left operand of both is read from
+//                    tensor memory: shared memory, whose bandwidth a product with both operands
+//                    there uses up, serves K and V only.
+//   warp 9         : TMA producer: per key tile one box per page (or per 128 rows of a larger
+//                    page) and 64-element column block of K and of V into 128-byte-swizzled
+//                    shared memory, each in a ring of its own; no multicast.
+// K is a K-major operand (rows of 128 bytes, swizzled); V is used as stored, keys x columns, as
+// an MN-major operand.  Probabilities are multiplied as value + remainder, both bfloat16 (two
+// products), so that the product keeps 16 bits of them, as in the other kernels.
 //
 // The maximum that exponents are taken against is allowed to lag behind the true running
 // maximum by up to 2^8: the accumulator row is rescaled (a round trip through registers) only
@@ -42,15 +48,17 @@ namespace {
 
 constexpr int BM = 128;                 // query rows (tokens) per CTA
 constexpr int BN = 128;                 // keys per tile
-constexpr int NTHREADS = 192;
+constexpr int NTHREADS = 320;
+constexpr int W_ISSUE = 8, W_COPY = 9;   // warps 0-7 are the softmax
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LAG = 8.f;              // how far (in powers of two) the maximum in use may lag
 constexpr unsigned long long WAIT_NS = 2000ull * 1000ull * 1000ull;
 enum : int { ERR_PRODUCER_WAIT = 301, ERR_ISSUER_WAIT = 302, ERR_SOFTMAX_WAIT = 303, ERR_BAD_COPY = 304 };
-constexpr unsigned TMEM_COLS = 512;     // two score buffers of 128 columns and the accumulator
+constexpr unsigned TMEM_COLS = 512;     // two score buffers of 128 columns, the accumulator, the queries
 constexpr unsigned COL_S = 0, COL_O = 256;
 
 struct PrefillParams {
+    const __nv_bfloat16* q;
     __nv_bfloat16* out;
     const int* block_table;
     const int* q_start;
@@ -129,11 +137,13 @@ __device__ __forceinline__ unsigned long long desc_mn_major(unsigned addr, unsig
 __host__ __device__ constexpr unsigned idesc(int n, unsigned a_fmt, unsigned b_fmt, unsigned b_mn_major) {
     return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (b_mn_major << 16) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
 }
-__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
-                                     unsigned id, unsigned accumulate) {
+// D[tmem] (+)= A[tmem] . B[shared]: the left operand lies in tensor memory, row = lane, two 16-bit
+// elements of K to a column
+__device__ __forceinline__ void umma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long b_desc,
+                                        unsigned id, unsigned accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(id), "r"(accumulate) : "memory");
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(id), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -147,13 +157,21 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr));
 }
-__device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32]) {
+template <int N> __device__ __forceinline__ void tmem_st(unsigned taddr, const unsigned (&r)[N]);
+template <> __device__ __forceinline__ void tmem_st<32>(unsigned taddr, const unsigned (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                  "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
                  ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
                    "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
                    "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
                    "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+template <> __device__ __forceinline__ void tmem_st<16>(unsigned taddr, const unsigned (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
                  : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -170,49 +188,58 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
+template <int STAGES>
+struct Tail {                   // what lies behind the tiles in shared memory
+    unsigned long long q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+    unsigned long long s_full[2], p_full, pv_done;
+    unsigned tmem_base_slot;
+    int failed_flag;
+    float swap[2][2][BM];       // [tile parity][half][row]
+};
+
 template <int HD, int STAGES>
-__global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
-                                                                       const __grid_constant__ CUtensorMap map_k,
+__global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                        const __grid_constant__ CUtensorMap map_v,
                                                                        const PrefillParams p) {
     constexpr int HALVES = HD / 64;                      // 64-element (128-byte) column blocks of a row
     constexpr unsigned HALF_BYTES = BN * 128;            // one [128 rows x 128 B] block
-    constexpr unsigned Q_BYTES = HALVES * HALF_BYTES;
     constexpr unsigned KV_BYTES = HALVES * HALF_BYTES;   // K (or V) of a tile
-    constexpr unsigned STAGE_BYTES = 2 * KV_BYTES;
-    constexpr unsigned P_BYTES = 2 * HALF_BYTES;         // [128 rows x 128 keys] bfloat16 as two 64-key blocks; value, then remainder
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
-    unsigned char* Qs = base;
-    unsigned char* Ps = base + Q_BYTES;
-    unsigned char* tiles = Ps + 2 * P_BYTES;
-    __shared__ __align__(8) unsigned long long q_full;
-    __shared__ __align__(8) unsigned long long kv_full[STAGES];
-    __shared__ __align__(8) unsigned long long kv_empty[STAGES];
-    __shared__ __align__(8) unsigned long long s_full[2];
-    __shared__ __align__(8) unsigned long long s_empty[2];
-    __shared__ __align__(8) unsigned long long p_full;
-    __shared__ __align__(8) unsigned long long pv_done;
-    __shared__ unsigned tmem_base_slot;
-    __shared__ int failed_flag;
+    constexpr unsigned COL_Q = COL_O + HD;               // Q as bfloat16 pairs: HD / 2 columns
+    // All shared memory is dynamic and laid out by hand: the K and V rings first (they need
+    // 1024-byte alignment for the 128-byte swizzle, which the start of the window has; the producer
+    // checks), then the barriers and the little that threads exchange.
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* tiles = smem_raw;
+    Tail<STAGES>& tail = *reinterpret_cast<Tail<STAGES>*>(tiles + 2 * STAGES * KV_BYTES);
+    unsigned long long& q_full = tail.q_full;
+    unsigned long long (&k_full)[STAGES] = tail.k_full;
+    unsigned long long (&k_empty)[STAGES] = tail.k_empty;
+    unsigned long long (&v_full)[STAGES] = tail.v_full;
+    unsigned long long (&v_empty)[STAGES] = tail.v_empty;
+    unsigned long long (&s_full)[2] = tail.s_full;
+    unsigned long long& p_full = tail.p_full;
+    unsigned long long& pv_done = tail.pv_done;
+    unsigned& tmem_base_slot = tail.tmem_base_slot;
+    int& failed_flag = tail.failed_flag;
+    float (&swap_max)[2][2][BM] = tail.swap;                 // the two halves of a row tell each other their maximum
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
         failed_flag = 0;
-        mbar_init(&q_full, 1);
+        mbar_init(&q_full, 8);
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&kv_full[s], 1);
-            mbar_init(&kv_empty[s], 1);
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], 1);
         }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&s_full[i], 1);
-            mbar_init(&s_empty[i], 4);
-        }
-        mbar_init(&p_full, 4);
+        mbar_init(&s_full[0], 1);
+        mbar_init(&s_full[1], 1);
+        mbar_init(&p_full, 8);
         mbar_init(&pv_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) {
+    if (warp == W_ISSUE) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -240,93 +267,116 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
     const int k_start = k_lo & ~(BN - 1);
     const int n_tiles = active ? (k_hi - k_start + BN - 1) / BN : 0;
 
-    if (warp == 5) {
-        if (lane == 0 && active) {
-            // ---- producer
-            bool sound = (smem_u32(base) & 1023u) == 0u;
-#pragma unroll
-            for (int h = 0; h < HALVES; ++h) sound = sound && copy_is_sound(Qs + h * HALF_BYTES, head * HD + h * 64, qs + tok0);
-            if (!sound) {
+    if (warp == W_COPY) {
+        if (active) {
+            // ---- producer (the whole warp: lanes look pages up and issue copies side by side).
+            // K and V have rings of their own: a K stage is free as soon as the scores of its tile
+            // are computed, long before the V stage of the same tile.
+            bool sound = (smem_u32(tiles) & 1023u) == 0u;
+            if (!sound && lane == 0) {
                 failed_flag = 1;
                 atomicExch(p.status, ERR_BAD_COPY);
             }
-            mbar_expect_tx(&q_full, Q_BYTES);
-#pragma unroll
-            for (int h = 0; h < HALVES; ++h)
-                if (sound) tma_load_2d(Qs + h * HALF_BYTES, &map_q, &q_full, head * HD + h * 64, qs + tok0);
             const int* table = p.block_table + (size_t)b * p.table_stride;
+            const int n_boxes = BN / p.box_rows;
             for (int j = 0; j < n_tiles && sound; ++j) {
                 const int s = j % STAGES;
-                if (j >= STAGES && !mbar_wait(&kv_empty[s], ((j / STAGES) - 1) & 1, failed)) {
-                    failed_flag = 1;
-                    atomicExch(p.status, ERR_PRODUCER_WAIT);
-                    break;
-                }
-                mbar_expect_tx(&kv_full[s], STAGE_BYTES);
-                unsigned char* kt = tiles + s * STAGE_BYTES;
                 const int k0 = k_start + j * BN;
-                for (int c = 0; c < BN / p.box_rows; ++c) {
-                    const int kpos = k0 + c * p.box_rows;
-                    // boxes past the last key start outside the tensor: the copy writes the zero fill, so
-                    // that what is multiplied by probability 0 there is finite
-                    int row = p.total_rows;
-                    if (kpos < k_hi) {
-                        const int page = table[kpos >> p.page_shift];
-                        row = (page * p.n_kv_heads + kvh) * p.page_size + (kpos & (p.page_size - 1));
-                    }
-#pragma unroll
-                    for (int h = 0; h < HALVES; ++h) {
-                        unsigned char* dst = kt + h * HALF_BYTES + c * p.box_rows * 128;
-                        if (!copy_is_sound(dst, h * 64, row) || !copy_is_sound(dst + KV_BYTES, h * 64, row)) {
+                for (int which = 0; which < 2 && sound; ++which) {
+                    unsigned long long* full = which == 0 ? &k_full[s] : &v_full[s];
+                    unsigned long long* empty = which == 0 ? &k_empty[s] : &v_empty[s];
+                    if (j >= STAGES && !__all_sync(0xffffffffu, mbar_wait(empty, ((j / STAGES) - 1) & 1, failed))) {
+                        if (lane == 0) {
                             failed_flag = 1;
-                            atomicExch(p.status, ERR_BAD_COPY);
-                            sound = false;
-                            continue;
+                            atomicExch(p.status, ERR_PRODUCER_WAIT);
                         }
-                        tma_load_2d(dst, &map_k, &kv_full[s], h * 64, row);
-                        tma_load_2d(dst + KV_BYTES, &map_v, &kv_full[s], h * 64, row);
+                        sound = false;
+                        break;
                     }
+                    if (lane == 0) mbar_expect_tx(full, KV_BYTES);
+                    __syncwarp();
+                    unsigned char* dst0 = tiles + (which * STAGES + s) * KV_BYTES;
+                    const CUtensorMap* map = which == 0 ? &map_k : &map_v;
+                    for (int c = lane; c < n_boxes; c += 32) {
+                        const int kpos = k0 + c * p.box_rows;
+                        // boxes past the last key start outside the tensor: the copy writes the zero fill,
+                        // so that what is multiplied by probability 0 there is finite
+                        int row = p.total_rows;
+                        if (kpos < k_hi) {
+                            const int page = table[kpos >> p.page_shift];
+                            row = (page * p.n_kv_heads + kvh) * p.page_size + (kpos & (p.page_size - 1));
+                        }
+#pragma unroll
+                        for (int h = 0; h < HALVES; ++h) {
+                            unsigned char* dst = dst0 + h * HALF_BYTES + c * p.box_rows * 128;
+                            if (!copy_is_sound(dst, h * 64, row)) {
+                                failed_flag = 1;
+                                atomicExch(p.status, ERR_BAD_COPY);
+                                continue;
+                            }
+                            tma_load_2d(dst, map, full, h * 64, row);
+                        }
+                    }
+                    __syncwarp();
                 }
             }
         }
-    } else if (warp == 4) {
+    } else if (warp == W_ISSUE) {
         if (lane == 0 && active) {
-            // ---- issuer: S_0, then per tile S_{j+1} (while the softmax works on S_j) and O += P_j V_j
-            constexpr unsigned id_s = idesc(BN, 1u, 1u, 0u);     // bf16 x bf16, both K-major
+            // ---- issuer.  Two queues, scores S_j = Q K_j^T and products O += P_j V_j; whichever has
+            // its inputs is issued, scores first.  The left operand of both comes from tensor memory
+            // (Q, and the probabilities where the scores of their tile were), so shared memory is read
+            // for K and V only.  S_{j+2} goes where P_j lies: it is issued after O += P_j V_j, and
+            // products issued by one thread run in order.
+            constexpr unsigned id_s = idesc(BN, 1u, 1u, 0u);     // bf16 x bf16, K as stored (K-major)
             constexpr unsigned id_o = idesc(HD, 1u, 1u, 1u);     // bf16 probabilities x bf16 values as stored (MN-major)
             bool ok = mbar_wait(&q_full, 0, failed);
-            auto issue_s = [&](int j) -> bool {
-                const int s = j % STAGES, sb = j & 1;
-                if (!mbar_wait(&kv_full[s], (j / STAGES) & 1, failed)) return false;
-                if (j >= 2 && !mbar_wait(&s_empty[sb], ((j >> 1) - 1) & 1, failed)) return false;
-                tc_fence_after();
-                const unsigned qa = smem_u32(Qs), ka = smem_u32(tiles + s * STAGE_BYTES);
+            tc_fence_after();
+            int ns = 0, npv = 0;
+            unsigned long long t0 = 0;
+            unsigned spins = 0;
+            while (ok && npv < n_tiles) {
+                bool did = false;
+                if (ns < n_tiles && ns < npv + 2) {
+                    const int s = ns % STAGES, sb = ns & 1;
+                    if (mbar_try_wait(&k_full[s], (ns / STAGES) & 1)) {
+                        tc_fence_after();
+                        const unsigned ka = smem_u32(tiles + s * KV_BYTES);
 #pragma unroll
-                for (int kd = 0; kd < HD / 16; ++kd) {
-                    const unsigned off = (kd / 4) * HALF_BYTES + (kd % 4) * 32;
-                    umma(tmem + COL_S + sb * BN, desc_k_major(qa + off), desc_k_major(ka + off), id_s, kd > 0 ? 1u : 0u);
+                        for (int kd = 0; kd < HD / 16; ++kd)
+                            umma_ts(tmem + COL_S + sb * BN, tmem + COL_Q + kd * 8,
+                                    desc_k_major(ka + (kd / 4) * HALF_BYTES + (kd % 4) * 32), id_s, kd > 0 ? 1u : 0u);
+                        umma_commit(&s_full[sb]);
+                        umma_commit(&k_empty[s]);        // the K stage is free once the scores are computed
+                        ++ns;
+                        did = true;
+                    }
                 }
-                umma_commit(&s_full[sb]);
-                return true;
-            };
-            ok = ok && issue_s(0);
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                if (j + 1 < n_tiles) ok = issue_s(j + 1);
-                if (!ok || !mbar_wait(&p_full, j & 1, failed)) {
-                    ok = false;
-                    break;
+                if (!did && npv < ns) {
+                    const int s = npv % STAGES, sb = npv & 1;
+                    if (mbar_try_wait(&p_full, npv & 1) && mbar_try_wait(&v_full[s], (npv / STAGES) & 1)) {
+                        tc_fence_after();
+                        const unsigned va = smem_u32(tiles + (STAGES + s) * KV_BYTES);
+#pragma unroll
+                        for (int part = 0; part < 2; ++part)             // value, then remainder
+#pragma unroll
+                            for (int kk = 0; kk < BN / 16; ++kk)
+                                umma_ts(tmem + COL_O, tmem + COL_S + sb * BN + part * (BN / 2) + kk * 8,
+                                        desc_mn_major(va + kk * 2048, HALF_BYTES), id_o, (npv > 0 || part > 0 || kk > 0) ? 1u : 0u);
+                        umma_commit(&v_empty[s]);        // the V stage is free once these products have read it
+                        umma_commit(&pv_done);           // the accumulator is up to date
+                        ++npv;
+                        did = true;
+                    }
                 }
-                tc_fence_after();
-                const int s = j % STAGES;
-                const unsigned pa = smem_u32(Ps), va = smem_u32(tiles + s * STAGE_BYTES + KV_BYTES);
-#pragma unroll
-                for (int part = 0; part < 2; ++part)             // value, then remainder
-#pragma unroll
-                    for (int kk = 0; kk < BN / 16; ++kk)
-                        umma(tmem + COL_O, desc_k_major(pa + part * P_BYTES + (kk / 4) * HALF_BYTES + (kk % 4) * 32),
-                             desc_mn_major(va + kk * 2048, HALF_BYTES), id_o, (j > 0 || part > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(&kv_empty[s]);       // the stage is free once these products have read it
-                umma_commit(&pv_done);           // and so are the probabilities; the accumulator is up to date
+                if (did) {
+                    spins = 0;
+                } else if ((++spins & 1023u) == 0u) {
+                    unsigned long long t1;
+                    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+                    if (spins == 1024u) t0 = t1;
+                    if (*failed || t1 - t0 > WAIT_NS) ok = false;
+                }
             }
             if (!ok) {
                 failed_flag = 1;
@@ -334,105 +384,136 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
             }
         }
     } else if (active) {
-        // ---- softmax: thread r owns row r of the tile, TMEM lane r
-        const int r = tid;                                   // warp w reads lanes 32 w .. 32 w + 31
-        const unsigned lane_addr = tmem + ((unsigned)(warp * 32) << 16);
+        // ---- softmax: row r = TMEM lane r; this thread has its keys 64 half .. 64 half + 63 of every tile
+        constexpr int HN = BN / 2;                           // keys per thread and tile
+        constexpr int HO = HD / 2;                           // accumulator columns per thread
+        const int half = warp >> 2;
+        const int r = (warp & 3) * 32 + lane;
+        const unsigned lane_addr = tmem + ((unsigned)((warp & 3) * 32) << 16);
         const bool valid = r < rows;
         const int qpos = qpos_base + tok0 + (valid ? r : rows - 1);      // idle rows follow the last real one
         const int tile_qmin = qpos_base + tok0;
+        const int pair_barrier = 1 + (warp & 3);             // named barrier of the two warps that share 32 rows
+        // this thread's half of its query row goes into tensor memory, two bfloat16 to a column
+        {
+            unsigned qw[HO / 2];
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + tok0 + r) * p.n_heads + head) * HD + half * HO);
+#pragma unroll
+            for (int i = 0; i < HO / 8; ++i) {
+                const uint4 v = valid ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+                qw[4 * i] = v.x; qw[4 * i + 1] = v.y; qw[4 * i + 2] = v.z; qw[4 * i + 3] = v.w;
+            }
+            tmem_st<HO / 2>(lane_addr + COL_Q + half * (HO / 2), qw);
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&q_full);
+        }
         float m_used = -INFINITY, l = 0.f;
-        unsigned char* prow = Ps + r * 128;
         bool ok = true;
+        // Once a wait has failed (ok = false) the loop only keeps its appointments at the pair's
+        // barrier: both warps of a pair pass it once per tile whatever happens, so neither can be
+        // left waiting there.
         for (int j = 0; j < n_tiles; ++j) {
             const int sb = j & 1;
             // (a wait's verdict is taken by the whole warp: the loads below need all of its lanes)
-            if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], (j >> 1) & 1, failed))) {
-                ok = false;
-                break;
-            }
-            tc_fence_after();
-            unsigned raw[BN];
-#pragma unroll
-            for (int c = 0; c < BN / 32; ++c)
-                tmem_ld32(lane_addr + COL_S + sb * BN + c * 32, *reinterpret_cast<unsigned(*)[32]>(&raw[c * 32]));
-            tmem_wait_ld();
-            float sc[BN];
-#pragma unroll
-            for (int i = 0; i < BN; ++i) sc[i] = __uint_as_float(raw[i]);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[sb]);        // the score buffer may be written again
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (j >> 1) & 1, failed));
+            if (!ok) failed_flag = 1;
+            unsigned raw[HN];                                // the scores
+            float mine = -INFINITY;
             const int k0 = k_start + j * BN;
-            // the whole tile is visible to every row of this CTA?
-            const bool clear = k0 + BN - 1 <= tile_qmin && k0 >= k_lo &&
-                               (p.window <= 0 || k0 > qpos_base + tok0 + rows - 1 - p.window);
-            if (!clear) {
-#pragma unroll
-                for (int i = 0; i < BN; ++i) {
-                    const int kpos = k0 + i;
-                    const bool vis = kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
-                    if (!vis) sc[i] = -INFINITY;
-                }
-            }
-            float mx0 = sc[0], mx1 = sc[1], mx2 = sc[2], mx3 = sc[3];
-#pragma unroll
-            for (int i = 4; i < BN; i += 4) {
-                mx0 = fmaxf(mx0, sc[i]); mx1 = fmaxf(mx1, sc[i + 1]);
-                mx2 = fmaxf(mx2, sc[i + 2]); mx3 = fmaxf(mx3, sc[i + 3]);
-            }
-            const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
-            const bool grow = m_new > m_used + LAG;          // also true for the first keys a row sees
-            // before the probabilities are overwritten and the accumulator is touched, the product
-            // that reads them must be over
-            if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(&pv_done, (j - 1) & 1, failed))) {
-                ok = false;
-                break;
-            }
-            if (j > 0 && __any_sync(0xffffffffu, grow)) {
+            if (ok) {
                 tc_fence_after();
-                const float alpha = grow ? ex2(m_used - m_new) : 1.f;     // 0 for a row that had seen nothing
+#pragma unroll
+                for (int c = 0; c < HN / 32; ++c)
+                    tmem_ld32(lane_addr + COL_S + sb * BN + half * HN + c * 32, *reinterpret_cast<unsigned(*)[32]>(&raw[c * 32]));
+                tmem_wait_ld();
+                // the whole tile is visible to every row of this CTA?
+                const bool clear = k0 + BN - 1 <= tile_qmin && k0 >= k_lo &&
+                                   (p.window <= 0 || k0 > qpos_base + tok0 + rows - 1 - p.window);
+                if (!clear) {
+#pragma unroll
+                    for (int i = 0; i < HN; ++i) {
+                        const int kpos = k0 + half * HN + i;
+                        const bool vis = kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
+                        if (!vis) raw[i] = 0xff800000u;      // -inf
+                    }
+                }
+                float mx0 = __uint_as_float(raw[0]), mx1 = __uint_as_float(raw[1]);
+                float mx2 = __uint_as_float(raw[2]), mx3 = __uint_as_float(raw[3]);
+#pragma unroll
+                for (int i = 4; i < HN; i += 4) {
+                    mx0 = fmaxf(mx0, __uint_as_float(raw[i])); mx1 = fmaxf(mx1, __uint_as_float(raw[i + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(raw[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(raw[i + 3]));
+                }
+                mine = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            }
+            // The partner can be one tile ahead at most (it stops at the next barrier until this
+            // thread gets there), so two slots, used in turn, are never overwritten unread.  Past the
+            // barrier both have their scores in registers: the probabilities may go where they were.
+            swap_max[sb][half][r] = mine;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
+            if (!ok) continue;
+            const float both = fmaxf(mine, swap_max[sb][half ^ 1][r]);
+            const float m_new = fmaxf(m_used, both * p.scale_log2);
+            const bool grow = m_new > m_used + LAG;          // also true for the first keys a row sees
+            const bool rescale = j > 0 && __any_sync(0xffffffffu, grow);
+            const float alpha = grow ? ex2(m_used - m_new) : 1.f;        // 0 for a row that had seen nothing
+            if (grow) m_used = m_new;
+            const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;   // nothing seen yet: keep exponents finite
+            // probabilities as value + remainder, two bfloat16 to a column: columns 32 half .. of the
+            // tile's buffer hold the values of this thread's keys, columns 64 + 32 half .. the remainders
+            unsigned hi[HN / 2], lo[HN / 2];
+            float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < HN; i += 4) {
+                const float e0 = ex2(fmaf(__uint_as_float(raw[i]), p.scale_log2, -m_safe));
+                const float e1 = ex2(fmaf(__uint_as_float(raw[i + 1]), p.scale_log2, -m_safe));
+                const float e2 = ex2(fmaf(__uint_as_float(raw[i + 2]), p.scale_log2, -m_safe));
+                const float e3 = ex2(fmaf(__uint_as_float(raw[i + 3]), p.scale_log2, -m_safe));
+                l0 += e0; l1 += e1; l2 += e2; l3 += e3;
+                const __nv_bfloat162 ha = __floats2bfloat162_rn(e0, e1), hb = __floats2bfloat162_rn(e2, e3);
+                const float2 ba = __bfloat1622float2(ha), bb = __bfloat1622float2(hb);
+                hi[i / 2] = *reinterpret_cast<const unsigned*>(&ha);
+                hi[i / 2 + 1] = *reinterpret_cast<const unsigned*>(&hb);
+                lo[i / 2] = pack_bf16(e0 - ba.x, e1 - ba.y);
+                lo[i / 2 + 1] = pack_bf16(e2 - bb.x, e3 - bb.y);
+            }
+            if (rescale) {
+                // the product that last wrote the accumulator must be over
+                ok = __all_sync(0xffffffffu, mbar_wait(&pv_done, (j - 1) & 1, failed));
+                if (!ok) {
+                    failed_flag = 1;
+                    continue;
+                }
+                tc_fence_after();
                 l *= alpha;
 #pragma unroll
-                for (int c = 0; c < HD / 32; ++c) {
+                for (int c = 0; c < HO / 32; ++c) {
                     unsigned v[32];
-                    tmem_ld32(lane_addr + COL_O + c * 32, v);
+                    tmem_ld32(lane_addr + COL_O + half * HO + c * 32, v);
                     tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                    tmem_st32(lane_addr + COL_O + c * 32, v);
+                    tmem_st<32>(lane_addr + COL_O + half * HO + c * 32, v);
                 }
-                tmem_wait_st();
-            }
-            if (grow) m_used = m_new;
-            const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;   // nothing seen yet: keep exponents finite
-            float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-#pragma unroll
-            for (int c = 0; c < BN / 8; ++c) {
-                float e[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) e[i] = ex2(fmaf(sc[c * 8 + i], p.scale_log2, -m_safe));
-                l0 += e[0] + e[4]; l1 += e[1] + e[5]; l2 += e[2] + e[6]; l3 += e[3] + e[7];
-                unsigned hi[4], lo[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const __nv_bfloat162 h2 = __floats2bfloat162_rn(e[2 * i], e[2 * i + 1]);
-                    const float2 back = __bfloat1622float2(h2);
-                    hi[i] = *reinterpret_cast<const unsigned*>(&h2);
-                    lo[i] = pack_bf16(e[2 * i] - back.x, e[2 * i + 1] - back.y);
-                }
-                // chunk c of this row: 64-key block c / 8, 16-byte chunk c % 8, swizzled with the row
-                unsigned char* at = prow + (c >> 3) * HALF_BYTES + (((c & 7) ^ (r & 7)) << 4);
-                *reinterpret_cast<uint4*>(at) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<uint4*>(at + P_BYTES) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
             }
             l += (l0 + l1) + (l2 + l3);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads what threads wrote
+            tmem_st<32>(lane_addr + COL_S + sb * BN + half * (HN / 2), hi);
+            tmem_st<32>(lane_addr + COL_S + sb * BN + BN / 2 + half * (HN / 2), lo);
+            tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full);
         }
         if (ok && n_tiles > 0) ok = mbar_wait(&pv_done, (n_tiles - 1) & 1, failed);
         ok = __all_sync(0xffffffffu, ok);
+        // the row's sum is the two halves' (both warps of a pair come here, failed or not), in the slot
+        // that the last tile did not use: the partner has read that one before the last tile's barrier
+        float (&swap_sum)[2][BM] = swap_max[n_tiles & 1];
+        swap_sum[half][r] = l;
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
+        l += swap_sum[half ^ 1][r];
         if (!ok) {
             if (lane == 0) {
                 failed_flag = 1;
@@ -441,11 +522,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
         } else {
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            __nv_bfloat16* orow = p.out + ((size_t)(qs + tok0 + r) * p.n_heads + head) * HD;
+            __nv_bfloat16* orow = p.out + ((size_t)(qs + tok0 + r) * p.n_heads + head) * HD + half * HO;
 #pragma unroll
-            for (int c = 0; c < HD / 32; ++c) {
+            for (int c = 0; c < HO / 32; ++c) {
                 unsigned v[32];
-                tmem_ld32(lane_addr + COL_O + c * 32, v);     // every lane takes part in the load
+                tmem_ld32(lane_addr + COL_O + half * HO + c * 32, v);     // every lane takes part in the load
                 tmem_wait_ld();
                 if (valid) {
 #pragma unroll
@@ -463,7 +544,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == W_ISSUE) {
         __syncwarp();
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
@@ -489,8 +570,7 @@ EncodeTiledFn encode_tiled() {
 }
 
 // rows x cols bfloat16, row-major; box = box_rows x 64 elements, 128-byte swizzle, zero fill outside.
-// Maps are kept per (pointer, rows, cols, box): page tensors live as long as the engine, and the
-// query buffer of a recorded step keeps its address.
+// Maps are kept per (pointer, rows, cols, box): page tensors live as long as the engine.
 int tiled_map(CUtensorMap* out, const void* base, long long rows, long long cols, int box_rows) {
     static std::map<std::tuple<const void*, long long, long long, int>, CUtensorMap> cache;
     static std::mutex lock;
@@ -518,10 +598,12 @@ int tiled_map(CUtensorMap* out, const void* base, long long rows, long long cols
     return TL_OK;
 }
 
-template <int HD> constexpr int stages_for() { return HD == 128 ? 2 : 3; }
+template <int HD> constexpr int stages_for() { return HD == 128 ? 3 : 4; }
 template <int HD> constexpr size_t smem_for() {
-    return (size_t)(HD / 64) * BN * 128 + 2 * 2 * BN * 128 + (size_t)stages_for<HD>() * 2 * (HD / 64) * BN * 128 + 1024;
+    return (size_t)stages_for<HD>() * 2 * (HD / 64) * BN * 128 + sizeof(Tail<stages_for<HD>()>);
 }
+static_assert(smem_for<128>() <= 227 * 1024 && smem_for<64>() <= 227 * 1024, "a CTA has 227 KB of shared memory");
+static_assert(COL_O + 128 + 64 <= TMEM_COLS, "scores, accumulator and queries must fit the tensor memory of a CTA");
 
 bool takes(int n_heads, int n_kv_heads, int head_dim, int page_size) {
     if (head_dim != 64 && head_dim != 128) return false;
@@ -530,7 +612,7 @@ bool takes(int n_heads, int n_kv_heads, int head_dim, int page_size) {
 }
 
 template <int HD>
-int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, dim3 grid, cudaStream_t s) {
+int launch(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, dim3 grid, cudaStream_t s) {
     constexpr size_t smem = smem_for<HD>();
     auto kern = attention_prefill_kernel<HD, stages_for<HD>()>;
     static bool raised = false;
@@ -539,7 +621,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
-    return (int)tl_launch(kern, grid, dim3(NTHREADS), smem, s, mq, mk, mv, p);
+    return (int)tl_launch(kern, grid, dim3(NTHREADS), smem, s, mk, mv, p);
 }
 
 }  // namespace
@@ -563,6 +645,7 @@ extern "C" int tl_paged_attention_prefill(const void* q, const void* k_pages, co
     if (n_seqs > 65535 || n_heads > 65535) return TL_BAD_SIZE;
 
     PrefillParams p;
+    p.q = (const __nv_bfloat16*)q;
     p.out = (__nv_bfloat16*)out;
     p.block_table = block_table; p.q_start = q_start; p.kv_len = kv_len; p.table_stride = table_stride;
     p.status = status;
@@ -576,15 +659,13 @@ extern "C" int tl_paged_attention_prefill(const void* q, const void* k_pages, co
     p.scale_log2 = scale * LOG2E;
 
     const long long rows = n_pages * n_kv_heads * page_size;
-    CUtensorMap mq, mk, mv;
-    int rc = tiled_map(&mq, q, q_rows, (long long)n_heads * head_dim, BM);
-    if (rc != TL_OK) return rc;
-    rc = tiled_map(&mk, k_pages, rows, head_dim, p.box_rows);
+    CUtensorMap mk, mv;
+    int rc = tiled_map(&mk, k_pages, rows, head_dim, p.box_rows);
     if (rc != TL_OK) return rc;
     rc = tiled_map(&mv, v_pages, rows, head_dim, p.box_rows);
     if (rc != TL_OK) return rc;
 
     dim3 grid(p.n_q_tiles, n_heads, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;
-    return head_dim == 128 ? launch<128>(mq, mk, mv, p, grid, s) : launch<64>(mq, mk, mv, p, grid, s);
+    return head_dim == 128 ? launch<128>(mk, mv, p, grid, s) : launch<64>(mk, mv, p, grid, s);
 }
