@@ -46,16 +46,17 @@
 
 namespace {
 
-constexpr int BM = 128;                 // query rows (tokens) per CTA
+constexpr int BM = 128;                 // rows of a query tile (tokens of one head)
+constexpr int QT = 2;                   // query tiles per CTA: they share every K and V tile that is loaded
 constexpr int BN = 128;                 // keys per tile
-constexpr int NTHREADS = 320;
-constexpr int W_ISSUE = 8, W_COPY = 9;   // warps 0-7 are the softmax
+constexpr int NTHREADS = 352;
+constexpr int W_COPY = 8, W_ISSUE = 9;   // warps 0-7 are the softmax, warp 8 copies, warps 9 and 10 issue
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LAG = 8.f;              // how far (in powers of two) the maximum in use may lag
 constexpr unsigned long long WAIT_NS = 2000ull * 1000ull * 1000ull;
 enum : int { ERR_PRODUCER_WAIT = 301, ERR_ISSUER_WAIT = 302, ERR_SOFTMAX_WAIT = 303, ERR_BAD_COPY = 304 };
 constexpr unsigned TMEM_COLS = 512;     // two score buffers of 128 columns, the accumulator, the queries
-constexpr unsigned COL_S = 0, COL_O = 256;
+constexpr unsigned COL_S = 0, COL_O = 256;     // scores (then probabilities) of tile t at COL_S + 128 t, its accumulator at COL_O + 128 t
 
 struct PrefillParams {
     const __nv_bfloat16* q;
@@ -67,7 +68,7 @@ struct PrefillParams {
     int table_stride;
     int n_heads, n_kv_heads, page_size, page_shift, box_rows;
     int total_rows;             // rows of the page tensor: a copy that starts there reads only the zero fill
-    int n_q_tiles;
+    int n_q_blocks;             // blocks of QT query tiles
     int window;
     float scale_log2;
 };
@@ -137,6 +138,13 @@ __device__ __forceinline__ unsigned long long desc_mn_major(unsigned addr, unsig
 __host__ __device__ constexpr unsigned idesc(int n, unsigned a_fmt, unsigned b_fmt, unsigned b_mn_major) {
     return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (b_mn_major << 16) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
 }
+// D[tmem] (+)= A[shared] . B[shared]
+__device__ __forceinline__ void umma_ss(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
+                                        unsigned id, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(id), "r"(accumulate) : "memory");
+}
 // D[tmem] (+)= A[tmem] . B[shared]: the left operand lies in tensor memory, row = lane, two 16-bit
 // elements of K to a column
 __device__ __forceinline__ void umma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long b_desc,
@@ -157,21 +165,13 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr));
 }
-template <int N> __device__ __forceinline__ void tmem_st(unsigned taddr, const unsigned (&r)[N]);
-template <> __device__ __forceinline__ void tmem_st<32>(unsigned taddr, const unsigned (&r)[32]) {
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                  "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
                  ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
                    "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
                    "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
                    "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-                 : "memory");
-}
-template <> __device__ __forceinline__ void tmem_st<16>(unsigned taddr, const unsigned (&r)[16]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
                  : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -191,10 +191,15 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 template <int STAGES>
 struct Tail {                   // what lies behind the tiles in shared memory
     unsigned long long q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-    unsigned long long s_full[2], p_full, pv_done;
+    unsigned long long s_full[QT], p_full[QT], pv_done[QT];
     unsigned tmem_base_slot;
     int failed_flag;
-    float swap[2][2][BM];       // [tile parity][half][row]
+    float swap[2][2][BM];       // [parity of the softmax's step][half][row]
+};
+
+// What a query tile has to do with the CTA's key tiles: it works on tiles first .. last - 1.
+struct TileRange {
+    int rows, first, last;
 };
 
 template <int HD, int STAGES>
@@ -203,22 +208,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
                                                                        const PrefillParams p) {
     constexpr int HALVES = HD / 64;                      // 64-element (128-byte) column blocks of a row
     constexpr unsigned HALF_BYTES = BN * 128;            // one [128 rows x 128 B] block
-    constexpr unsigned KV_BYTES = HALVES * HALF_BYTES;   // K (or V) of a tile
-    constexpr unsigned COL_Q = COL_O + HD;               // Q as bfloat16 pairs: HD / 2 columns
-    // All shared memory is dynamic and laid out by hand: the K and V rings first (they need
-    // 1024-byte alignment for the 128-byte swizzle, which the start of the window has; the producer
-    // checks), then the barriers and the little that threads exchange.
+    constexpr unsigned KV_BYTES = HALVES * HALF_BYTES;   // K (or V) of a tile; a query tile has the same layout
+    // All shared memory is dynamic and laid out by hand: the two query tiles and the K and V rings
+    // first (they need 1024-byte alignment for the 128-byte swizzle, which the start of the window
+    // has; the producer checks), then the barriers and the little that threads exchange.
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    unsigned char* tiles = smem_raw;
+    unsigned char* Qs = smem_raw;                        // [QT] query tiles
+    unsigned char* tiles = Qs + QT * KV_BYTES;           // K ring, then V ring
     Tail<STAGES>& tail = *reinterpret_cast<Tail<STAGES>*>(tiles + 2 * STAGES * KV_BYTES);
     unsigned long long& q_full = tail.q_full;
     unsigned long long (&k_full)[STAGES] = tail.k_full;
     unsigned long long (&k_empty)[STAGES] = tail.k_empty;
     unsigned long long (&v_full)[STAGES] = tail.v_full;
     unsigned long long (&v_empty)[STAGES] = tail.v_empty;
-    unsigned long long (&s_full)[2] = tail.s_full;
-    unsigned long long& p_full = tail.p_full;
-    unsigned long long& pv_done = tail.pv_done;
+    unsigned long long (&s_full)[QT] = tail.s_full;
+    unsigned long long (&p_full)[QT] = tail.p_full;
+    unsigned long long (&pv_done)[QT] = tail.pv_done;
     unsigned& tmem_base_slot = tail.tmem_base_slot;
     int& failed_flag = tail.failed_flag;
     float (&swap_max)[2][2][BM] = tail.swap;                 // the two halves of a row tell each other their maximum
@@ -229,14 +234,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
         mbar_init(&q_full, 8);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&k_full[s], 1);
-            mbar_init(&k_empty[s], 1);
+            mbar_init(&k_empty[s], QT);       // every query tile's issuer lets go of a stage
             mbar_init(&v_full[s], 1);
-            mbar_init(&v_empty[s], 1);
+            mbar_init(&v_empty[s], QT);
         }
-        mbar_init(&s_full[0], 1);
-        mbar_init(&s_full[1], 1);
-        mbar_init(&p_full, 8);
-        mbar_init(&pv_done, 1);
+        for (int t = 0; t < QT; ++t) {
+            mbar_init(&s_full[t], 1);
+            mbar_init(&p_full[t], 8);
+            mbar_init(&pv_done[t], 1);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == W_ISSUE) {
@@ -257,22 +263,32 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
     const int qs = p.q_start[b];
     const int ql = p.q_start[b + 1] - qs;
     const int kl = p.kv_len[b];
-    const int tok0 = (p.n_q_tiles - 1 - (int)blockIdx.x) * BM;      // the tiles with most keys start first
+    const int tok0 = (p.n_q_blocks - 1 - (int)blockIdx.x) * (QT * BM);      // the blocks with most keys start first
     const bool active = tok0 < ql;
     const int qpos_base = kl - ql;
-    const int rows = active ? min(BM, ql - tok0) : 0;
-    // keys this tile can see: from the window's start of its first row to its last row's own position
-    const int k_lo = p.window > 0 ? max(0, qpos_base + tok0 - p.window + 1) : 0;
-    const int k_hi = qpos_base + tok0 + rows;
-    const int k_start = k_lo & ~(BN - 1);
-    const int n_tiles = active ? (k_hi - k_start + BN - 1) / BN : 0;
+    // Keys the CTA walks: from the window's start of its first row to its last row's own position, in
+    // tiles of 128 counted from k_start.  Each query tile takes part in the key tiles it can see.
+    const int k_start = (p.window > 0 ? max(0, qpos_base + tok0 - p.window + 1) : 0) & ~(BN - 1);
+    TileRange range[QT];
+    int n_tiles = 0;
+#pragma unroll
+    for (int t = 0; t < QT; ++t) {
+        const int t0 = tok0 + t * BM;
+        const int rows = active ? max(0, min(BM, ql - t0)) : 0;
+        const int lo = p.window > 0 ? max(0, qpos_base + t0 - p.window + 1) : 0;
+        range[t].rows = rows;
+        range[t].first = rows > 0 ? ((lo & ~(BN - 1)) - k_start) / BN : 0;
+        range[t].last = rows > 0 ? (qpos_base + t0 + rows - k_start + BN - 1) / BN : 0;
+        n_tiles = max(n_tiles, range[t].last);
+    }
+    const int k_hi = qpos_base + min(ql, tok0 + QT * BM);    // one past the last key anybody here sees
 
     if (warp == W_COPY) {
         if (active) {
             // ---- producer (the whole warp: lanes look pages up and issue copies side by side).
             // K and V have rings of their own: a K stage is free as soon as the scores of its tile
             // are computed, long before the V stage of the same tile.
-            bool sound = (smem_u32(tiles) & 1023u) == 0u;
+            bool sound = (smem_u32(Qs) & 1023u) == 0u;
             if (!sound && lane == 0) {
                 failed_flag = 1;
                 atomicExch(p.status, ERR_BAD_COPY);
@@ -321,61 +337,59 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
                 }
             }
         }
-    } else if (warp == W_ISSUE) {
+    } else if (warp >= W_ISSUE) {
         if (lane == 0 && active) {
-            // ---- issuer.  Two queues, scores S_j = Q K_j^T and products O += P_j V_j; whichever has
-            // its inputs is issued, scores first.  The left operand of both comes from tensor memory
-            // (Q, and the probabilities where the scores of their tile were), so shared memory is read
-            // for K and V only.  S_{j+2} goes where P_j lies: it is issued after O += P_j V_j, and
-            // products issued by one thread run in order.
+            // ---- issuers, one per query tile (warp W_ISSUE + t).  For every key tile its query tile
+            // takes part in: scores S_j = Q K_j^T, then, once the softmax has put the probabilities
+            // where the scores were, the product O += P_j V_j with the probabilities read from tensor
+            // memory.  The two tiles' chains do not depend on each other: while one issuer waits for its
+            // softmax, the other keeps the tensor core busy.  A stage of K or V is released by both.
             constexpr unsigned id_s = idesc(BN, 1u, 1u, 0u);     // bf16 x bf16, K as stored (K-major)
             constexpr unsigned id_o = idesc(HD, 1u, 1u, 1u);     // bf16 probabilities x bf16 values as stored (MN-major)
+            const int t = warp - W_ISSUE;
+            const int first = t ? range[1].first : range[0].first, last = t ? range[1].last : range[0].last;
             bool ok = mbar_wait(&q_full, 0, failed);
             tc_fence_after();
-            int ns = 0, npv = 0;
-            unsigned long long t0 = 0;
-            unsigned spins = 0;
-            while (ok && npv < n_tiles) {
-                bool did = false;
-                if (ns < n_tiles && ns < npv + 2) {
-                    const int s = ns % STAGES, sb = ns & 1;
-                    if (mbar_try_wait(&k_full[s], (ns / STAGES) & 1)) {
-                        tc_fence_after();
-                        const unsigned ka = smem_u32(tiles + s * KV_BYTES);
+            const unsigned long long qd0 = desc_k_major(smem_u32(Qs + t * KV_BYTES));
+            const unsigned d_s = tmem + COL_S + t * BN, d_o = tmem + COL_O + t * BN;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % STAGES;
+                const unsigned ring = (j / STAGES) & 1;
+                const bool mine = j >= first && j < last;
+                ok = mbar_wait(&k_full[s], ring, failed);
+                if (!ok) break;
+                if (mine) {
+                    tc_fence_after();
+                    // (the address is the low field of a descriptor, in units of 16 bytes: moving
+                    // along K is an addition to the descriptor as a whole)
+                    const unsigned long long kd0 = desc_k_major(smem_u32(tiles + s * KV_BYTES));
 #pragma unroll
-                        for (int kd = 0; kd < HD / 16; ++kd)
-                            umma_ts(tmem + COL_S + sb * BN, tmem + COL_Q + kd * 8,
-                                    desc_k_major(ka + (kd / 4) * HALF_BYTES + (kd % 4) * 32), id_s, kd > 0 ? 1u : 0u);
-                        umma_commit(&s_full[sb]);
-                        umma_commit(&k_empty[s]);        // the K stage is free once the scores are computed
-                        ++ns;
-                        did = true;
+                    for (int kd = 0; kd < HD / 16; ++kd) {
+                        const unsigned off = ((kd / 4) * HALF_BYTES + (kd % 4) * 32) >> 4;
+                        umma_ss(d_s, qd0 + off, kd0 + off, id_s, kd > 0 ? 1u : 0u);
                     }
+                    umma_commit(&s_full[t]);
+                    umma_commit(&k_empty[s]);        // this tile is done with the K stage once its scores are computed
+                } else {
+                    mbar_arrive(&k_empty[s]);        // not this tile's keys: nothing to wait for
                 }
-                if (!did && npv < ns) {
-                    const int s = npv % STAGES, sb = npv & 1;
-                    if (mbar_try_wait(&p_full, npv & 1) && mbar_try_wait(&v_full[s], (npv / STAGES) & 1)) {
-                        tc_fence_after();
-                        const unsigned va = smem_u32(tiles + (STAGES + s) * KV_BYTES);
+                if (mine) ok = mbar_wait(&p_full[t], (j - first) & 1, failed);
+                ok = ok && mbar_wait(&v_full[s], ring, failed);
+                if (!ok) break;
+                if (mine) {
+                    tc_fence_after();
+                    const unsigned long long vd0 = desc_mn_major(smem_u32(tiles + (STAGES + s) * KV_BYTES), HALF_BYTES);
+                    const unsigned acc = j > first ? 1u : 0u;
 #pragma unroll
-                        for (int part = 0; part < 2; ++part)             // value, then remainder
+                    for (int part = 0; part < 2; ++part)             // value, then remainder
 #pragma unroll
-                            for (int kk = 0; kk < BN / 16; ++kk)
-                                umma_ts(tmem + COL_O, tmem + COL_S + sb * BN + part * (BN / 2) + kk * 8,
-                                        desc_mn_major(va + kk * 2048, HALF_BYTES), id_o, (npv > 0 || part > 0 || kk > 0) ? 1u : 0u);
-                        umma_commit(&v_empty[s]);        // the V stage is free once these products have read it
-                        umma_commit(&pv_done);           // the accumulator is up to date
-                        ++npv;
-                        did = true;
-                    }
-                }
-                if (did) {
-                    spins = 0;
-                } else if ((++spins & 1023u) == 0u) {
-                    unsigned long long t1;
-                    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
-                    if (spins == 1024u) t0 = t1;
-                    if (*failed || t1 - t0 > WAIT_NS) ok = false;
+                        for (int kk = 0; kk < BN / 16; ++kk)         // 16 keys on: 2048 bytes of V, 8 columns of P
+                            umma_ts(d_o, d_s + part * (BN / 2) + kk * 8, vd0 + kk * (2048 >> 4), id_o,
+                                    (part > 0 || kk > 0) ? 1u : acc);
+                    umma_commit(&pv_done[t]);        // the accumulator is up to date
+                    umma_commit(&v_empty[s]);        // and this tile is done with the V stage
+                } else {
+                    mbar_arrive(&v_empty[s]);
                 }
             }
             if (!ok) {
@@ -384,136 +398,164 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
             }
         }
     } else if (active) {
-        // ---- softmax: row r = TMEM lane r; this thread has its keys 64 half .. 64 half + 63 of every tile
+        // ---- softmax: row r = TMEM lane r of either query tile; this thread has the keys
+        // 64 half .. 64 half + 63 of every key tile
         constexpr int HN = BN / 2;                           // keys per thread and tile
         constexpr int HO = HD / 2;                           // accumulator columns per thread
         const int half = warp >> 2;
         const int r = (warp & 3) * 32 + lane;
         const unsigned lane_addr = tmem + ((unsigned)((warp & 3) * 32) << 16);
-        const bool valid = r < rows;
-        const int qpos = qpos_base + tok0 + (valid ? r : rows - 1);      // idle rows follow the last real one
-        const int tile_qmin = qpos_base + tok0;
         const int pair_barrier = 1 + (warp & 3);             // named barrier of the two warps that share 32 rows
-        // this thread's half of its query row goes into tensor memory, two bfloat16 to a column
-        {
-            unsigned qw[HO / 2];
-            const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + tok0 + r) * p.n_heads + head) * HD + half * HO);
+        // this thread's half of its query rows goes into shared memory in the layout of a K tile:
+        // rows of 128 bytes (64 elements), 16-byte chunks swizzled with the row
+#pragma unroll
+        for (int t = 0; t < QT; ++t) {
+            const bool valid = r < range[t].rows;
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + tok0 + t * BM + r) * p.n_heads + head) * HD + half * HO);
 #pragma unroll
             for (int i = 0; i < HO / 8; ++i) {
                 const uint4 v = valid ? src[i] : make_uint4(0u, 0u, 0u, 0u);
-                qw[4 * i] = v.x; qw[4 * i + 1] = v.y; qw[4 * i + 2] = v.z; qw[4 * i + 3] = v.w;
+                const int chunk = (half * HO) / 8 + i;              // of the row: block chunk / 8, chunk % 8 within it
+                *reinterpret_cast<uint4*>(Qs + t * KV_BYTES + (chunk >> 3) * HALF_BYTES + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) = v;
             }
-            tmem_st<HO / 2>(lane_addr + COL_Q + half * (HO / 2), qw);
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&q_full);
         }
-        float m_used = -INFINITY, l = 0.f;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads what threads wrote
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&q_full);
+
+        // The state of the two query tiles lives in scalars picked by hand, and the loop over the
+        // tiles is not unrolled: one copy of the body, no indexed arrays, fewer registers.
+        static_assert(QT == 2, "the softmax keeps the state of two query tiles");
+        float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+        const int rows_a = range[0].rows, rows_b = range[1].rows;
+        const int first_a = range[0].first, first_b = range[1].first, last_a = range[0].last, last_b = range[1].last;
         bool ok = true;
+        int step = 0;                                        // counts the (key tile, query tile) pairs done: slot of the swap
         // Once a wait has failed (ok = false) the loop only keeps its appointments at the pair's
-        // barrier: both warps of a pair pass it once per tile whatever happens, so neither can be
+        // barrier: both warps of a pair pass it once per step whatever happens, so neither can be
         // left waiting there.
         for (int j = 0; j < n_tiles; ++j) {
-            const int sb = j & 1;
-            // (a wait's verdict is taken by the whole warp: the loads below need all of its lanes)
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (j >> 1) & 1, failed));
-            if (!ok) failed_flag = 1;
-            unsigned raw[HN];                                // the scores
-            float mine = -INFINITY;
             const int k0 = k_start + j * BN;
-            if (ok) {
-                tc_fence_after();
+#pragma unroll 1
+            for (int t = 0; t < QT; ++t) {
+                const int first = t ? first_b : first_a, last = t ? last_b : last_a, rows = t ? rows_b : rows_a;
+                if (j < first || j >= last) continue;
+                const int it = j - first;                    // how many tiles this query tile has done
+                const int slot = step & 1;
+                ++step;
+                float m_used = t ? m_b : m_a;
+                const int t0 = qpos_base + tok0 + t * BM;    // position of the tile's first row
+                const int qpos = t0 + (r < rows ? r : rows - 1);         // idle rows follow the last real one
+                const unsigned col_s = COL_S + t * BN, col_o = COL_O + t * BN;
+                // (a wait's verdict is taken by the whole warp: the loads below need all of its lanes)
+                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], it & 1, failed));
+                if (!ok) failed_flag = 1;
+                unsigned raw[HN];                            // the scores
+                float mine = -INFINITY;
+                if (ok) {
+                    tc_fence_after();
 #pragma unroll
-                for (int c = 0; c < HN / 32; ++c)
-                    tmem_ld32(lane_addr + COL_S + sb * BN + half * HN + c * 32, *reinterpret_cast<unsigned(*)[32]>(&raw[c * 32]));
-                tmem_wait_ld();
-                // the whole tile is visible to every row of this CTA?
-                const bool clear = k0 + BN - 1 <= tile_qmin && k0 >= k_lo &&
-                                   (p.window <= 0 || k0 > qpos_base + tok0 + rows - 1 - p.window);
-                if (!clear) {
+                    for (int c = 0; c < HN / 32; ++c)
+                        tmem_ld32(lane_addr + col_s + half * HN + c * 32, *reinterpret_cast<unsigned(*)[32]>(&raw[c * 32]));
+                    tmem_wait_ld();
+                    // the whole key tile is visible to every row of this query tile?
+                    const bool clear = k0 + BN - 1 <= t0 && (p.window <= 0 || k0 > t0 + rows - 1 - p.window);
+                    if (!clear) {
 #pragma unroll
-                    for (int i = 0; i < HN; ++i) {
-                        const int kpos = k0 + half * HN + i;
-                        const bool vis = kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
-                        if (!vis) raw[i] = 0xff800000u;      // -inf
+                        for (int i = 0; i < HN; ++i) {
+                            const int kpos = k0 + half * HN + i;
+                            const bool vis = kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
+                            if (!vis) raw[i] = 0xff800000u;  // -inf
+                        }
+                    }
+                    float mx0 = __uint_as_float(raw[0]), mx1 = __uint_as_float(raw[1]);
+                    float mx2 = __uint_as_float(raw[2]), mx3 = __uint_as_float(raw[3]);
+#pragma unroll
+                    for (int i = 4; i < HN; i += 4) {
+                        mx0 = fmaxf(mx0, __uint_as_float(raw[i])); mx1 = fmaxf(mx1, __uint_as_float(raw[i + 1]));
+                        mx2 = fmaxf(mx2, __uint_as_float(raw[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(raw[i + 3]));
+                    }
+                    mine = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+                }
+                // The partner can be one step ahead at most (it stops at the next barrier until this
+                // thread gets there), so two slots, used in turn, are never overwritten unread.  Past the
+                // barrier both have their scores in registers: the probabilities may go where they were.
+                swap_max[slot][half][r] = mine;
+                asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
+                if (!ok) continue;
+                const float both = fmaxf(mine, swap_max[slot][half ^ 1][r]);
+                const float m_new = fmaxf(m_used, both * p.scale_log2);
+                const bool grow = m_new > m_used + LAG;      // also true for the first keys a row sees
+                const bool rescale = it > 0 && __any_sync(0xffffffffu, grow);
+                const float alpha = grow ? ex2(m_used - m_new) : 1.f;        // 0 for a row that had seen nothing
+                if (grow) m_used = m_new;
+                const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;   // nothing seen yet: keep exponents finite
+                // probabilities as value + remainder, two bfloat16 to a column: columns 32 half .. of the
+                // tile's buffer hold the values of this thread's keys, columns 64 + 32 half .. the remainders
+                unsigned hi[HN / 2], lo[HN / 2];
+                float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < HN; i += 4) {
+                    const float e0 = ex2(fmaf(__uint_as_float(raw[i]), p.scale_log2, -m_safe));
+                    const float e1 = ex2(fmaf(__uint_as_float(raw[i + 1]), p.scale_log2, -m_safe));
+                    const float e2 = ex2(fmaf(__uint_as_float(raw[i + 2]), p.scale_log2, -m_safe));
+                    const float e3 = ex2(fmaf(__uint_as_float(raw[i + 3]), p.scale_log2, -m_safe));
+                    l0 += e0; l1 += e1; l2 += e2; l3 += e3;
+                    const __nv_bfloat162 ha = __floats2bfloat162_rn(e0, e1), hb = __floats2bfloat162_rn(e2, e3);
+                    const float2 ba = __bfloat1622float2(ha), bb = __bfloat1622float2(hb);
+                    hi[i / 2] = *reinterpret_cast<const unsigned*>(&ha);
+                    hi[i / 2 + 1] = *reinterpret_cast<const unsigned*>(&hb);
+                    lo[i / 2] = pack_bf16(e0 - ba.x, e1 - ba.y);
+                    lo[i / 2 + 1] = pack_bf16(e2 - bb.x, e3 - bb.y);
+                }
+                float l_sum = (t ? l_b : l_a);
+                if (rescale) {
+                    // the product that last wrote the accumulator must be over
+                    ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[t], (it - 1) & 1, failed));
+                    if (!ok) {
+                        failed_flag = 1;
+                        continue;
+                    }
+                    tc_fence_after();
+                    l_sum *= alpha;
+#pragma unroll
+                    for (int c = 0; c < HO / 32; ++c) {
+                        unsigned v[32];
+                        tmem_ld32(lane_addr + col_o + half * HO + c * 32, v);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                        tmem_st32(lane_addr + col_o + half * HO + c * 32, v);
                     }
                 }
-                float mx0 = __uint_as_float(raw[0]), mx1 = __uint_as_float(raw[1]);
-                float mx2 = __uint_as_float(raw[2]), mx3 = __uint_as_float(raw[3]);
-#pragma unroll
-                for (int i = 4; i < HN; i += 4) {
-                    mx0 = fmaxf(mx0, __uint_as_float(raw[i])); mx1 = fmaxf(mx1, __uint_as_float(raw[i + 1]));
-                    mx2 = fmaxf(mx2, __uint_as_float(raw[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(raw[i + 3]));
-                }
-                mine = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+                l_sum += (l0 + l1) + (l2 + l3);
+                if (t) { m_b = m_used; l_b = l_sum; } else { m_a = m_used; l_a = l_sum; }
+                tmem_st32(lane_addr + col_s + half * (HN / 2), hi);
+                tmem_st32(lane_addr + col_s + BN / 2 + half * (HN / 2), lo);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[t]);
             }
-            // The partner can be one tile ahead at most (it stops at the next barrier until this
-            // thread gets there), so two slots, used in turn, are never overwritten unread.  Past the
-            // barrier both have their scores in registers: the probabilities may go where they were.
-            swap_max[sb][half][r] = mine;
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
-            if (!ok) continue;
-            const float both = fmaxf(mine, swap_max[sb][half ^ 1][r]);
-            const float m_new = fmaxf(m_used, both * p.scale_log2);
-            const bool grow = m_new > m_used + LAG;          // also true for the first keys a row sees
-            const bool rescale = j > 0 && __any_sync(0xffffffffu, grow);
-            const float alpha = grow ? ex2(m_used - m_new) : 1.f;        // 0 for a row that had seen nothing
-            if (grow) m_used = m_new;
-            const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;   // nothing seen yet: keep exponents finite
-            // probabilities as value + remainder, two bfloat16 to a column: columns 32 half .. of the
-            // tile's buffer hold the values of this thread's keys, columns 64 + 32 half .. the remainders
-            unsigned hi[HN / 2], lo[HN / 2];
-            float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-#pragma unroll
-            for (int i = 0; i < HN; i += 4) {
-                const float e0 = ex2(fmaf(__uint_as_float(raw[i]), p.scale_log2, -m_safe));
-                const float e1 = ex2(fmaf(__uint_as_float(raw[i + 1]), p.scale_log2, -m_safe));
-                const float e2 = ex2(fmaf(__uint_as_float(raw[i + 2]), p.scale_log2, -m_safe));
-                const float e3 = ex2(fmaf(__uint_as_float(raw[i + 3]), p.scale_log2, -m_safe));
-                l0 += e0; l1 += e1; l2 += e2; l3 += e3;
-                const __nv_bfloat162 ha = __floats2bfloat162_rn(e0, e1), hb = __floats2bfloat162_rn(e2, e3);
-                const float2 ba = __bfloat1622float2(ha), bb = __bfloat1622float2(hb);
-                hi[i / 2] = *reinterpret_cast<const unsigned*>(&ha);
-                hi[i / 2 + 1] = *reinterpret_cast<const unsigned*>(&hb);
-                lo[i / 2] = pack_bf16(e0 - ba.x, e1 - ba.y);
-                lo[i / 2 + 1] = pack_bf16(e2 - bb.x, e3 - bb.y);
-            }
-            if (rescale) {
-                // the product that last wrote the accumulator must be over
-                ok = __all_sync(0xffffffffu, mbar_wait(&pv_done, (j - 1) & 1, failed));
-                if (!ok) {
-                    failed_flag = 1;
-                    continue;
-                }
-                tc_fence_after();
-                l *= alpha;
-#pragma unroll
-                for (int c = 0; c < HO / 32; ++c) {
-                    unsigned v[32];
-                    tmem_ld32(lane_addr + COL_O + half * HO + c * 32, v);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                    tmem_st<32>(lane_addr + COL_O + half * HO + c * 32, v);
-                }
-            }
-            l += (l0 + l1) + (l2 + l3);
-            tmem_st<32>(lane_addr + COL_S + sb * BN + half * (HN / 2), hi);
-            tmem_st<32>(lane_addr + COL_S + sb * BN + BN / 2 + half * (HN / 2), lo);
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full);
         }
-        if (ok && n_tiles > 0) ok = mbar_wait(&pv_done, (n_tiles - 1) & 1, failed);
+        float l[QT] = {l_a, l_b};
+        // ---- the end: wait for the last products, add the two halves' sums, divide, store
+#pragma unroll
+        for (int t = 0; t < QT; ++t) {
+            const int n = range[t].last - range[t].first;
+            if (ok && n > 0) ok = mbar_wait(&pv_done[t], (n - 1) & 1, failed);
+        }
         ok = __all_sync(0xffffffffu, ok);
-        // the row's sum is the two halves' (both warps of a pair come here, failed or not), in the slot
-        // that the last tile did not use: the partner has read that one before the last tile's barrier
-        float (&swap_sum)[2][BM] = swap_max[n_tiles & 1];
-        swap_sum[half][r] = l;
+        // (both warps of a pair come here, failed or not; the slot is the one the last step did not
+        // use: the partner has read that one before it came to the last step's barrier)
+        float (&swap_sum)[2][BM] = swap_max[step & 1];
+        float (&swap_sum2)[2][BM] = swap_max[(step & 1) ^ 1];
+        swap_sum[half][r] = l[0];
         asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
-        l += swap_sum[half ^ 1][r];
+        l[0] += swap_sum[half ^ 1][r];
+        swap_sum2[half][r] = l[1];
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
+        l[1] += swap_sum2[half ^ 1][r];
         if (!ok) {
             if (lane == 0) {
                 failed_flag = 1;
@@ -521,22 +563,27 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
             }
         } else {
             tc_fence_after();
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            __nv_bfloat16* orow = p.out + ((size_t)(qs + tok0 + r) * p.n_heads + head) * HD + half * HO;
 #pragma unroll
-            for (int c = 0; c < HO / 32; ++c) {
-                unsigned v[32];
-                tmem_ld32(lane_addr + COL_O + half * HO + c * 32, v);     // every lane takes part in the load
-                tmem_wait_ld();
-                if (valid) {
+            for (int t = 0; t < QT; ++t) {
+                if (range[t].rows == 0) continue;
+                const bool valid = r < range[t].rows;
+                const float inv = l[t] > 0.f ? 1.f / l[t] : 0.f;
+                __nv_bfloat16* orow = p.out + ((size_t)(qs + tok0 + t * BM + r) * p.n_heads + head) * HD + half * HO;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint4 w;
-                        w.x = pack_bf16(__uint_as_float(v[8 * i]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
-                        w.y = pack_bf16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
-                        w.z = pack_bf16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
-                        w.w = pack_bf16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = w;
+                for (int c = 0; c < HO / 32; ++c) {
+                    unsigned v[32];
+                    tmem_ld32(lane_addr + COL_O + t * BN + half * HO + c * 32, v);     // every lane takes part in the load
+                    tmem_wait_ld();
+                    if (valid) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint4 w;
+                            w.x = pack_bf16(__uint_as_float(v[8 * i]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
+                            w.y = pack_bf16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
+                            w.z = pack_bf16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
+                            w.w = pack_bf16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+                            *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = w;
+                        }
                     }
                 }
             }
@@ -598,12 +645,12 @@ int tiled_map(CUtensorMap* out, const void* base, long long rows, long long cols
     return TL_OK;
 }
 
-template <int HD> constexpr int stages_for() { return HD == 128 ? 3 : 4; }
+template <int HD> constexpr int stages_for() { return HD == 128 ? 2 : 4; }
 template <int HD> constexpr size_t smem_for() {
-    return (size_t)stages_for<HD>() * 2 * (HD / 64) * BN * 128 + sizeof(Tail<stages_for<HD>()>);
+    return (size_t)(QT + 2 * stages_for<HD>()) * (HD / 64) * BN * 128 + sizeof(Tail<stages_for<HD>()>);
 }
 static_assert(smem_for<128>() <= 227 * 1024 && smem_for<64>() <= 227 * 1024, "a CTA has 227 KB of shared memory");
-static_assert(COL_O + 128 + 64 <= TMEM_COLS, "scores, accumulator and queries must fit the tensor memory of a CTA");
+static_assert(COL_O + QT * 128 <= TMEM_COLS && COL_S + QT * 128 <= COL_O, "scores and accumulators of the query tiles must fit the tensor memory of a CTA");
 
 bool takes(int n_heads, int n_kv_heads, int head_dim, int page_size) {
     if (head_dim != 64 && head_dim != 128) return false;
@@ -654,7 +701,7 @@ extern "C" int tl_paged_attention_prefill(const void* q, const void* k_pages, co
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.box_rows = page_size < BN ? page_size : BN;
     p.total_rows = (int)(n_pages * n_kv_heads * page_size);
-    p.n_q_tiles = (max_q_len + BM - 1) / BM;
+    p.n_q_blocks = (max_q_len + QT * BM - 1) / (QT * BM);
     p.window = window > 0 ? window : 0;
     p.scale_log2 = scale * LOG2E;
 
@@ -665,7 +712,7 @@ extern "C" int tl_paged_attention_prefill(const void* q, const void* k_pages, co
     rc = tiled_map(&mv, v_pages, rows, head_dim, p.box_rows);
     if (rc != TL_OK) return rc;
 
-    dim3 grid(p.n_q_tiles, n_heads, n_seqs);
+    dim3 grid(p.n_q_blocks, n_heads, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;
     return head_dim == 128 ? launch<128>(mk, mv, p, grid, s) : launch<64>(mk, mv, p, grid, s);
 }
