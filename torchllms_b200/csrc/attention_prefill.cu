@@ -3,31 +3,36 @@
 //
 // Same contract as the kernels in attention_mma.cu (causal, optional sliding window, grouped
 // heads, float32 scores / running maximum / sum / accumulator), other machinery: both products
-// are tcgen05.mma with accumulators in tensor memory, operands arrive by TMA, and a thread owns
-// a whole query row, so the softmax needs no exchange between threads.
+// are tcgen05.mma with accumulators in tensor memory, K and V arrive by TMA, and a query row
+// belongs to two threads that exchange one number per key tile.
 //
-// A CTA serves 128 consecutive tokens of one request and one query head (M = 128), walking the
-// visible keys in tiles of 128.  320 threads:
-//   warps 0-7      : softmax.  Row r = TMEM lane r belongs to two threads, one in warp r / 32 for
-//                    the tile's first 64 keys and one in warp 4 + r / 32 for the other 64 (a warp
-//                    reaches the lanes 32 (w mod 4) .. + 31 only).  At the start each puts its half
-//                    of the query row into tensor memory.  Per tile each reads its scores
-//                    (tcgen05.ld), masks, and the two swap their maxima through shared memory;
-//                    both then keep the same running maximum, a sum of their own, write their
-//                    probabilities back into tensor memory where the scores were (tcgen05.st),
-//                    rescale their half of the accumulator row when the maximum has grown, and at
-//                    the end divide it by the sum and store it.  No other exchange between threads.
-//   warp 8, lane 0 : issues the products.  S_j = Q K_j^T into one of two score buffers (so that
-//                    S_{j+1} is computed while the softmax works on S_j), then O += P_j V_j once
-//                    the probabilities are in place.  The left operand of both is read from
-//                    tensor memory: shared memory, whose bandwidth a product with both operands
-//                    there uses up, serves K and V only.
-//   warp 9         : TMA producer: per key tile one box per page (or per 128 rows of a larger
+// A CTA serves 256 consecutive tokens of one request and one query head as two query tiles of
+// 128 rows (M = 128 each), walking the visible keys in tiles of 128.  Every K and V tile that is
+// loaded serves both query tiles: the step is bound by what the SMs can pull out of L2 otherwise.
+// 352 threads:
+//   warps 0-7      : softmax, for one query tile after the other.  Row r = TMEM lane r belongs to
+//                    two threads, one in warp r / 32 for the key tile's first 64 keys and one in
+//                    warp 4 + r / 32 for the other 64 (a warp reaches the lanes 32 (w mod 4) ..
+//                    + 31 only).  At the start each writes its half of its query rows into shared
+//                    memory in the operand layout.  Per (key tile, query tile) each reads its
+//                    scores (tcgen05.ld), masks, and the two swap their maxima through shared
+//                    memory; both then keep the same running maximum, a sum of their own, write
+//                    their probabilities back into tensor memory where the scores were
+//                    (tcgen05.st), rescale their half of the accumulator row when the maximum has
+//                    grown, and at the end divide it by the sum and store it.
+//   warp 8         : TMA producer: per key tile one box per page (or per 128 rows of a larger
 //                    page) and 64-element column block of K and of V into 128-byte-swizzled
 //                    shared memory, each in a ring of its own; no multicast.
-// K is a K-major operand (rows of 128 bytes, swizzled); V is used as stored, keys x columns, as
-// an MN-major operand.  Probabilities are multiplied as value + remainder, both bfloat16 (two
-// products), so that the product keeps 16 bits of them, as in the other kernels.
+//   warps 9 and 10 : one lane each issues the products of one query tile: S_j = Q K_j^T, then,
+//                    once the probabilities are in place, O += P_j V_j with the probabilities
+//                    read from tensor memory.  While the softmax works on one query tile the
+//                    tensor core works for the other.  (One thread polling for both tiles left
+//                    the tensor core idle between its turns.)
+// Q and K are K-major operands (rows of 128 bytes, swizzled); V is used as stored, keys x
+// columns, as an MN-major operand.  Probabilities are multiplied as value + remainder, both
+// bfloat16 (two products), so that the product keeps 16 bits of them, as in the other kernels.
+// (A float16 left operand against a bfloat16 right operand in one tcgen05.mma.kind::f16 raised
+// "illegal instruction" on a B200: the two formats have to be the same.)
 //
 // The maximum that exponents are taken against is allowed to lag behind the true running
 // maximum by up to 2^8: the accumulator row is rescaled (a round trip through registers) only
