@@ -262,13 +262,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
     grid_launch_dependents();
     grid_dependency_wait();
 
+    // CTAs start in the order x, then y, then z: the heads run along x, so that all heads of the
+    // query block with most keys start first and the short blocks fill the gaps at the end
     const int b = blockIdx.z;
-    const int head = blockIdx.y;
+    const int head = blockIdx.x;
     const int kvh = head / (p.n_heads / p.n_kv_heads);
     const int qs = p.q_start[b];
     const int ql = p.q_start[b + 1] - qs;
     const int kl = p.kv_len[b];
-    const int tok0 = (p.n_q_blocks - 1 - (int)blockIdx.x) * (QT * BM);      // the blocks with most keys start first
+    const int tok0 = (p.n_q_blocks - 1 - (int)blockIdx.y) * (QT * BM);
     const bool active = tok0 < ql;
     const int qpos_base = kl - ql;
     // Keys the CTA walks: from the window's start of its first row to its last row's own position, in
@@ -663,6 +665,8 @@ bool takes(int n_heads, int n_kv_heads, int head_dim, int page_size) {
     return page_size >= 1 && (page_size & (page_size - 1)) == 0;           // a power of two
 }
 
+bool p_blocks_too_many(int max_q_len) { return (max_q_len + QT * BM - 1) / (QT * BM) > 65535; }
+
 template <int HD>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, dim3 grid, cudaStream_t s) {
     constexpr size_t smem = smem_for<HD>();
@@ -694,7 +698,7 @@ extern "C" int tl_paged_attention_prefill(const void* q, const void* k_pages, co
     if (!takes(n_heads, n_kv_heads, head_dim, page_size) || max_q_len <= 0 || n_pages <= 0 || q_rows < n_tokens) return TL_BAD_SIZE;
     if (n_pages * n_kv_heads * page_size >= (1LL << 31)) return TL_BAD_SIZE;
     if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(out) || status == nullptr) return TL_BAD_ALIGN;
-    if (n_seqs > 65535 || n_heads > 65535) return TL_BAD_SIZE;
+    if (n_seqs > 65535 || p_blocks_too_many(max_q_len)) return TL_BAD_SIZE;
 
     PrefillParams p;
     p.q = (const __nv_bfloat16*)q;
@@ -717,7 +721,7 @@ extern "C" int tl_paged_attention_prefill(const void* q, const void* k_pages, co
     rc = tiled_map(&mv, v_pages, rows, head_dim, p.box_rows);
     if (rc != TL_OK) return rc;
 
-    dim3 grid(p.n_q_blocks, n_heads, n_seqs);
+    dim3 grid(n_heads, p.n_q_blocks, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;
     return head_dim == 128 ? launch<128>(mk, mv, p, grid, s) : launch<64>(mk, mv, p, grid, s);
 }
