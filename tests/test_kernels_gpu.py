@@ -343,6 +343,26 @@ def test_attention_refuses_sizes_it_cannot_do(ops):
         ops.embed(torch.zeros(3, dtype=torch.int32), torch.zeros(4, 4))  # CPU tensors
 
 
+def test_a_wait_that_nothing_satisfies_gives_up_and_reports(ops):
+    """The tensor-core and TMA kernels wait on mbarriers with a time limit and report through a
+    status word instead of hanging.  A kernel with one such wait, which nothing will ever
+    satisfy, shows the mechanism: it returns after the limit, the status says so, and the device
+    goes on working."""
+    from torchllms_b200.kernels.native import KernelError
+    ops.check_status()                                   # clean before
+    waited = ops.wait_selftest(limit_ms=2.0)
+    assert 2.0 <= waited < 50.0, waited
+    with pytest.raises(KernelError, match="gave up waiting"):
+        ops.check_status()
+    ops.check_status()                                   # the word was cleared
+    x = torch.randn(8, 256, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(128, 256, device="cuda", dtype=torch.bfloat16)
+    got = ops.linear(x, w)                               # the context is alive and the kernels still run
+    got = got.sum(0) if got.dim() == 3 else got
+    torch.testing.assert_close(got.float(), (x.float() @ w.float().t()), atol=0.5, rtol=2e-2)
+    ops.check_status()
+
+
 # -------------------------------------------------------------------------------- sampling
 
 def test_greedy_is_first_argmax(ops):

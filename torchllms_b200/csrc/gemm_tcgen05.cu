@@ -30,7 +30,7 @@ constexpr int UMMA_K = 16;
 constexpr int NTHREADS = 192;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000ull * 1000ull * 1000ull;   // two seconds, then give up
 
-enum : int { ERR_TMA_WAIT = 101, ERR_MMA_WAIT = 102, ERR_EPI_WAIT = 103 };
+enum : int { ERR_TMA_WAIT = 101, ERR_MMA_WAIT = 102, ERR_EPI_WAIT = 103, ERR_SELFTEST_WAIT = 109 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -51,13 +51,33 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-// false once WAIT_LIMIT_NS have passed, or as soon as another role has given up
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag) {
+// false once limit_ns have passed, or as soon as another role has given up
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (unsigned i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 0u && (*abort_flag || global_ns() - t0 > WAIT_LIMIT_NS)) return false;
+        if ((i & 255u) == 0u && (*abort_flag || global_ns() - t0 > limit_ns)) return false;
+    }
+}
+
+// A wait that nothing will ever satisfy, with a short limit: it must give up, report, and leave the
+// context usable.  What the tests run to see that the bounded waits of the kernels do what they say.
+__global__ void wait_selftest_kernel(int* status, unsigned long long limit_ns, unsigned long long* waited_ns) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned long long t0 = global_ns();
+        const bool ok = mbar_wait(&bar, 0, &abort_flag, limit_ns);      // nobody arrives
+        *waited_ns = global_ns() - t0;
+        if (!ok) atomicExch(status, ERR_SELFTEST_WAIT);
     }
 }
 
@@ -303,6 +323,13 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, in
 }  // namespace
 
 // How many K splits the kernel uses for M rows against a [N, K] weight.
+// Launches a kernel whose only wait can never be satisfied and gives up after limit_ns (at most a
+// second): the status word receives code 109, waited_ns (device memory) the time the wait took.
+extern "C" int tl_wait_selftest(int* status, unsigned long long limit_ns, unsigned long long* waited_ns, void* stream) {
+    if (status == nullptr || waited_ns == nullptr || limit_ns == 0 || limit_ns > 1000ull * 1000ull * 1000ull) return TL_BAD_SIZE;
+    return (int)tl_launch(wait_selftest_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, status, limit_ns, waited_ns);
+}
+
 extern "C" int tl_gemm_tcgen05_splits(int M, int N, int K) {
     // Two CTAs fit an SM; all CTAs of a launch should be resident at once (one wave), because a
     // second, partly filled wave streams at a fraction of the bandwidth.  So: as many splits as

@@ -271,6 +271,18 @@ class NativeOps:
             self._status[0] = 0
             raise KernelError(f"a kernel gave up waiting (code {code}); its output is not valid")
 
+    def wait_selftest(self, limit_ms: float = 1.0) -> float:
+        """Run a kernel whose only mbarrier wait nothing will ever satisfy, with a limit of
+        ``limit_ms``.  It must give up and say so: :meth:`check_status` then raises, and the device
+        stays usable.  Returns the milliseconds the wait took."""
+        waited = torch.zeros(1, dtype=torch.int64, device="cuda")
+        lib = self._lib("gemm_tcgen05")
+        rc = lib.tl_wait_selftest(ctypes.c_void_p(self._status.data_ptr()), ctypes.c_ulonglong(int(limit_ms * 1e6)),
+                                  _ptr(waited), _stream())
+        _check(rc, "wait_selftest")
+        torch.cuda.synchronize()
+        return float(waited.item()) / 1e6
+
     def gemm_simt(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         _cuda_contig(x, "gemm input")
         _cuda_contig(w, "gemm weight")
