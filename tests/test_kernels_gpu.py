@@ -142,6 +142,31 @@ def test_gemm_tcgen05_few_rows(ops, M, N, K):
     assert parts.dim() in (2, 3)
 
 
+@pytest.mark.parametrize("M,hidden,K", [(1, 64, 64), (8, 192, 264), (16, 14336, 128), (17, 448, 1000), (33, 128, 4096), (64, 1024, 520)])
+def test_gated_product_is_product_then_swiglu(ops, M, hidden, K):
+    """SwiGLU in the epilogue of the gate/up product: the same numbers as product + SwiGLU kernel,
+    and both near the float32 formula.  Sizes that are no power of two, one to 64 rows, a K with a
+    ragged last block, one slab and hundreds of them."""
+    torch.manual_seed(M * 7 + hidden)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w13 = (torch.randn(2 * hidden, K, device="cuda") * K ** -0.5).to(torch.bfloat16)
+    one = ops.linear_swiglu(x, w13, fused=True)
+    two = ops.linear_swiglu(x, w13, fused=False)
+    ops.check_status()
+    gu = x.float() @ w13.float().t()
+    g, u = gu[:, :hidden], gu[:, hidden:]
+    want = g / (1 + torch.exp(-g)) * u
+    assert one.dtype == torch.bfloat16 and one.shape == (M, hidden)
+    torch.testing.assert_close(one.float(), want, atol=3e-2, rtol=3e-2)
+    # two kernels: the product may be split over K (float32 partial sums, no rounding before the
+    # activation), so equality is exact only where it is not
+    lib = ops._lib("gemm_tcgen05")
+    if lib.tl_gemm_tcgen05_splits(M, 2 * hidden, K) == 1:
+        assert torch.equal(one, two)
+    else:
+        torch.testing.assert_close(one.float(), two.float(), atol=2e-2, rtol=2e-2)
+
+
 def test_gemm_tcgen05_rows_do_not_depend_on_the_batch(ops):
     """A token's product is the same bits whatever else shares its bucket of rows (1-16, 17-32,
     33-64: the buckets split K differently, so across them results agree to float32 rounding)."""

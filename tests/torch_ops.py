@@ -78,6 +78,9 @@ class TorchOps:
         g, u = gate_up[:, :hidden].float(), gate_up[:, hidden:].float()
         return (g / (1 + torch.exp(-g)) * u).to(out_dtype)
 
+    def linear_swiglu(self, x, w13, fused=None):
+        return self.swiglu(self.linear(x, w13), out_dtype=x.dtype)
+
     def linear(self, x, w, out_dtype=None, partials_ok=False):
         out_dtype = out_dtype or x.dtype
         if x.dtype == torch.float32:

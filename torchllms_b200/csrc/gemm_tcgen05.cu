@@ -133,9 +133,13 @@ struct GemmParams {
     int M, N, K;
     int k_blocks_per_split; // stages each split walks
     int out_is_f32;
+    int hidden;             // gated form: W is [2 * hidden, K], gate rows above up rows; out is [M, hidden] bfloat16
 };
 
-template <int BQ, int STAGES>
+// GATED: the slab is 64 rows of the gate projection and the 64 matching rows of the up projection
+// (two TMA boxes per stage), and the epilogue writes silu(gate) * up in bfloat16: the SwiGLU costs
+// no kernel and no round trip of the projections through memory.  One K split only.
+template <int BQ, int STAGES, bool GATED>
 __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_a,
                                                                 const GemmParams p) {
@@ -182,9 +186,17 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
             // ---- producer.  The weights depend on no earlier kernel: their first tiles are fetched
             // before the dependency on the predecessor is resolved, the activations after it.
             const int pre = n_kb < STAGES ? n_kb : STAGES;
+            auto load_w = [&](unsigned char* dst, unsigned long long* bar, int kb) {
+                if (GATED) {
+                    tma_load_2d(dst, &map_w, bar, kb * BK, slab * (BP / 2));
+                    tma_load_2d(dst + (BP / 2) * BK * 2, &map_w, bar, kb * BK, p.hidden + slab * (BP / 2));
+                } else {
+                    tma_load_2d(dst, &map_w, bar, kb * BK, slab * BP);
+                }
+            };
             for (int i = 0; i < pre; ++i) {
                 mbar_expect_tx(&full_bar[i], STAGE_BYTES);
-                tma_load_2d(tiles + i * STAGE_BYTES, &map_w, &full_bar[i], (kb0 + i) * BK, slab * BP);
+                load_w(tiles + i * STAGE_BYTES, &full_bar[i], kb0 + i);
             }
             grid_dependency_wait();
             for (int i = 0; i < pre; ++i)
@@ -198,7 +210,7 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
                 }
                 unsigned char* wt = tiles + s * STAGE_BYTES;
                 mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-                tma_load_2d(wt, &map_w, &full_bar[s], (kb0 + i) * BK, slab * BP);
+                load_w(wt, &full_bar[s], kb0 + i);
                 tma_load_2d(wt + W_BYTES, &map_a, &full_bar[s], (kb0 + i) * BK, 0);
             }
         }
@@ -239,7 +251,52 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
         }
         ok = __all_sync(0xffffffffu, ok);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
+        if (GATED) {
+            // Rows 0-63 of the accumulator are gates, rows 64-127 the matching ups.  The ups go through
+            // shared memory (the stages are done with: every product has finished) to the threads
+            // that hold the gates.  All four warps keep the appointment at the barrier, failed or not.
+            float* xch = reinterpret_cast<float*>(tiles);              // [64][BQ + 1]
+            const int row = quarter * 32 + lane;
+            if (ok && n_kb > 0 && row >= BP / 2) {
+#pragma unroll
+                for (int c0 = 0; c0 < BQ; c0 += 16) {
+                    unsigned r[16];
+                    TmemLoad<16>::run(tmem_d + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) xch[(row - BP / 2) * (BQ + 1) + c0 + j] = __uint_as_float(r[j]);
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (ok && row < BP / 2) {
+                const int f = slab * (BP / 2) + row;                   // column of the output
+#pragma unroll
+                for (int c0 = 0; c0 < BQ; c0 += 16) {
+                    unsigned r[16];
+                    if (n_kb > 0) {
+                        TmemLoad<16>::run(tmem_d + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, r);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) r[j] = 0u;
+                    }
+                    if (f < p.hidden) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int tok = c0 + j;
+                            if (tok < p.M) {
+                                // (rounded to bfloat16 first, as they are when they pass through memory:
+                                // this form and the two-kernel form give the same numbers)
+                                const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j])));
+                                const float u = __bfloat162float(__float2bfloat16_rn(n_kb > 0 ? xch[row * (BQ + 1) + tok] : 0.f));
+                                reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)tok * p.hidden + f] =
+                                    __float2bfloat16_rn(__fdividef(g, 1.f + __expf(-g)) * u);
+                            }
+                        }
+                    }
+                }
+            }
+        } else if (ok) {
             const size_t plane = (size_t)p.M * p.N;
 #pragma unroll
             for (int c0 = 0; c0 < BQ; c0 += 16) {
@@ -307,10 +364,11 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, in
     return rc == CUDA_SUCCESS ? TL_OK : TL_BAD_SIZE;
 }
 
-template <int BQ, int STAGES>
+template <int BQ, int STAGES, bool GATED = false>
 int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, int slabs, int splits, cudaStream_t s) {
     constexpr size_t smem = (size_t)STAGES * (BP * BK * 2 + BQ * BK * 2) + 1024;
-    auto kern = gemm_tcgen05_kernel<BQ, STAGES>;
+    static_assert(!GATED || (size_t)64 * (BQ + 1) * 4 <= (size_t)STAGES * (BP * BK * 2 + BQ * BK * 2), "the ups pass through the stages' memory");
+    auto kern = gemm_tcgen05_kernel<BQ, STAGES, GATED>;
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -322,7 +380,6 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, in
 
 }  // namespace
 
-// How many K splits the kernel uses for M rows against a [N, K] weight.
 // Launches a kernel whose only wait can never be satisfied and gives up after limit_ns (at most a
 // second): the status word receives code 109, waited_ns (device memory) the time the wait took.
 extern "C" int tl_wait_selftest(int* status, unsigned long long limit_ns, unsigned long long* waited_ns, void* stream) {
@@ -330,6 +387,7 @@ extern "C" int tl_wait_selftest(int* status, unsigned long long limit_ns, unsign
     return (int)tl_launch(wait_selftest_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, status, limit_ns, waited_ns);
 }
 
+// How many K splits the kernel uses for M rows against a [N, K] weight.
 extern "C" int tl_gemm_tcgen05_splits(int M, int N, int K) {
     // Two CTAs fit an SM; all CTAs of a launch should be resident at once (one wave), because a
     // second, partly filled wave streams at a fraction of the bandwidth.  So: as many splits as
@@ -375,8 +433,44 @@ extern "C" int tl_gemm_tcgen05(const void* A, const void* W, void* out, int out_
     p.out = out; p.status = status; p.M = M; p.N = N; p.K = K;
     p.k_blocks_per_split = (k_blocks + splits - 1) / splits;
     p.out_is_f32 = out_is_f32;
+    p.hidden = 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (bq == 16) return launch<16, 6>(mw, ma, p, slabs, splits, s);
     if (bq == 32) return launch<32, 5>(mw, ma, p, slabs, splits, s);
     return launch<64, 4>(mw, ma, p, slabs, splits, s);
+}
+
+// 1 if the gated form takes this problem (W is [2 * hidden, K]) and is the better choice: what
+// tl_gemm_tcgen05 takes, hidden a multiple of 64, and a shape that the plain form would not split
+// over K either (a split has no whole sums to gate).
+extern "C" int tl_gemm_tcgen05_gated_supports(int M, int hidden, int K) {
+    if (hidden <= 0 || hidden % (BP / 2) != 0) return 0;
+    if (!tl_gemm_tcgen05_supports(M, 2 * hidden, K)) return 0;
+    return tl_gemm_tcgen05_splits(M, 2 * hidden, K) == 1 ? 1 : 0;
+}
+
+// out[M, hidden] (bfloat16) = silu(A . W[:hidden]^T) * (A . W[hidden:]^T), A: [M, K] bf16, W: [2 * hidden, K] bf16.
+// Any hidden that is a multiple of 64 is computed correctly; tl_gemm_tcgen05_gated_supports says when
+// it is also the faster way.
+extern "C" int tl_gemm_tcgen05_gated(const void* A, const void* W, void* out, int M, int hidden, int K, int* status,
+                                     void* stream) {
+    if (M <= 0 || hidden <= 0) return TL_OK;
+    if (hidden % (BP / 2) != 0 || !tl_gemm_tcgen05_supports(M, 2 * hidden, K)) return TL_BAD_SIZE;
+    if (!aligned16(A) || !aligned16(W) || !aligned16(out) || status == nullptr) return TL_BAD_ALIGN;
+    const int slabs = hidden / (BP / 2);
+    const int bq = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    CUtensorMap mw, ma;
+    int rc = make_map(&mw, W, 2LL * hidden, K, BP / 2);
+    if (rc != TL_OK) return rc;
+    rc = make_map(&ma, A, M, K, bq);
+    if (rc != TL_OK) return rc;
+    GemmParams p;
+    p.out = out; p.status = status; p.M = M; p.N = 2 * hidden; p.K = K;
+    p.k_blocks_per_split = (K + BK - 1) / BK;
+    p.out_is_f32 = 0;
+    p.hidden = hidden;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (bq == 16) return launch<16, 6, true>(mw, ma, p, slabs, 1, s);
+    if (bq == 32) return launch<32, 5, true>(mw, ma, p, slabs, 1, s);
+    return launch<64, 4, true>(mw, ma, p, slabs, 1, s);
 }

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import contextlib
 import ctypes
+import os
 import functools
 from typing import Dict, Optional, Tuple
 
@@ -93,6 +94,8 @@ class NativeOps:
         self._workspace: Dict[Tuple[int, str], torch.Tensor] = {}
         self._retired: list = []
         self.use_tcgen05 = True
+        # SwiGLU in the epilogue of the gate/up product (TORCHLLMS_B200_NO_GATED=1 keeps the two kernels, for comparisons)
+        self.use_gated = os.environ.get("TORCHLLMS_B200_NO_GATED", "") not in ("1", "true")
         # error word of kernels with bounded waits: pinned host memory the device writes to directly
         self._status = torch.zeros(4, dtype=torch.int32).pin_memory()
         self._mm_out_dtype: Optional[bool] = None
@@ -242,6 +245,39 @@ class NativeOps:
         if self._mm_out_dtype:
             return torch.mm(x, w.t(), out_dtype=torch.float32)
         return self.gemm_simt(x, w, torch.float32)
+
+    def linear_swiglu(self, x: torch.Tensor, w13: torch.Tensor, fused: Optional[bool] = None) -> torch.Tensor:
+        """``silu(x @ w13[:H]^T) * (x @ w13[H:]^T)`` for a stacked gate/up weight ``[2 H, K]``, in
+        ``x``'s dtype.  Decode-sized bfloat16 inputs whose product needs no K split run as one
+        kernel (the activation in the product's epilogue); everything else as product + SwiGLU
+        kernel, with the same numbers.  ``fused`` forces the choice (tests)."""
+        _cuda_contig(x, "linear input")
+        _cuda_contig(w13, "linear weight")
+        _need(x.dim() == 2 and w13.dim() == 2 and x.shape[1] == w13.shape[1] and w13.shape[0] % 2 == 0,
+              "linear_swiglu: x [M, K] against w13 [2 H, K]")
+        M, K = x.shape
+        hidden = w13.shape[0] // 2
+        can = (x.dtype == torch.bfloat16 and w13.dtype == torch.bfloat16 and self.use_tcgen05 and M <= 64 and hidden % 64 == 0
+               and K % 8 == 0 and K >= 8 and x.data_ptr() % 16 == 0 and w13.data_ptr() % 16 == 0)
+        if fused is None:
+            fused = (can and self.use_gated and
+                     self._lib("gemm_tcgen05").tl_gemm_tcgen05_gated_supports(M, hidden, K) == 1)
+        _need(can or not fused, "the fused form takes bfloat16, at most 64 rows, hidden % 64 == 0 and K % 8 == 0")
+        if not fused:
+            return self.swiglu(self.linear(x, w13, partials_ok=True), out_dtype=x.dtype)
+        return self.gemm_gated(x, w13)
+
+    @_timed
+    def gemm_gated(self, x: torch.Tensor, w13: torch.Tensor) -> torch.Tensor:
+        """The one-kernel form of :meth:`linear_swiglu` (its caller has checked the sizes)."""
+        M, K = x.shape
+        hidden = w13.shape[0] // 2
+        out = torch.empty((M, hidden), dtype=torch.bfloat16, device=x.device)
+        rc = self._lib("gemm_tcgen05").tl_gemm_tcgen05_gated(
+            _ptr(x), _ptr(w13), _ptr(out), M, hidden, K, ctypes.c_void_p(self._status.data_ptr()), _stream())
+        _check(rc, "gemm_tcgen05_gated")
+        self.launches += 1
+        return out
 
     def gemm_tcgen05(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """At most 64 rows of bfloat16 against a bfloat16 weight on the tcgen05 kernel.  Returns

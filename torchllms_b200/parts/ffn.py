@@ -38,5 +38,6 @@ class SwiGLU(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         ops = self.env.ops
-        gate_up = ops.linear(x, self.w13, partials_ok=True)   # [T, 2 * hidden]: gate columns, then up columns
-        return ops.linear(ops.swiglu(gate_up, out_dtype=self.env.dtype), self.w2, partials_ok=True)
+        # gate and up in one product over the stacked weight, the activation in its epilogue where the
+        # kernel can (decode steps), else product [T, 2 * hidden] + SwiGLU kernel
+        return ops.linear(ops.linear_swiglu(x, self.w13), self.w2, partials_ok=True)
