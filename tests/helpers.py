@@ -32,7 +32,16 @@ TINY_B = {
                      "original_max_position_embeddings": 64},
     "tie_word_embeddings": True, "max_position_embeddings": 256,
 }
-TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8)}   # name -> (config, seed, page size)
+# A third one for what the two above cannot reach: heads of 64 (the TMA-fed decode kernel and the
+# tcgen05 prefill kernel take 64 and 128 only), a feed-forward width that the gated product takes,
+# and room for prompts of several hundred tokens.
+TINY_C = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 128, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 320,
+    "vocab_size": 777, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "rope_scaling": None,
+    "tie_word_embeddings": False, "max_position_embeddings": 1024,
+}
+TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16)}   # name -> (config, seed, page size)
 
 
 def tensor_table(cfg: dict) -> List[tuple]:

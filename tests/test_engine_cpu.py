@@ -22,7 +22,8 @@ ATOL = 1e-4
 @pytest.fixture(scope="module")
 def setups(tmp_path_factory):
     out = {}
-    for name, (cfg, seed, page) in TINY.items():
+    for name in ("A", "B"):                      # the third configuration is for GPU kernels
+        cfg, seed, page = TINY[name]
         folder = tiny_folder(tmp_path_factory.mktemp(name), name)
         rng = random.Random(seed)
         reqs = {f"r{i}": [rng.randrange(cfg["vocab_size"]) for _ in range(n)] for i, n in enumerate(LENGTHS[name])}

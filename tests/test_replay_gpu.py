@@ -14,7 +14,12 @@ from plain_llama import PlainModel, to_bfloat16_and_back
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [1, 7, 33, 64, 97, 120, 50], "B": [2, 5, 17, 40, 100, 200, 65, 129]}
+LENGTHS = {"A": [1, 7, 33, 64, 97, 120, 50], "B": [2, 5, 17, 40, 100, 200, 65, 129],
+           "C": [300, 97, 513, 130, 700, 64, 260]}
+# configuration C is there for long portions (the tcgen05 prefill kernel takes 96 tokens and more,
+# 256 to a CTA): its cuttings include them
+MODE_ARGS = {("C", "portions"): dict(sizes=(2, 130, 5, 257, 96, 31, 300, 3, 128, 17)),
+             ("C", "mixed"): dict(chunks=(2, 5, 24, 96, 150, 260, 40))}
 # float32: the reference's own gate is 1e-3 (torchllms/inference/validate_qwen3.py:579-584); these
 # models are tiny, so a tenth of it.
 # bfloat16: weights are stored in bfloat16 and read exactly by both sides, and the plain
@@ -79,11 +84,11 @@ def compare(got, places, ref, tol):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 @pytest.mark.parametrize("mode", ["whole", "tail_one_by_one", "portions", "mixed"])
 def test_replay(setups, tmp_path, name, dtype, mode):
     folder, reqs, ref, tol = setups[(name, dtype)]
-    steps, places, peak = getattr(traces, mode)(reqs)
+    steps, places, peak = getattr(traces, mode)(reqs, **MODE_ARGS.get((name, mode), {}))
     got = run_trace(folder, dtype, steps, tmp_path / "out", max_tokens=peak)
     worst = compare(got, places, ref, tol)
     print(f"{name} {dtype} {mode}: {len(steps)} steps, pool {peak} tokens, worst error {worst:.3g} (allowed {tol:.3g})")

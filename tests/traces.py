@@ -78,7 +78,8 @@ def portions(reqs: Dict[str, List[int]], sizes=(2, 3, 5, 24, 7, 2, 16, 9, 2, 31,
     return b.result()
 
 
-def mixed(reqs: Dict[str, List[int]], seed: int = 0, live_max: int = 4, tail: int = 12):
+def mixed(reqs: Dict[str, List[int]], seed: int = 0, live_max: int = 4, tail: int = 12,
+          chunks=(2, 3, 5, 8, 13, 24, 40)):
     """Up to ``live_max`` live requests: portions of some beside single decoded tokens of others,
     requests now and then left out of a step; finished requests end, new ones take their pages."""
     rng = random.Random(seed)
@@ -95,7 +96,7 @@ def mixed(reqs: Dict[str, List[int]], seed: int = 0, live_max: int = 4, tail: in
                 continue                                   # left out of this step
             left = len(toks) - done
             if left > tail:
-                n = min(left - tail, rng.choice([2, 3, 5, 8, 13, 24, 40]))
+                n = min(left - tail, rng.choice(list(chunks)))
             else:
                 n = 1
             want = list(range(n)) if n <= 8 else sorted({0, n // 2, n - 2, n - 1})
