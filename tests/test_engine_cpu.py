@@ -71,3 +71,37 @@ def test_step_rejects_bad_input(setups):
         eng.step([StepEntry(h, list(range(10)))])        # 70 tokens do not fit 64
     assert eng.cache.length(h) == 60                     # nothing changed
     eng.cache.check_invariants()
+
+
+def test_a_step_in_two_halves_and_a_step_called_off(setups):
+    """``step`` is ``prepare`` (cache growth and index data, no token values) plus ``run_prepared``
+    (token ids from a host list or from a device tensor with a row index).  A prepared step that is
+    called off, or whose tokens turn out bad, leaves the cache as it was."""
+    from torchllms_b200.engine.step import StepEntry, StepError
+    folder, page, reqs, ref = setups["B"]
+    rp = Replayer(folder, "float32", 256, page_size=page, device="cpu", ops=TorchOps())
+    eng = rp.engine
+    toks = reqs["r3"]                                    # 40 tokens
+    a, b = eng.claim(), eng.claim()
+    eng.step([StepEntry(a, toks[:30], []), StepEntry(b, toks[:7], [])])
+    before = (eng.cache.length(a), eng.cache.length(b), eng.cache.free_pages())
+    called_off = eng.prepare([(a, 5, None), (b, 20, [0])])
+    assert (eng.cache.length(a), eng.cache.length(b)) == (35, 27)
+    eng.discard(called_off)
+    assert (eng.cache.length(a), eng.cache.length(b), eng.cache.free_pages()) == before
+    bad = eng.prepare([(a, 2, None)])
+    with pytest.raises(StepError):
+        eng.run_prepared(bad, [1, 100000])               # outside the vocabulary: rolled back
+    assert (eng.cache.length(a), eng.cache.length(b), eng.cache.free_pages()) == before
+    # the same step from a host list and from a "device" tensor gathered by rows
+    want = eng.step([StepEntry(a, toks[30:31], [0]), StepEntry(b, toks[7:8], [0])]).clone()
+    eng.cache.truncate(a, 30)
+    eng.cache.truncate(b, 7)
+    prepared = eng.prepare([(a, 1, [0]), (b, 1, [0])])
+    pool = torch.tensor([toks[7], 3, toks[30]], dtype=torch.int32)
+    got = eng.run_prepared(prepared, pool, rows=[2, 0])
+    assert torch.equal(got, want)
+    assert np.abs(got[0].numpy() - ref["r3"][30]).max() < ATOL
+    with pytest.raises(StepError):
+        eng.run_prepared(eng.prepare([(a, 1, None)]), pool, rows=[3])    # no such row
+    eng.cache.check_invariants()
