@@ -54,8 +54,10 @@ namespace {
 constexpr int BM = 128;                 // rows of a query tile (tokens of one head)
 constexpr int QT = 2;                   // query tiles per CTA: they share every K and V tile that is loaded
 constexpr int BN = 128;                 // keys per tile
-constexpr int NTHREADS = 352;
-constexpr int W_COPY = 8, W_ISSUE = 9;   // warps 0-7 are the softmax, warp 8 copies, warps 9 and 10 issue
+constexpr int RT = 2;                   // threads that share a query row in the softmax (warps w, w + 4, ..: same TMEM lanes);
+                                        // 4 measured the same speed: the softmax is bound by instruction issue, not by latency
+constexpr int W_COPY = 4 * RT, W_ISSUE = 4 * RT + 1;   // warps 0 .. 4 RT - 1 are the softmax, then one copies, two issue
+constexpr int NTHREADS = (4 * RT + 3) * 32;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LAG = 8.f;              // how far (in powers of two) the maximum in use may lag
 constexpr unsigned long long WAIT_NS = 2000ull * 1000ull * 1000ull;
@@ -161,23 +163,28 @@ __device__ __forceinline__ void umma_ts(unsigned tmem_d, unsigned tmem_a, unsign
 __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(taddr));
 }
-__device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+__device__ __forceinline__ void tmem_st16(unsigned taddr, const unsigned (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
                  ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
                  : "memory");
+}
+// N words (a multiple of 16) of this thread's lane, in pieces of 16 columns
+template <int N> __device__ __forceinline__ void tmem_ld(unsigned taddr, unsigned (&r)[N]) {
+    static_assert(N % 16 == 0, "whole pieces of 16 columns");
+#pragma unroll
+    for (int c = 0; c < N / 16; ++c) tmem_ld16(taddr + c * 16, *reinterpret_cast<unsigned(*)[16]>(&r[c * 16]));
+}
+template <int N> __device__ __forceinline__ void tmem_st(unsigned taddr, const unsigned (&r)[N]) {
+    static_assert(N % 16 == 0, "whole pieces of 16 columns");
+#pragma unroll
+    for (int c = 0; c < N / 16; ++c) tmem_st16(taddr + c * 16, *reinterpret_cast<const unsigned(*)[16]>(&r[c * 16]));
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -199,7 +206,7 @@ struct Tail {                   // what lies behind the tiles in shared memory
     unsigned long long s_full[QT], p_full[QT], pv_done[QT];
     unsigned tmem_base_slot;
     int failed_flag;
-    float swap[2][2][BM];       // [parity of the softmax's step][half][row]
+    float swap[2][RT][BM];      // [parity of the softmax's step][part of the row][row]
 };
 
 // What a query tile has to do with the CTA's key tiles: it works on tiles first .. last - 1.
@@ -231,12 +238,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
     unsigned long long (&pv_done)[QT] = tail.pv_done;
     unsigned& tmem_base_slot = tail.tmem_base_slot;
     int& failed_flag = tail.failed_flag;
-    float (&swap_max)[2][2][BM] = tail.swap;                 // the two halves of a row tell each other their maximum
+    float (&swap_max)[2][RT][BM] = tail.swap;                // the threads of a row tell each other their maximum
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
         failed_flag = 0;
-        mbar_init(&q_full, 8);
+        mbar_init(&q_full, 4 * RT);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&k_empty[s], QT);       // every query tile's issuer lets go of a stage
@@ -245,7 +252,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
         }
         for (int t = 0; t < QT; ++t) {
             mbar_init(&s_full[t], 1);
-            mbar_init(&p_full[t], 8);
+            mbar_init(&p_full[t], 4 * RT);
             mbar_init(&pv_done[t], 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -406,13 +413,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
         }
     } else if (active) {
         // ---- softmax: row r = TMEM lane r of either query tile; this thread has the keys
-        // 64 half .. 64 half + 63 of every key tile
-        constexpr int HN = BN / 2;                           // keys per thread and tile
-        constexpr int HO = HD / 2;                           // accumulator columns per thread
+        // HN half .. HN half + HN - 1 of every key tile (half: which of the row's RT threads this is)
+        constexpr int HN = BN / RT;                          // keys per thread and tile
+        constexpr int HO = HD / RT;                          // accumulator columns per thread
         const int half = warp >> 2;
         const int r = (warp & 3) * 32 + lane;
         const unsigned lane_addr = tmem + ((unsigned)((warp & 3) * 32) << 16);
-        const int pair_barrier = 1 + (warp & 3);             // named barrier of the two warps that share 32 rows
+        const int pair_barrier = 1 + (warp & 3);             // named barrier of the RT warps that share 32 rows
         // this thread's half of its query rows goes into shared memory in the layout of a K tile:
         // rows of 128 bytes (64 elements), 16-byte chunks swizzled with the row
 #pragma unroll
@@ -461,9 +468,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
                 float mine = -INFINITY;
                 if (ok) {
                     tc_fence_after();
-#pragma unroll
-                    for (int c = 0; c < HN / 32; ++c)
-                        tmem_ld32(lane_addr + col_s + half * HN + c * 32, *reinterpret_cast<unsigned(*)[32]>(&raw[c * 32]));
+                    tmem_ld<HN>(lane_addr + col_s + half * HN, raw);
                     tmem_wait_ld();
                     // the whole key tile is visible to every row of this query tile?
                     const bool clear = k0 + BN - 1 <= t0 && (p.window <= 0 || k0 > t0 + rows - 1 - p.window);
@@ -488,9 +493,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
                 // thread gets there), so two slots, used in turn, are never overwritten unread.  Past the
                 // barrier both have their scores in registers: the probabilities may go where they were.
                 swap_max[slot][half][r] = mine;
-                asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
+                asm volatile("bar.sync %0, %1;" ::"r"(pair_barrier), "n"(32 * RT) : "memory");
                 if (!ok) continue;
-                const float both = fmaxf(mine, swap_max[slot][half ^ 1][r]);
+                float both = mine;
+#pragma unroll
+                for (int o = 1; o < RT; ++o) both = fmaxf(both, swap_max[slot][(half + o) % RT][r]);
                 const float m_new = fmaxf(m_used, both * p.scale_log2);
                 const bool grow = m_new > m_used + LAG;      // also true for the first keys a row sees
                 const bool rescale = it > 0 && __any_sync(0xffffffffu, grow);
@@ -525,20 +532,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
                     }
                     tc_fence_after();
                     l_sum *= alpha;
+                    unsigned v[HO];
+                    tmem_ld<HO>(lane_addr + col_o + half * HO, v);
+                    tmem_wait_ld();
 #pragma unroll
-                    for (int c = 0; c < HO / 32; ++c) {
-                        unsigned v[32];
-                        tmem_ld32(lane_addr + col_o + half * HO + c * 32, v);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                        tmem_st32(lane_addr + col_o + half * HO + c * 32, v);
-                    }
+                    for (int i = 0; i < HO; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    tmem_st<HO>(lane_addr + col_o + half * HO, v);
                 }
                 l_sum += (l0 + l1) + (l2 + l3);
                 if (t) { m_b = m_used; l_b = l_sum; } else { m_a = m_used; l_a = l_sum; }
-                tmem_st32(lane_addr + col_s + half * (HN / 2), hi);
-                tmem_st32(lane_addr + col_s + BN / 2 + half * (HN / 2), lo);
+                tmem_st<HN / 2>(lane_addr + col_s + half * (HN / 2), hi);
+                tmem_st<HN / 2>(lane_addr + col_s + BN / 2 + half * (HN / 2), lo);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
@@ -555,14 +559,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
         ok = __all_sync(0xffffffffu, ok);
         // (both warps of a pair come here, failed or not; the slot is the one the last step did not
         // use: the partner has read that one before it came to the last step's barrier)
-        float (&swap_sum)[2][BM] = swap_max[step & 1];
-        float (&swap_sum2)[2][BM] = swap_max[(step & 1) ^ 1];
+        float (&swap_sum)[RT][BM] = swap_max[step & 1];
+        float (&swap_sum2)[RT][BM] = swap_max[(step & 1) ^ 1];
         swap_sum[half][r] = l[0];
-        asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
-        l[0] += swap_sum[half ^ 1][r];
+        asm volatile("bar.sync %0, %1;" ::"r"(pair_barrier), "n"(32 * RT) : "memory");
+#pragma unroll
+        for (int o = 1; o < RT; ++o) l[0] += swap_sum[(half + o) % RT][r];
         swap_sum2[half][r] = l[1];
-        asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
-        l[1] += swap_sum2[half ^ 1][r];
+        asm volatile("bar.sync %0, %1;" ::"r"(pair_barrier), "n"(32 * RT) : "memory");
+#pragma unroll
+        for (int o = 1; o < RT; ++o) l[1] += swap_sum2[(half + o) % RT][r];
         if (!ok) {
             if (lane == 0) {
                 failed_flag = 1;
@@ -576,21 +582,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
                 const bool valid = r < range[t].rows;
                 const float inv = l[t] > 0.f ? 1.f / l[t] : 0.f;
                 __nv_bfloat16* orow = p.out + ((size_t)(qs + tok0 + t * BM + r) * p.n_heads + head) * HD + half * HO;
+                unsigned v[HO];
+                tmem_ld<HO>(lane_addr + COL_O + t * BN + half * HO, v);     // every lane takes part in the load
+                tmem_wait_ld();
+                if (valid) {
 #pragma unroll
-                for (int c = 0; c < HO / 32; ++c) {
-                    unsigned v[32];
-                    tmem_ld32(lane_addr + COL_O + t * BN + half * HO + c * 32, v);     // every lane takes part in the load
-                    tmem_wait_ld();
-                    if (valid) {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            uint4 w;
-                            w.x = pack_bf16(__uint_as_float(v[8 * i]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
-                            w.y = pack_bf16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
-                            w.z = pack_bf16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
-                            w.w = pack_bf16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
-                            *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = w;
-                        }
+                    for (int i = 0; i < HO / 8; ++i) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(v[8 * i]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + i * 8) = w;
                     }
                 }
             }
