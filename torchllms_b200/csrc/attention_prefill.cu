@@ -507,21 +507,27 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
                 // probabilities as value + remainder, two bfloat16 to a column: columns 32 half .. of the
                 // tile's buffer hold the values of this thread's keys, columns 64 + 32 half .. the remainders
                 unsigned hi[HN / 2], lo[HN / 2];
-                float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+                // (arithmetic two floats at a time, fma.f32x2 and add.f32x2 of this architecture: the softmax
+                // is bound by how many instructions it issues)
+                float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
+                const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_safe, -m_safe);
+                const float2 neg1 = make_float2(-1.f, -1.f);
 #pragma unroll
                 for (int i = 0; i < HN; i += 4) {
-                    const float e0 = ex2(fmaf(__uint_as_float(raw[i]), p.scale_log2, -m_safe));
-                    const float e1 = ex2(fmaf(__uint_as_float(raw[i + 1]), p.scale_log2, -m_safe));
-                    const float e2 = ex2(fmaf(__uint_as_float(raw[i + 2]), p.scale_log2, -m_safe));
-                    const float e3 = ex2(fmaf(__uint_as_float(raw[i + 3]), p.scale_log2, -m_safe));
-                    l0 += e0; l1 += e1; l2 += e2; l3 += e3;
-                    const __nv_bfloat162 ha = __floats2bfloat162_rn(e0, e1), hb = __floats2bfloat162_rn(e2, e3);
-                    const float2 ba = __bfloat1622float2(ha), bb = __bfloat1622float2(hb);
+                    const float2 xa = __ffma2_rn(make_float2(__uint_as_float(raw[i]), __uint_as_float(raw[i + 1])), sc2, nm2);
+                    const float2 xb = __ffma2_rn(make_float2(__uint_as_float(raw[i + 2]), __uint_as_float(raw[i + 3])), sc2, nm2);
+                    const float2 ea = make_float2(ex2(xa.x), ex2(xa.y)), eb = make_float2(ex2(xb.x), ex2(xb.y));
+                    la = __fadd2_rn(la, ea);
+                    lb = __fadd2_rn(lb, eb);
+                    const __nv_bfloat162 ha = __floats2bfloat162_rn(ea.x, ea.y), hb = __floats2bfloat162_rn(eb.x, eb.y);
+                    const float2 ra = __ffma2_rn(__bfloat1622float2(ha), neg1, ea);      // what the rounding left, exactly
+                    const float2 rb = __ffma2_rn(__bfloat1622float2(hb), neg1, eb);
                     hi[i / 2] = *reinterpret_cast<const unsigned*>(&ha);
                     hi[i / 2 + 1] = *reinterpret_cast<const unsigned*>(&hb);
-                    lo[i / 2] = pack_bf16(e0 - ba.x, e1 - ba.y);
-                    lo[i / 2 + 1] = pack_bf16(e2 - bb.x, e3 - bb.y);
+                    lo[i / 2] = pack_bf16(ra.x, ra.y);
+                    lo[i / 2 + 1] = pack_bf16(rb.x, rb.y);
                 }
+                const float l0 = la.x, l1 = la.y, l2 = lb.x, l3 = lb.y;
                 float l_sum = (t ? l_b : l_a);
                 if (rescale) {
                     // the product that last wrote the accumulator must be over
