@@ -461,7 +461,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
                 const int t0 = qpos_base + tok0 + t * BM;    // position of the tile's first row
                 const int qpos = t0 + (r < rows ? r : rows - 1);         // idle rows follow the last real one
                 const unsigned col_s = COL_S + t * BN, col_o = COL_O + t * BN;
-                // (a wait's verdict is taken by the whole warp: the loads below need all of its lanes)
+                // (a wait's outcome is taken by the whole warp: the loads below need all of its lanes)
                 if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], it & 1, failed));
                 if (!ok) failed_flag = 1;
                 unsigned raw[HN];                            // the scores
