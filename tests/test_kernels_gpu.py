@@ -340,6 +340,31 @@ def test_attention_finds_one_far_key_among_hundreds(ops, dtype, impl, key_pos):
 
 
 @pytest.mark.parametrize("dtype,impl", IMPLS)
+@pytest.mark.parametrize("key_pos", [0, 127, 128, 300, 511, 640])
+def test_a_long_portion_finds_one_far_key(ops, dtype, impl, key_pos):
+    """The same for a portion of hundreds of rows late in a longer context (several query tiles and
+    key tiles, two query tiles to a CTA in the tcgen05 kernel, pages in shuffled order): every row
+    that can see the key must return its value, every row before it must not."""
+    if impl == "decode":
+        pytest.skip("the decode kernel takes no long portions")
+    L, Q, H, KV, hd, P = 700, 600, 4, 2, (64 if impl == "prefill" else 32), 16
+    a = build_paged([L, 40], [Q, 1], H, KV, hd, P, dtype, seed=key_pos + 1, peak=(0, key_pos, 10.0))
+    got = ops.paged_attention(**a, scale=hd ** -0.5, window=None, impl=impl).float()
+    page, slot = a["block_table"][0, key_pos // P].item(), key_pos % P
+    first_row = L - Q                                     # position of the portion's first token
+    for h in range(H):
+        v = a["v_pages"][page, h // (H // KV), slot].float()
+        err = (got[:Q, h] - v).abs().amax(dim=1)          # per row
+        sees = torch.arange(first_row, L, device=err.device) >= key_pos
+        assert (err[sees] < 0.06).all(), (h, int(torch.nonzero(err * sees >= 0.06)[0]))
+        if (~sees).any():
+            assert (err[~sees] > 0.06).all()
+    want = TWIN.paged_attention(**a, scale=hd ** -0.5, window=None).float()
+    t = tol(dtype, 2e-5, 2e-2)
+    torch.testing.assert_close(got, want, atol=t, rtol=t)
+
+
+@pytest.mark.parametrize("dtype,impl", IMPLS)
 def test_window_edge_is_exact(ops, dtype, impl):
     """The key just outside the window gets a huge score: if the edge were off by one it would
     take over the output."""
