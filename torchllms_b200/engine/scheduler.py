@@ -23,13 +23,13 @@ from __future__ import annotations
 import time
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Deque, Dict, Iterable, List, Optional, Sequence, Set, Tuple
+from typing import Deque, Iterable, List, Optional, Sequence, Set, Tuple
 
 import torch
 
 from ..cache.manager import OutOfPages
 from ..sampling.sampler import Sampler, SamplingParams
-from .step import Engine, StepEntry
+from .step import Engine
 
 
 @dataclass

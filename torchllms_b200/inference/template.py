@@ -9,7 +9,7 @@ header as generation prompt, content stripped of surrounding whitespace, and sto
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Sequence, Tuple
 
 

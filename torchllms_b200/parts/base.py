@@ -24,7 +24,7 @@ What each family adds is documented on its base class below.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Mapping, Optional, Tuple, Type
+from typing import Any, Callable, Dict, Mapping, Optional, Tuple
 
 import torch
 

@@ -12,7 +12,7 @@ from typing import Dict, Mapping
 import torch
 
 from ..weights.loader import ExpectedTensor
-from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, BuildEnv, Residual, register_block)
+from .base import FEED_FORWARDS, MIXERS, NORMS, Block, BuildEnv, Residual, register_block
 from .spec import PartSpec
 
 
