@@ -4,6 +4,7 @@
     python -m torchllms_b200.kernels.microbench attention_prefill --lengths 2048,8192 --impls mma,prefill
     python -m torchllms_b200.kernels.microbench gemm
     python -m torchllms_b200.kernels.microbench elementwise --tokens 2048
+    python -m torchllms_b200.kernels.microbench peaks
 
 Every case is timed with CUDA events after warm-up.  Memory-bound kernels run inside a CUDA
 graph over several copies of their operands (more than the 126 MB of L2 together), so that a
@@ -132,6 +133,22 @@ def elementwise(args) -> None:
     print(f"swiglu  T {T}: {us:7.1f} us  {T * HIDDEN * 6 / us / 1e6:5.2f} TB/s")
 
 
+def peaks(args) -> None:
+    """What this GPU gives a plain copy and a library bfloat16 product: the denominators of a roofline."""
+    n = 1 << 30
+    src = torch.empty(n, dtype=torch.int32, device="cuda")
+    dst = torch.empty_like(src)
+    us = _time(lambda: dst.copy_(src), 10)
+    print(f"copy of {4 * n / 1e9:.1f} GB: {us:9.1f} us  {2 * 4 * n / us / 1e6:5.2f} TB/s (read + write)")
+    m = 8192
+    a = torch.randn(m, m, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(m, m, device="cuda", dtype=torch.bfloat16)
+    us = _time(lambda: torch.mm(a, b), 10)
+    print(f"library product {m}^3 bfloat16, ten in a row: {us:9.1f} us  {2 * m ** 3 / us / 1e6:7.1f} TFLOP/s")
+    us = _time(lambda: torch.mm(a, b), 400)
+    print(f"library product {m}^3 bfloat16, four hundred in a row: {us:9.1f} us  {2 * m ** 3 / us / 1e6:7.1f} TFLOP/s")
+
+
 def main(argv=None) -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = parser.add_subparsers(dest="case", required=True)
@@ -147,6 +164,8 @@ def main(argv=None) -> None:
     p = sub.add_parser("gemm")
     p.add_argument("--rows", default="8,64")
     p.set_defaults(run=gemm)
+    p = sub.add_parser("peaks")
+    p.set_defaults(run=peaks)
     p = sub.add_parser("elementwise")
     p.add_argument("--tokens", type=int, default=2048)
     p.set_defaults(run=elementwise)
