@@ -101,3 +101,25 @@ def test_launching_ahead_gives_the_same_tokens_on_the_device(tmp_path, precision
         assert ahead.last_stats.launched_ahead > 10 and stepwise.last_stats.launched_ahead == 0
         ahead.engine.cache.check_invariants()
         assert ahead.engine.cache.n_live() == 0
+
+
+def test_cache_pool_as_a_share_of_free_memory(tmp_path):
+    """Three ways to size the cache: requests x length (default), GiB, or a share of what the device
+    has free once the weights are on it."""
+    from torchllms_b200.inference import LLM
+    cfg, _, page = TINY["A"]
+    folder = tiny_folder(tmp_path, "A")
+    kw = dict(precision="float32", max_len=128, max_bsz=2, page_size=page)
+    by_count = LLM(folder, **kw)
+    assert by_count.engine.cache.groups[0].allocator.n_pages * page == 2 * 128
+    free_before, _ = torch.cuda.mem_get_info()
+    by_share = LLM(folder, kv_memory_fraction=0.001, **kw)
+    per_token = 2 * cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * cfg["head_dim"] * 4
+    tokens = by_share.engine.cache.groups[0].allocator.n_pages * page
+    assert 0.5 * 0.001 * free_before / per_token < tokens <= 0.001 * free_before / per_token + page
+    out = by_share.generate(prompt_token_ids=PROMPTS["A"][:2], max_new_tokens=4)
+    assert [r.token_ids for r in out] == [r.token_ids for r in by_count.generate(prompt_token_ids=PROMPTS["A"][:2], max_new_tokens=4)]
+    with pytest.raises(ValueError):
+        LLM(folder, kv_memory_fraction=0.5, kv_memory_gb=1.0, **kw)
+    with pytest.raises(ValueError):
+        LLM(folder, kv_memory_fraction=1.5, **kw)

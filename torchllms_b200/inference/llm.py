@@ -54,6 +54,7 @@ class LLM:
         batched: bool = True,
         page_size: int = 16,
         kv_memory_gb: Optional[float] = None,
+        kv_memory_fraction: Optional[float] = None,
         *,
         max_num_batched_tokens: int = 2048,
         prefill_chunk: Optional[int] = None,
@@ -67,7 +68,8 @@ class LLM:
         one, or a list of them loaded in order, later tensors overriding earlier ones (the
         configuration is read beside the first).  Alternatively ``config`` and ``random_seed``
         build a model with random weights on the device.  ``max_bsz`` is the number of requests
-        that may run at once; the cache holds ``max_bsz * max_len`` tokens unless ``kv_memory_gb``
+        that may run at once; the cache holds ``max_bsz * max_len`` tokens unless ``kv_memory_fraction``
+        (a share of the device memory that is free once the weights are loaded) or ``kv_memory_gb``
         gives its size in GiB (torchllms/models/networks.py:872-884)."""
         ops = ops or get_ops()
         precision = precision or "bfloat16"
@@ -92,7 +94,17 @@ class LLM:
         self.batched = batched
         bytes_per_token = sum(g_need.n_kv_heads * g_need.head_dim * 2 * n_runs for g_need, n_runs in self._kv_layout())
         bytes_per_token *= torch.empty((), dtype=self.dtype).element_size()
-        if kv_memory_gb is None:
+        if kv_memory_gb is not None and kv_memory_fraction is not None:
+            raise ValueError("give kv_memory_gb or kv_memory_fraction, not both")
+        if kv_memory_fraction is not None:
+            # a share of what the device has free now that the weights are on it
+            if not 0.0 < float(kv_memory_fraction) <= 1.0:
+                raise ValueError(f"kv_memory_fraction must lie in (0, 1], got {kv_memory_fraction}")
+            if self.model.device.type != "cuda":
+                raise ValueError("kv_memory_fraction needs a CUDA device to ask for its free memory")
+            free_bytes, _total = torch.cuda.mem_get_info(self.model.device)
+            pool_tokens = max(int(float(kv_memory_fraction) * free_bytes) // max(bytes_per_token, 1), page_size)
+        elif kv_memory_gb is None:
             pool_tokens = self.max_bsz * self.max_len
         else:
             pool_tokens = max(int(kv_memory_gb * (1 << 30)) // max(bytes_per_token, 1), page_size)
