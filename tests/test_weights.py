@@ -177,3 +177,26 @@ def test_later_paths_override_earlier_ones(tmp_path):
     write_safetensors(tmp_path / "patch.safetensors", {"norm.weight": torch.full((64,), 2.0)})
     _, _, model = load_model([base, tmp_path / "patch.safetensors"], dtype="float32", device="cpu", ops=OPS)
     assert torch.equal(model.final_norm.weight, torch.full((64,), 2.0))
+
+
+def test_random_weights_command_line_writes_a_loadable_folder(tmp_path):
+    """``python -m torchllms_b200.weights.random_init``: configuration + seed -> model folder."""
+    import json
+    import subprocess
+    import sys
+
+    from torch_ops import TorchOps
+    from torchllms_b200.engine.loading import load_model
+    cfg_file = tmp_path / "some_config.json"
+    cfg_file.write_text(json.dumps(TINY_B))
+    outs = []
+    for seed, name in ((3, "a"), (3, "b"), (4, "c")):
+        run = subprocess.run([sys.executable, "-m", "torchllms_b200.weights.random_init", "--config", str(cfg_file),
+                              "--seed", str(seed), "--out", str(tmp_path / name), "--dtype", "float32"],
+                             capture_output=True, text=True)
+        assert run.returncode == 0, run.stderr
+        assert sorted(p.name for p in (tmp_path / name).iterdir()) == ["config.json", "model.safetensors"]
+        outs.append((tmp_path / name / "model.safetensors").read_bytes())
+    assert outs[0] == outs[1] and outs[0] != outs[2]            # the seed decides, and nothing else
+    _, config, model = load_model(tmp_path / "a", dtype="float32", device="cpu", ops=TorchOps())
+    assert config.n_layers == TINY_B["num_hidden_layers"] and config.vocab_size == TINY_B["vocab_size"]

@@ -32,3 +32,33 @@ def write_random_model(out_dir, config, seed: int, *, dtype: torch.dtype = torch
                       arch.random_tensors(config, seed, device="cpu", dtype=dtype, **init),
                       metadata={"format": "pt", "seed": str(seed)})
     return out_dir
+
+
+def main(argv=None) -> None:
+    """``python -m torchllms_b200.weights.random_init --config config.json --seed 0 --out DIR``"""
+    import argparse
+
+    from ..config.registry import architecture_of, load_config
+    from ..engine.loading import parse_dtype
+
+    p = argparse.ArgumentParser(description="Write a model folder with random weights for a configuration.")
+    p.add_argument("--config", required=True, help="A config.json or params.json, or a folder that holds one.")
+    p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--out", required=True, help="Folder to write config.json and model.safetensors into.")
+    p.add_argument("--dtype", default="bfloat16", help="Stored dtype: bfloat16 or float32.")
+    args = p.parse_args(argv)
+    src = Path(args.config)
+    if src.is_dir():
+        arch, config = load_config(src)
+    else:
+        with open(src) as f:
+            raw = json.load(f)
+        kind = "params.json" if "dim" in raw and "hidden_size" not in raw else "config.json"
+        arch = architecture_of(raw, kind)
+        config = arch.parse_config(raw, str(src))
+    folder = write_random_model(args.out, config, args.seed, dtype=parse_dtype(args.dtype), arch=arch)
+    print(folder)
+
+
+if __name__ == "__main__":
+    main()
