@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+    python bench.py --workload serve_1b | long_3b      (secondary: whole serving runs, a JSON line each)
 
 The workload is the Llama-3.1-8B shape (32 layers, dim 4096, 32 heads, 8 kv heads, head_dim 128,
 SwiGLU hidden 14336, vocabulary 128256, llama3 rope scaling, untied head) in bfloat16 with random
@@ -144,6 +145,74 @@ def reference_arm(args):
     return 0
 
 
+# ---------------------------------------------------------------------- secondary serving workloads
+SERVE = {
+    # 64 requests at once, prompts uniform in 128..4096, 256 new tokens each, greedy: chunked prefill beside decoding
+    "serve_1b": dict(shape=dict(n_layers=16, dim=2048, n_heads=32, n_kv_heads=8, head_dim=64, ffn_hidden=8192,
+                                vocab_size=128256, norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=True),
+                     rope=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                               original_max_position_embeddings=8192),
+                     requests=64, prompt=(128, 4096), new_tokens=256, temperature=0.0, name="llama-3.2-1b-shape"),
+    # 32 requests with 16,384-token prompts, 512 new tokens each at temperature 1
+    "long_3b": dict(shape=dict(n_layers=28, dim=3072, n_heads=24, n_kv_heads=8, head_dim=128, ffn_hidden=8192,
+                               vocab_size=128256, norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=True),
+                    rope=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                              original_max_position_embeddings=8192),
+                    requests=32, prompt=(16384, 16384), new_tokens=512, temperature=1.0, name="llama-3.2-3b-shape"),
+}
+
+
+def serving_workload(args):
+    """A whole serving run through ``LLM.generate`` (continuous batching, prompts cut into portions of
+    2,048 tokens beside decoded tokens): one JSON line with tokens per second, wall clock around the call
+    (host token lists in, host token lists out)."""
+    import random
+
+    import torch
+    from torchllms_b200.config import LlamaConfig, RopeScaling
+    from torchllms_b200.inference import LLM
+
+    w = SERVE[args.workload]
+    lo, hi = w["prompt"]
+    max_len = hi + w["new_tokens"] + 16
+    cfg = LlamaConfig(architecture="LlamaForCausalLM", rope_scaling=RopeScaling(**w["rope"]), max_seq_len=max_len, **w["shape"])
+    llm = LLM(config=cfg, random_seed=0, precision="bfloat16", max_len=max_len, max_bsz=w["requests"],
+              max_num_batched_tokens=2048 + w["requests"], prefill_chunk=2048, page_size=16)
+    llm.warmup()
+    rng = random.Random(0)
+    gen = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (rng.randint(lo, hi),), generator=gen).tolist() for _ in range(w["requests"])]
+    llm.generate(prompt_token_ids=[p[:64] for p in prompts[:4]], max_new_tokens=4)      # warm the path
+    ops = llm.model.ops
+    launches0 = ops.launches
+    with ClockSampler() as clocks:
+        torch.cuda.synchronize()
+        t0 = time.time()
+        out = llm.generate(prompt_token_ids=prompts, max_new_tokens=w["new_tokens"], temperature=w["temperature"], seed=1)
+        torch.cuda.synchronize()
+        t1 = time.time()
+        clocks.mark(t0, t1)
+        time.sleep(0.15)
+    st = llm.last_stats
+    n_prompt = sum(len(p) for p in prompts)
+    n_new = sum(len(o.token_ids) for o in out)
+    secs = t1 - t0
+    print(json.dumps({
+        "metric": f"tokens/s through LLM.generate, {args.workload} (prompt and generated tokens)",
+        "value": round((n_prompt + n_new) / secs, 1), "unit": "tokens/s", "n_gpus": 1, "steps": st.steps, "warmup": 1,
+        "ms_per_step": round(secs * 1e3 / max(st.steps, 1), 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights N(0, 0.02))",
+        "generated_tokens_per_s": round(n_new / secs, 1), "seconds": round(secs, 3),
+        "config": {"model": w["name"], "n_layers": cfg.n_layers, "dim": cfg.dim, "n_heads": cfg.n_heads,
+                   "n_kv_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim, "ffn_hidden": cfg.ffn_hidden,
+                   "vocab_size": cfg.vocab_size, "global_batch": w["requests"], "prompt_min": lo, "prompt_max": hi,
+                   "new_tokens": w["new_tokens"], "temperature": w["temperature"], "prefill_chunk": 2048,
+                   "page_size": 16, "prompt_tokens": n_prompt, "parallelism": "single-gpu"},
+        "gpu_launches": ops.launches - launches0, "preemptions": st.preemptions, "clocks": clocks.summary(),
+    }))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -153,6 +222,8 @@ def main():
     ap.add_argument("--layers", type=int, default=SHAPE_8B["n_layers"], help="fewer layers than the shape has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch and the prefill")
+    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b"] + sorted(SERVE),
+                    help="decode_8b: the headline (default); serve_1b, long_3b: whole serving runs through LLM.generate")
     ap.add_argument("--profile", action="store_true",
                     help="also print, on standard error, per-kernel times of one prefill and one decode step")
     args = ap.parse_args()
@@ -161,6 +232,8 @@ def main():
         return 2
     if args.impl == "reference":
         return reference_arm(args)
+    if args.workload != "decode_8b":
+        return serving_workload(args)
     args.warmup = max(args.warmup, 3)
 
     import torch
