@@ -145,7 +145,10 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 3 : 2) attention_decode_ke
     __shared__ int failed_flag;
 
     grid_launch_dependents();
-    grid_dependency_wait();
+    // What follows, down to the dependency wait, reads nothing that the kernels just before this one
+    // write: the step's index data were uploaded before its first kernel, and keys and values of
+    // positions before the step's own tokens were written by earlier steps.  Under programmatic
+    // dependent launch this part runs while the predecessor is still at work.
     const int b = blockIdx.z;
     const int qs = p.q_start[b];
     const int ql = p.q_start[b + 1] - qs;
@@ -209,7 +212,14 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 3 : 2) attention_decode_ke
             mbar_init(&empty_bar[s], NCW);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        for (int it = 0; it < STAGES && it < n_tiles; ++it) issue_tile(it);
+        // tiles that end before the step's first new position can go now; a tile that may hold a key
+        // written by the predecessor (only the last tile of the last split can) waits for it
+        int it = 0;
+        for (; it < STAGES && it < n_tiles && k_start + (it + 1) * BN <= qpos_base; ++it) issue_tile(it);
+        grid_dependency_wait();
+        for (; it < STAGES && it < n_tiles; ++it) issue_tile(it);
+    } else {
+        grid_dependency_wait();
     }
     // queries (zero rows where the tile has none)
     for (int c = tid; c < 16 * (HD / 8); c += NTHREADS) {
@@ -414,27 +424,34 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 3 : 2) attention_decode_ke
     }
     __syncthreads();
     const int n_rows = min(p.tpw, ql - tok0) * ng;
-    for (int idx = tid; idx < n_rows * HD; idx += NTHREADS) {
-        const int rr = idx / HD, d = idx - rr * HD;
+    for (int idx = tid; idx < n_rows * (HD / 4); idx += NTHREADS) {      // four columns of a row per turn
+        const int rr = idx / (HD / 4), d = (idx - rr * (HD / 4)) * 4;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < NCW; ++w) M = fmaxf(M, Mm[w * NROWS + rr]);
-        float num = 0.f, den = 0.f;
+        float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+        float den = 0.f;
 #pragma unroll
         for (int w = 0; w < NCW; ++w) {
             const float mw = Mm[w * NROWS + rr];
             if (mw == -INFINITY) continue;
             const float f = exp2f(mw - M);
-            num = fmaf(f, Om[(w * NROWS + rr) * OPITCH + d], num);
+            const float4 o4 = *reinterpret_cast<const float4*>(Om + (w * NROWS + rr) * OPITCH + d);
+            num.x = fmaf(f, o4.x, num.x); num.y = fmaf(f, o4.y, num.y);
+            num.z = fmaf(f, o4.z, num.z); num.w = fmaf(f, o4.w, num.w);
             den = fmaf(f, Lm[w * NROWS + rr], den);
         }
         const int tok = qs + tok0 + rr / ng;
         const int head = kvh * p.group + g0 + rr % ng;
         const size_t row = (size_t)tok * p.n_heads + head;
         if (p.n_splits == 1) {
-            p.out[row * HD + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+            const float inv = den > 0.f ? 1.f / den : 0.f;
+            uint2 w2;
+            w2.x = pack_bf16(num.x * inv, num.y * inv);
+            w2.y = pack_bf16(num.z * inv, num.w * inv);
+            *reinterpret_cast<uint2*>(p.out + row * HD + d) = w2;
         } else {
-            p.part_o[(row * p.n_splits + split) * HD + d] = num;
+            *reinterpret_cast<float4*>(p.part_o + (row * p.n_splits + split) * HD + d) = num;
             if (d == 0) {
                 p.part_ml[(row * p.n_splits + split) * 2] = (M == -INFINITY) ? -INFINITY : M * LN2;   // natural-log scale
                 p.part_ml[(row * p.n_splits + split) * 2 + 1] = den;
