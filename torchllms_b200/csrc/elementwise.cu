@@ -48,9 +48,12 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
     extern __shared__ __align__(16) float row_buf[];  // the summed row, kept for the second pass
     __shared__ float warp_part[32];
     grid_launch_dependents();
-    grid_dependency_wait();
+    // the row index and the norm's weight do not come from the kernel before this one
     const int o = blockIdx.x;
     const int r = rows ? rows[o] : o;
+    float4 w_first = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (VEC == 4 && threadIdx.x * 4 < dim) w_first = load4(weight + threadIdx.x * 4);
+    grid_dependency_wait();
     float* hr = h + (size_t)r * dim;
     const TD* dr = delta ? delta + (size_t)r * dim : nullptr;
     float ss = 0.f;
@@ -95,7 +98,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
     if (VEC == 4) {
         for (int d = threadIdx.x * 4; d < dim; d += blockDim.x * 4) {   // each thread re-reads what it wrote
             const float4 x = load4(row_buf + d);
-            const float4 w = load4(weight + d);
+            const float4 w = d == (int)threadIdx.x * 4 ? w_first : load4(weight + d);
             if (write_back) store4(hr + d, x);
             store4(orow + d, make_float4(x.x * rstd * w.x, x.y * rstd * w.y, x.z * rstd * w.z, x.w * rstd * w.w));
         }

@@ -107,7 +107,8 @@ __global__ void rope_kv_write_vec_kernel(const TI* __restrict__ qkv, int splits,
                                          T* __restrict__ k_pages, T* __restrict__ v_pages, int n_heads, int n_kv_heads,
                                          int head_dim, int page_size, int table_rows) {
     grid_launch_dependents();
-    grid_dependency_wait();
+    // positions, cache slots and the rotation table do not come from the kernel before this one (the
+    // step's index data were uploaded before its first kernel): they are fetched before waiting for it
     const int t = blockIdx.x;
     const int heads = n_heads + 2 * n_kv_heads;
     const int per_head = head_dim >> 3;
@@ -122,7 +123,12 @@ __global__ void rope_kv_write_vec_kernel(const TI* __restrict__ qkv, int splits,
         page = sm / page_size;
         slot = sm - page * page_size;
     }
-    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < heads * per_head; c += gridDim.y * blockDim.x) {
+    const int c_first = blockIdx.y * blockDim.x + threadIdx.x;
+    float r_first[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (c_first < heads * per_head && c_first / per_head < n_heads + n_kv_heads)
+        load8(cs + ((c_first - (c_first / per_head) * per_head) << 3), r_first);
+    grid_dependency_wait();
+    for (int c = c_first; c < heads * per_head; c += gridDim.y * blockDim.x) {
         const int head = c / per_head;
         const int off = (c - head * per_head) << 3;
         float x[8];
@@ -135,7 +141,12 @@ __global__ void rope_kv_write_vec_kernel(const TI* __restrict__ qkv, int splits,
         }
         if (head < n_heads + n_kv_heads) {
             float r[8];
-            load8(cs + off, r);          // (cos, sin) of the four pairs
+            if (c == c_first) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) r[i] = r_first[i];
+            } else {
+                load8(cs + off, r);      // (cos, sin) of the four pairs
+            }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float a = x[2 * i], b = x[2 * i + 1], co = r[2 * i], si = r[2 * i + 1];
