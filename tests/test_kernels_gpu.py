@@ -322,6 +322,28 @@ def test_decode_attention_split_over_keys(ops, dtype, impl, B, L):
     torch.testing.assert_close(whole.float(), want.float(), atol=t, rtol=t)
 
 
+@pytest.mark.parametrize("n_splits", [2, 3, 6, 8, 12])
+@pytest.mark.parametrize("case", [
+    ([2000, 1987, 300], [1, 1, 1], 8, 2, 64, 16, None),
+    ([1000, 130, 5, 64], [1, 1, 1, 1], 32, 8, 128, 16, None),     # short requests leave some splits without keys
+    ([700, 45], [3, 4], 32, 8, 128, 16, None),                    # 16 rows to a tile
+    ([1500, 1499, 3], [1, 1, 1], 32, 8, 128, 16, 512),            # behind a window
+    ([900, 130], [2, 1], 16, 2, 64, 32, 77),                      # a window narrower than the splits
+], ids=["hd64", "8b", "rows16", "window", "narrow"])
+def test_decode_attention_with_a_given_number_of_splits(ops, case, n_splits):
+    """However many CTAs share a request's keys, the merged result is what one CTA per request
+    gives, also where some splits see no key at all."""
+    seq_lens, q_lens, H, KV, hd, P, window = case
+    a = build_paged(seq_lens, q_lens, H, KV, hd, P, torch.bfloat16, seed=n_splits)
+    scale = hd ** -0.5
+    got = ops.paged_attention(**a, scale=scale, window=window, allow_split=n_splits, impl="decode")
+    whole = ops.paged_attention(**a, scale=scale, window=window, allow_split=False, impl="decode")
+    want = TWIN.paged_attention(**a, scale=scale, window=window)
+    ops.check_status()
+    torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(got.float(), whole.float(), atol=1e-2, rtol=1e-2)
+
+
 @pytest.mark.parametrize("dtype,impl", IMPLS)
 @pytest.mark.parametrize("key_pos", [0, 15, 16, 511, 640])
 def test_attention_finds_one_far_key_among_hundreds(ops, dtype, impl, key_pos):

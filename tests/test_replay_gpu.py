@@ -105,3 +105,37 @@ def test_replay_first_tokens_and_long_decoding(setups, tmp_path, dtype):
     places = {i: [(rid, i)] for i in range(len(toks))}
     got = run_trace(folder, dtype, steps, tmp_path / "out", max_tokens=256)
     compare(got, places, ref, tol)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_decoding_past_a_context_bound(tmp_path, dtype):
+    """Decode steps plan their attention (over how many CTAs the keys are split) for the power of two
+    that holds the longest context, and are recorded once per such bound.  A request that grows from
+    990 to 1,070 tokens one by one crosses the bound at 1,024 beside a short request: other plan,
+    other recorded step, same logits."""
+    from helpers import TINY_C, make_tensors, write_model_folder
+    cfg = dict(TINY_C, max_position_embeddings=4096)
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = write_model_folder(tmp_path / "tiny_long", cfg, make_tensors(cfg, 5, std=0.05, qk_std=0.25), store)
+    rng = random.Random(11)
+    reqs = {"long": [rng.randrange(cfg["vocab_size"]) for _ in range(1070)],
+            "short": [rng.randrange(cfg["vocab_size"]) for _ in range(120)]}
+    plain = PlainModel(folder)
+    if dtype == "float32":
+        ref = {rid: plain.logits(t).numpy() for rid, t in reqs.items()}
+        tol = F32_ATOL
+    else:
+        ref = {rid: plain.logits(t, stored=to_bfloat16_and_back).numpy() for rid, t in reqs.items()}
+        tol = BF16_SHARE * max(float(np.abs(ref[rid] - plain.logits(t).numpy()).max()) for rid, t in reqs.items())
+    head = {"long": 990, "short": 40}
+    steps = [{"step": 0, "entries": [{"id": "long", "tokens": reqs["long"][:990], "want": [989]}], "end": []},
+             {"step": 1, "entries": [{"id": "short", "tokens": reqs["short"][:40], "want": [39]}], "end": []}]
+    places = {0: [("long", 989)], 1: [("short", 39)]}
+    for i in range(80):
+        step = len(steps)
+        steps.append({"step": step, "entries": [{"id": "long", "tokens": [reqs["long"][990 + i]], "want": [0]},
+                                                {"id": "short", "tokens": [reqs["short"][40 + i]], "want": [0]}],
+                      "end": ["long", "short"] if i == 79 else []})
+        places[step] = [("long", 990 + i), ("short", 40 + i)]
+    got = run_trace(folder, dtype, steps, tmp_path / "out", max_tokens=1088 + 128)
+    compare(got, places, ref, tol)

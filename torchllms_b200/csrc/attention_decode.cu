@@ -566,10 +566,15 @@ Plan make_plan(int n_seqs, int n_heads, int n_kv_heads, int head_dim, int max_q_
     pl.tpw = 16 / pl.ng;
     pl.n_q_tiles = (max_q_len + pl.tpw - 1) / pl.tpw;
     pl.n_splits = 1;
-    if (allow_split && max_kv_len >= 2 * MIN_SPLIT) {
+    if (allow_split > 1) {                       // a given number of splits (tests and measurements)
+        pl.n_splits = allow_split < MERGE_MAX_SPLITS ? allow_split : MERGE_MAX_SPLITS;
+    } else if (allow_split && max_kv_len >= 2 * MIN_SPLIT) {
         // CTAs run in waves; with s splits a CTA does 1/s of the keys.  Pick the s that makes
-        // (waves / s), the time in units of one unsplit CTA, smallest, charging each split a
-        // little for its partial results and the merge.
+        // (waves / s), the time in units of one unsplit CTA, smallest.  While everything fits one
+        // wave, more splits cost next to nothing (a CTA walks its tiles one after the other, so few
+        // CTAs with long walks leave most of the memory system idle: one request of 8,192 keys
+        // takes 21.8 us in 8 splits and 11.2 us in 32); beyond one wave each split is charged
+        // for its partial results and the merge.
         const size_t per_cta = head_dim == 128 ? smem_for<128>() : smem_for<64>();
         int per_sm = (int)((size_t)224 * 1024 / (per_cta + 1024));
         if (per_sm > 6) per_sm = 6;
@@ -580,7 +585,7 @@ Plan make_plan(int n_seqs, int n_heads, int n_kv_heads, int head_dim, int max_q_
         double best = 1e30;
         for (int sp = 1; sp <= most; ++sp) {
             const long long waves = (base * sp + slots - 1) / slots;
-            const double cost = (double)waves / sp + 0.01 * sp;
+            const double cost = (double)waves / sp + (waves == 1 ? 0.0005 : 0.01) * sp;
             if (cost < best - 1e-9) {
                 best = cost;
                 pl.n_splits = sp;

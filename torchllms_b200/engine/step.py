@@ -163,10 +163,12 @@ class Engine:
         self.vocab_size = model.spec.vocab_size
         self.steps_run = 0
         self.tokens_run = 0
-        # A step's launch shapes depend only on (tokens, requests, wanted rows, longest portion), never
-        # on how long the requests have grown: the kernels read lengths and tables from the uploaded
-        # buffers.  So a shape that keeps coming back (every decode step with the same number of
-        # requests; every full prompt chunk) is recorded once into a CUDA graph and replayed.
+        # A step's launch shapes depend only on (tokens, requests, wanted rows, longest portion) and, for
+        # steps of short portions, on a coarse bound of the longest context (a power of two: it decides
+        # over how many CTAs the keys are split), never on the exact lengths: the kernels read lengths
+        # and tables from the uploaded buffers.  So a shape that keeps coming back (every decode step
+        # with the same number of requests; every full prompt chunk) is recorded once into a CUDA graph
+        # and replayed.
         ops = model.ops
         self.use_graphs = bool(use_graphs and self.device.type == "cuda" and model.graph_safe
                                and getattr(ops, "graph_capturable", lambda d: False)(model.dtype))
@@ -175,6 +177,7 @@ class Engine:
         self.max_prompt_graphs = 16   # recorded shapes other than decode steps (each keeps its activations)
         self._graph_pool = None
         self.graph_replays = 0
+        self._forced_bound: Optional[int] = None      # capture_decode_graphs: record for this context bound
 
     # ----------------------------------------------------------------- requests
     def claim(self) -> int:
@@ -190,7 +193,8 @@ class Engine:
         """A decode shape is recorded the second time it occurs, any other shape the third time
         (while fewer than ``max_prompt_graphs`` of those exist); later steps replay.  The logits
         buffer of a shape is reused: its contents hold until the next step of that shape."""
-        key = self._shape_key(ctx.n_tokens, ctx.n_seqs, ctx.n_want, ctx.max_q_len, ctx.n_decode)
+        key = self._shape_key(ctx.n_tokens, ctx.n_seqs, ctx.n_want, ctx.max_q_len, ctx.n_decode,
+                              ctx.max_kv_len if ctx.max_q_len <= 16 else 0)
         entry = self._graphs.get(key)
         if entry is None:
             seen = self._graph_seen.get(key, 0)
@@ -214,8 +218,16 @@ class Engine:
         return self._replay(entry)
 
     @staticmethod
-    def _shape_key(n_tokens: int, n_seqs: int, n_want: int, max_q_len: int, n_decode: int):
-        return (n_tokens, n_seqs, n_want, max_q_len, n_decode)
+    def _shape_key(n_tokens: int, n_seqs: int, n_want: int, max_q_len: int, n_decode: int, kv_bound: int):
+        return (n_tokens, n_seqs, n_want, max_q_len, n_decode, kv_bound)
+
+    def kv_bound(self, longest: int) -> int:
+        """The bound that steps of short portions plan their attention for: the power of two (at
+        least 1,024, at most ``max_len``) that holds the longest context of the step."""
+        b = 1024
+        while b < longest:
+            b *= 2
+        return min(b, self.max_len)
 
     def _replay(self, entry) -> Optional[torch.Tensor]:
         entry[0].replay()
@@ -224,26 +236,31 @@ class Engine:
             self.model.ops.launches += entry[2]
         return entry[1]
 
-    def capture_decode_graphs(self, batch_sizes: Sequence[int]) -> int:
-        """Record the decode-step graphs for these numbers of requests ahead of time, with
-        throw-away requests (the cache must have room for one page each).  Returns how many
-        graphs exist afterwards.  Without this a shape is recorded the second time it occurs."""
+    def capture_decode_graphs(self, batch_sizes: Sequence[int], context_lengths: Sequence[int] = (1,)) -> int:
+        """Record the decode-step graphs for these numbers of requests, and for contexts of these
+        lengths (each stands for its power-of-two bound), ahead of time, with throw-away requests
+        (the cache must have room for one page each).  Returns how many graphs exist afterwards.
+        Without this a shape is recorded the second time it occurs."""
         if not self.use_graphs:
             return 0
+        bounds = sorted(set(self.kv_bound(int(n)) for n in context_lengths))
         for b in sorted(set(int(x) for x in batch_sizes)):
-            if b < 1 or b > self.cache.max_num_seqs or self._shape_key(b, b, b, 1, b) in self._graphs:
-                continue
-            if self.cache.n_live() + b > self.cache.max_num_seqs:
-                continue
-            handles = [self.claim() for _ in range(b)]
-            try:
-                for _ in range(3):          # one token each: eager, eager (first sight), recorded
-                    self.step([StepEntry(h, [0]) for h in handles])
-            except OutOfPages:
-                pass
-            finally:
-                for h in handles:
-                    self.release(h)
+            for bound in bounds:
+                if b < 1 or b > self.cache.max_num_seqs or self._shape_key(b, b, b, 1, b, bound) in self._graphs:
+                    continue
+                if self.cache.n_live() + b > self.cache.max_num_seqs:
+                    continue
+                handles = [self.claim() for _ in range(b)]
+                self._forced_bound = bound
+                try:
+                    for _ in range(3):          # one token each: eager, eager (first sight), recorded
+                        self.step([StepEntry(h, [0]) for h in handles])
+                except OutOfPages:
+                    pass
+                finally:
+                    self._forced_bound = None
+                    for h in handles:
+                        self.release(h)
         torch.cuda.synchronize()
         return len(self._graphs)
 
@@ -359,16 +376,18 @@ class Engine:
             n_decode = 0
             while n_decode < B and q_lens[n_decode] == 1:
                 n_decode += 1
-            recorded = self._graphs.get(self._shape_key(T, B, n_want, max_q, n_decode)) if self.use_graphs else None
+            # steps of short portions (where keys may be split over CTAs) plan for a coarse bound of the
+            # longest context, so that their launch shapes change only when a request outgrows it
+            short = max_q <= 16
+            bound = (self._forced_bound or self.kv_bound(max(kv_lens))) if short else 0
+            recorded = self._graphs.get(self._shape_key(T, B, n_want, max_q, n_decode, bound)) if self.use_graphs else None
             if recorded is not None:
                 # the graph reads the buffers uploaded above at their fixed addresses: nothing else to build
                 logits = self._replay(recorded)
             else:
                 ctx = StepContext(
                     n_tokens=T, n_seqs=B, n_want=n_want, max_q_len=max_q, n_decode=n_decode,
-                    # steps of short portions (where keys may be split over CTAs) plan for the longest
-                    # sequence there can be, so that their launch shapes do not depend on the lengths
-                    max_kv_len=self.max_len if max_q <= 16 else max(kv_lens),
+                    max_kv_len=bound if short else max(kv_lens),
                     token_ids=buf.dev_view("token_ids", T), positions=buf.dev_view("positions", T),
                     seq_of_token=buf.dev_view("seq_of_token", T), q_start=buf.dev_view("q_start", B + 1),
                     kv_len=buf.dev_view("kv_len", B), state_slot=buf.dev_view("state_slot", B),

@@ -400,7 +400,8 @@ class NativeOps:
         ``block_table``, ``q_start`` and ``kv_len`` may be slices that cover only some requests of
         the step (``q_start`` keeps counting tokens from the start of ``q``); ``n_tokens`` then
         bounds the rows those requests own (default: all of ``q``), and ``out`` lets several such
-        calls fill one tensor."""
+        calls fill one tensor.  ``allow_split``: False keeps every request's keys in one CTA, True lets
+        the kernel split them as it sees fit; the decode kernel also takes a number of splits (above 1)."""
         _cuda_contig(q, "q")
         _cuda_contig(k_pages, "k_pages", q.dtype)
         _cuda_contig(v_pages, "v_pages", q.dtype)
@@ -453,14 +454,14 @@ class NativeOps:
         if decode_ok:
             lib = self._lib("attention_decode")
             rc = lib.tl_attention_decode_plan(T, n_seqs, n_heads, n_kv_heads, head_dim, max_q_len, max_kv_len,
-                                              1 if allow_split else 0, ctypes.byref(n_splits), ctypes.byref(floats))
+                                              int(allow_split), ctypes.byref(n_splits), ctypes.byref(floats))
             _check(rc, "attention_decode_plan")
             ws = self._scratch(q.device, floats.value)
             rc = lib.tl_paged_attention_decode(
                 _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
                 _ptr(q_start), _ptr(kv_len), _ptr(ws), ctypes.c_void_p(self._status.data_ptr()), T, n_seqs,
                 n_heads, n_kv_heads, head_dim, page_size, ctypes.c_longlong(k_pages.shape[0]), max_q_len, max_kv_len,
-                int(window or 0), ctypes.c_float(scale), 1 if allow_split else 0, _stream())
+                int(window or 0), ctypes.c_float(scale), int(allow_split), _stream())
             _check(rc, "paged_attention_decode")
         elif use_mma:
             lib = self._lib("attention_mma")
