@@ -224,6 +224,8 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch and the prefill")
     ap.add_argument("--workload", default="decode_8b", choices=["decode_8b"] + sorted(SERVE),
                     help="decode_8b: the headline (default); serve_1b, long_3b: whole serving runs through LLM.generate")
+    ap.add_argument("--timeline", action="store_true",
+                    help="also print, on standard error, start and end of every kernel of one decode step in place")
     ap.add_argument("--profile", action="store_true",
                     help="also print, on standard error, per-kernel times of one prefill and one decode step")
     args = ap.parse_args()
@@ -346,6 +348,38 @@ def main():
         for x in [h] + hs:
             engine.release(x)
         engine.use_graphs = True
+
+    if args.timeline:
+        # Start and end of every kernel of one recorded decode step as the device ran it, kernels
+        # overlapping where programmatic dependent launch lets them (CUPTI through torch.profiler; the
+        # tracing stretches the step by a few per cent).  "+x" is the time from the end of the kernel
+        # before it to its own end: what the kernel added to the step.
+        from torch.profiler import ProfilerActivity, profile
+        hs = [engine.claim() for _ in range(args.batch)]
+        for x in hs:
+            engine.step([StepEntry(x, prompts(1)[0], [])])
+
+        def one():
+            ops.sample(engine.step([StepEntry(x, [1]) for x in hs]))
+        for _ in range(6):
+            one()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(3):
+                one()
+            torch.cuda.synchronize()
+        evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                     key=lambda e: e.time_range.start)
+        last = evs[-(len(evs) // 3):]
+        t0, prev = last[0].time_range.start, 0.0
+        print(f"-- one decode step, batch {args.batch}, context 2,048, {args.layers} layers: kernels in place (us)", file=sys.stderr)
+        for e in last:
+            a, b = e.time_range.start - t0, e.time_range.end - t0
+            name = e.name.replace("void ", "").replace("(anonymous namespace)::", "")
+            print(f"   {name[:44]:44s} start {a:8.1f}  end {b:8.1f}  {b - prev:+7.1f}", file=sys.stderr)
+            prev = b
+        for x in hs:
+            engine.release(x)
 
     # ------------------------------------------------------------------ end to end through LLM.generate
     n_new = args.warmup + args.steps
