@@ -221,13 +221,24 @@ class Engine:
     def _shape_key(n_tokens: int, n_seqs: int, n_want: int, max_q_len: int, n_decode: int, kv_bound: int):
         return (n_tokens, n_seqs, n_want, max_q_len, n_decode, kv_bound)
 
-    def kv_bound(self, longest: int) -> int:
-        """The bound that steps of short portions plan their attention for: the power of two (at
-        least 1,024, at most ``max_len``) that holds the longest context of the step."""
+    BOUND_BELOW = 16     # steps of fewer requests plan for a bound of their longest context, others for max_len
+
+    def kv_bound(self, longest: int, n_seqs: int) -> int:
+        """The context length that a step of short portions plans its attention for.  With few
+        requests the kernel splits each one's keys over many CTAs, as many as the length allows:
+        such steps plan for the power of two (at least 1,024, at most ``max_len``) that holds their
+        longest context.  With ``BOUND_BELOW`` requests or more the requests themselves fill the GPU
+        and the plan does not depend on the length: they plan for ``max_len``."""
+        if n_seqs >= self.BOUND_BELOW:
+            return self.max_len
         b = 1024
         while b < longest:
             b *= 2
         return min(b, self.max_len)
+
+    def kv_bounds(self, n_seqs: int) -> List[int]:
+        """Every value ``kv_bound`` can take for this many requests."""
+        return sorted(set(self.kv_bound(1 << k, n_seqs) for k in range(10, max(self.max_len, 1024).bit_length() + 1)))
 
     def _replay(self, entry) -> Optional[torch.Tensor]:
         entry[0].replay()
@@ -236,15 +247,16 @@ class Engine:
             self.model.ops.launches += entry[2]
         return entry[1]
 
-    def capture_decode_graphs(self, batch_sizes: Sequence[int], context_lengths: Sequence[int] = (1,)) -> int:
-        """Record the decode-step graphs for these numbers of requests, and for contexts of these
-        lengths (each stands for its power-of-two bound), ahead of time, with throw-away requests
-        (the cache must have room for one page each).  Returns how many graphs exist afterwards.
-        Without this a shape is recorded the second time it occurs."""
+    def capture_decode_graphs(self, batch_sizes: Sequence[int], context_lengths: Optional[Sequence[int]] = None) -> int:
+        """Record the decode-step graphs for these numbers of requests ahead of time, with throw-away
+        requests (the cache must have room for one page each): for every context bound that steps of
+        so many requests can plan for (``kv_bounds``), or only for those of the given context
+        lengths.  Returns how many graphs exist afterwards.  Without this a shape is recorded the
+        second time it occurs."""
         if not self.use_graphs:
             return 0
-        bounds = sorted(set(self.kv_bound(int(n)) for n in context_lengths))
         for b in sorted(set(int(x) for x in batch_sizes)):
+            bounds = self.kv_bounds(b) if context_lengths is None else sorted(set(self.kv_bound(int(n), b) for n in context_lengths))
             for bound in bounds:
                 if b < 1 or b > self.cache.max_num_seqs or self._shape_key(b, b, b, 1, b, bound) in self._graphs:
                     continue
@@ -379,7 +391,7 @@ class Engine:
             # steps of short portions (where keys may be split over CTAs) plan for a coarse bound of the
             # longest context, so that their launch shapes change only when a request outgrows it
             short = max_q <= 16
-            bound = (self._forced_bound or self.kv_bound(max(kv_lens))) if short else 0
+            bound = (self._forced_bound or self.kv_bound(max(kv_lens), B)) if short else 0
             recorded = self._graphs.get(self._shape_key(T, B, n_want, max_q, n_decode, bound)) if self.use_graphs else None
             if recorded is not None:
                 # the graph reads the buffers uploaded above at their fixed addresses: nothing else to build

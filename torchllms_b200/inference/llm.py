@@ -126,13 +126,12 @@ class LLM:
         self.eos_set = set(self.eos_ids)
         self.last_stats = None
 
-    def warmup(self, batch_sizes: Optional[Sequence[int]] = None, context_lengths: Sequence[int] = (1,)) -> int:
+    def warmup(self, batch_sizes: Optional[Sequence[int]] = None, context_lengths: Optional[Sequence[int]] = None) -> int:
         """Record the CUDA graphs of decode steps for these numbers of running requests (default:
         every number up to ``max_bsz``) before the first request arrives; returns how many exist.
-        A decode step plans its attention for the power of two that holds its longest context, so
-        there is one graph per number of requests and such bound: ``context_lengths`` names the
-        context lengths to prepare for (default: short ones only; the others are recorded the second
-        time they occur)."""
+        A step of few requests plans its attention for the power of two that holds its longest
+        context, so for those there is one graph per such bound: all of them are recorded, or only
+        those that ``context_lengths`` names (the others then the second time they occur)."""
         sizes = list(batch_sizes) if batch_sizes is not None else list(range(1, self.max_bsz + 1))
         return self.engine.capture_decode_graphs(sizes, context_lengths)
 
