@@ -105,3 +105,17 @@ def test_a_step_in_two_halves_and_a_step_called_off(setups):
     with pytest.raises(StepError):
         eng.run_prepared(eng.prepare([(a, 1, None)]), pool, rows=[3])    # no such row
     eng.cache.check_invariants()
+
+
+def test_the_context_bound_that_steps_of_short_portions_plan_for(setups):
+    """Few requests plan for the power of two that holds their longest context (at least 1,024, at
+    most the engine's limit), sixteen or more for the limit itself."""
+    folder, page, _, _ = setups["A"]
+    eng = Replayer(folder, "float32", 64, page_size=page, device="cpu", ops=TorchOps()).engine
+    assert eng.max_len == 128
+    assert eng.kv_bound(1, 1) == eng.kv_bound(128, 3) == 128 and eng.kv_bounds(1) == [128]
+    eng.max_len = 5000                                    # (the arithmetic only: no step runs with it)
+    assert [eng.kv_bound(n, 2) for n in (1, 1024, 1025, 2048, 2049, 4096, 4097, 5000)] == \
+           [1024, 1024, 2048, 2048, 4096, 4096, 5000, 5000]
+    assert eng.kv_bounds(15) == [1024, 2048, 4096, 5000]
+    assert eng.kv_bound(7, 16) == 5000 and eng.kv_bounds(16) == [5000] and eng.kv_bounds(64) == [5000]
