@@ -224,6 +224,8 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch and the prefill")
     ap.add_argument("--workload", default="decode_8b", choices=["decode_8b"] + sorted(SERVE),
                     help="decode_8b: the headline (default); serve_1b, long_3b: whole serving runs through LLM.generate")
+    ap.add_argument("--context-len", type=int, default=PROMPT_LEN,
+                    help="prompt length of the decode measurements (the headline is 2,048; the prefill figure stays at 2,048)")
     ap.add_argument("--timeline", action="store_true",
                     help="also print, on standard error, start and end of every kernel of one decode step in place")
     ap.add_argument("--profile", action="store_true",
@@ -245,10 +247,12 @@ def main():
 
     peaks = load_peaks()
     shape = dict(SHAPE_8B, n_layers=args.layers)
-    cfg = LlamaConfig(architecture="LlamaForCausalLM", rope_scaling=RopeScaling(**ROPE_8B), max_seq_len=CONTEXT, **shape)
+    ctx_len = args.context_len
+    max_len = max(CONTEXT, -(-(ctx_len + args.warmup + args.steps + 64) // 16) * 16)
+    cfg = LlamaConfig(architecture="LlamaForCausalLM", rope_scaling=RopeScaling(**ROPE_8B), max_seq_len=max_len, **shape)
     max_b = 64 if not args.skip_points else args.batch
-    llm = LLM(config=cfg, random_seed=0, precision="bfloat16", max_len=CONTEXT, max_bsz=max(max_b, args.batch),
-              max_num_batched_tokens=args.batch * PROMPT_LEN, page_size=16)   # the e2e batch's prompts go in one step
+    llm = LLM(config=cfg, random_seed=0, precision="bfloat16", max_len=max_len, max_bsz=max(max_b, args.batch),
+              max_num_batched_tokens=args.batch * ctx_len, page_size=16)   # the e2e batch's prompts go in one step
     engine, ops = llm.engine, llm.model.ops
     gen = torch.Generator().manual_seed(1234)
 
@@ -291,7 +295,7 @@ def main():
         if clocks:
             clocks.__enter__()
         handles = [engine.claim() for _ in range(batch)]
-        ps = prompts(batch)
+        ps = prompts(batch, ctx_len)
         for h, p in zip(handles, ps):                       # prefill, one prompt per step
             engine.step([StepEntry(h, p, [])])
         feed = torch.randint(0, cfg.vocab_size, (warmup + steps, batch), generator=gen).tolist()
@@ -315,7 +319,7 @@ def main():
         ms = a.elapsed_time(b) / steps
         for h in handles:
             engine.release(h)
-        mean_ctx = PROMPT_LEN + warmup + steps / 2
+        mean_ctx = ctx_len + warmup + steps / 2
         step_bytes = llm.model.weight_bytes() + batch * mean_ctx * kv_bytes_per_token
         return {"ms": ms, "tok_s": batch / (ms / 1e3), "bytes": step_bytes, "launches": ops.launches - launches0,
                 "clocks": clocks.summary() if clocks else None}
@@ -385,7 +389,7 @@ def main():
     n_new = args.warmup + args.steps
     llm.warmup(range(1, args.batch + 1))                                            # decode graphs, as at server start
     llm.generate(prompt_token_ids=prompts(args.batch, 64), max_new_tokens=4)        # warm the path
-    llm.generate(prompt_token_ids=prompts(args.batch), max_new_tokens=n_new)
+    llm.generate(prompt_token_ids=prompts(args.batch, ctx_len), max_new_tokens=n_new)
     st = llm.last_stats
     e2e_tok_s = st.decode_step_tokens / st.decode_seconds if st.decode_seconds > 0 else None
     h2d = engine._buf.uploaded_bytes                 # the last decode step's one upload (positions, slots, block tables)
@@ -393,14 +397,14 @@ def main():
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch}
 
     out = {
-        "metric": "decode tok/s at batch 8 (Llama-3.1-8B shape, 2,048-token prompts)",
+        "metric": f"decode tok/s at batch {args.batch} (Llama-3.1-8B shape, {ctx_len:,}-token prompts)",
         "value": round(head["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(head["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights N(0, 0.02))",
         "config": {"model": "llama-3.1-8b-shape", "n_layers": args.layers, "n_layers_full": SHAPE_8B["n_layers"],
                    "dim": cfg.dim, "n_heads": cfg.n_heads, "n_kv_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim,
                    "ffn_hidden": cfg.ffn_hidden, "vocab_size": cfg.vocab_size, "global_batch": args.batch,
-                   "seq_len": PROMPT_LEN, "context": CONTEXT, "page_size": 16, "parallelism": "single-gpu",
+                   "seq_len": ctx_len, "context": max_len, "page_size": 16, "parallelism": "single-gpu",
                    "l2": "inputs larger than L2 (16 GB of weights per step)"},
         "e2e": e2e, "gpu_launches": head["launches"], "clocks": head["clocks"],
         "prefill": prefill,
