@@ -32,7 +32,7 @@ def rand(shape, dtype, seed, scale=1.0):
 # ------------------------------------------------------------------------------ elementwise
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("vocab,dim,n", [(37, 24, 5), (1000, 96, 64), (50, 4100, 3)])
+@pytest.mark.parametrize("vocab,dim,n", [(37, 24, 5), (1000, 96, 64), (50, 4100, 3), (300, 4096, 70), (9, 8, 2)])
 def test_embed(ops, dtype, vocab, dim, n):
     table = rand((vocab, dim), dtype, 1)
     ids = torch.randint(0, vocab, (n,), dtype=torch.int32).cuda()

@@ -21,6 +21,26 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
     for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = to_float(src[d]);
 }
 
+// bfloat16 table, dim a multiple of 8, 16-byte aligned rows: eight elements per thread and turn
+__global__ void embed_bf16x8_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                    float* __restrict__ out, int dim, int vocab) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const __nv_bfloat16* src = table + (size_t)id * dim;
+    float* dst = out + (size_t)t * dim;
+    for (int d = threadIdx.x * 8; d < dim; d += blockDim.x * 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + d);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+        const float2 c = __bfloat1622float2(h[2]), e = __bfloat1622float2(h[3]);
+        *reinterpret_cast<float4*>(dst + d) = make_float4(a.x, a.y, b.x, b.y);
+        *reinterpret_cast<float4*>(dst + d + 4) = make_float4(c.x, c.y, e.x, e.y);
+    }
+}
+
 // four contiguous elements as floats
 __device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
@@ -154,6 +174,9 @@ extern "C" int tl_embed(const int* ids, const void* table, int table_dtype, floa
     cudaError_t e;
     if (table_dtype == TL_F32)
         e = tl_launch(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, ids, (const float*)table, out, dim, vocab);
+    else if (table_dtype == TL_BF16 && dim % 8 == 0 && aligned16(table) && aligned16(out))
+        e = tl_launch(embed_bf16x8_kernel, dim3(n_tokens), dim3(dim / 8 >= 256 ? 256 : (dim / 8 + 31) / 32 * 32), 0, s, ids,
+                      (const __nv_bfloat16*)table, out, dim, vocab);
     else if (table_dtype == TL_BF16)
         e = tl_launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, ids, (const __nv_bfloat16*)table, out, dim, vocab);
     else
