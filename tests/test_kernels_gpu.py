@@ -142,7 +142,7 @@ def test_gemm_tcgen05_few_rows(ops, M, N, K):
     assert parts.dim() in (2, 3)
 
 
-@pytest.mark.parametrize("M,hidden,K", [(1, 64, 64), (8, 192, 264), (16, 14336, 128), (17, 448, 1000), (33, 128, 4096), (64, 1024, 520)])
+@pytest.mark.parametrize("M,hidden,K", [(1, 64, 64), (8, 192, 264), (16, 14336, 128), (17, 448, 1000), (33, 128, 4096), (40, 192, 264), (64, 1024, 520)])
 def test_gated_product_is_product_then_swiglu(ops, M, hidden, K):
     """SwiGLU in the epilogue of the gate/up product: the same numbers as product + SwiGLU kernel,
     and both near the float32 formula.  Sizes that are no power of two, one to 64 rows, a K with a
