@@ -123,3 +123,28 @@ def test_cache_pool_as_a_share_of_free_memory(tmp_path):
         LLM(folder, kv_memory_fraction=0.5, kv_memory_gb=1.0, **kw)
     with pytest.raises(ValueError):
         LLM(folder, kv_memory_fraction=1.5, **kw)
+
+
+def test_chat_command_line_in_token_ids(tmp_path, monkeypatch, capsys):
+    """The chat command line on a folder without a tokenizer: lines of token ids in, generated ids out,
+    the history carried from turn to turn, ``!!reset`` starting over, end of input ending the chat."""
+    from torchllms_b200.inference import chat
+    cfg, _, _page = TINY["A"]
+    folder = tiny_folder(tmp_path, "A")
+    lines = iter(["5 17 3", "not ids", "8 9", "!!reset", "5 17 3"])
+
+    def fake_input(prompt=""):
+        try:
+            return next(lines)
+        except StopIteration:
+            raise EOFError
+    monkeypatch.setattr("builtins.input", fake_input)
+    chat.main(["--ckpt_paths", str(folder), "--precision", "float32", "--max_new_tokens", "6",
+               "--max_len", str(cfg["max_position_embeddings"])])
+    said = [l[len("[assistant]: "):] for l in capsys.readouterr().out.splitlines() if l.startswith("[assistant]: ")]
+    assert len(said) == 3
+    plain = PlainModel(folder)
+    first = plain.greedy([5, 17, 3], 6)
+    assert said[0] == " ".join(map(str, first))
+    assert said[1] == " ".join(map(str, plain.greedy([5, 17, 3] + first + [8, 9], 6)))     # the history is carried
+    assert said[2] == said[0]                                                               # and dropped by !!reset

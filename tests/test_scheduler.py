@@ -216,3 +216,14 @@ def test_chat_template_renders_llama3_turns():
     assert t.stop_token_ids == (128009,)
     with pytest.raises(ValueError):
         t.render([{"role": "wizard", "content": "x"}])
+
+
+def test_chat_command_line_takes_the_references_options():
+    """torchllms/inference/chat.py:15-46: the option names and defaults of the reference's chat."""
+    from torchllms_b200.inference.chat import parse_args
+    a = parse_args(["--ckpt_paths", "m1", "m2", "--template_config", "llama3_instruct", "--model_kwargs", '{"max_seq_len": 64}'])
+    assert [str(p) for p in a.ckpt_paths] == ["m1", "m2"] and a.template_config == "llama3_instruct"
+    assert a.max_new_tokens == 200 and a.temperature == 0.0 and a.device == "cuda" and a.precision is None
+    assert a.model_kwargs == {"max_seq_len": 64}
+    with pytest.raises(SystemExit):
+        parse_args([])                      # a model folder is required
