@@ -361,6 +361,25 @@ def test_attention_finds_one_far_key_among_hundreds(ops, dtype, impl, key_pos):
     torch.testing.assert_close(got, want, atol=t, rtol=t)
 
 
+@pytest.mark.parametrize("dtype,impl", [(torch.float32, "general"), (torch.bfloat16, "general"), (torch.bfloat16, "decode")])
+@pytest.mark.parametrize("key_pos", [5, 12345, 32767])
+def test_decoding_finds_one_key_among_tens_of_thousands(ops, dtype, impl, key_pos):
+    """Decoding at a context of 32,768 in the 8-billion-parameter head layout: block tables of
+    thousands of pages, the keys of a request split over as many CTAs as the plan gives at that
+    length, and one key, early, in the middle or the very last, that takes nearly all the weight."""
+    L, H, KV, hd, P = 32768, 32, 8, 128, 16
+    a = build_paged([L, 20000], [1, 1], H, KV, hd, P, dtype, seed=key_pos, peak=(0, key_pos, 4.0))
+    got = ops.paged_attention(**a, scale=hd ** -0.5, window=None, impl=impl).float()
+    ops.check_status()
+    page, slot = a["block_table"][0, key_pos // P].item(), key_pos % P
+    for h in range(H):
+        v = a["v_pages"][page, h // (H // KV), slot].float()
+        assert (got[0, h] - v).abs().max().item() < 0.05, (h, (got[0, h] - v).abs().max().item())
+    want = TWIN.paged_attention(**a, scale=hd ** -0.5, window=None).float()
+    t = tol(dtype, 2e-5, 2e-2)
+    torch.testing.assert_close(got, want, atol=t, rtol=t)
+
+
 @pytest.mark.parametrize("dtype,impl", IMPLS)
 @pytest.mark.parametrize("key_pos", [0, 127, 128, 300, 511, 640])
 def test_a_long_portion_finds_one_far_key(ops, dtype, impl, key_pos):
