@@ -41,7 +41,18 @@ TINY_C = {
     "vocab_size": 777, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "rope_scaling": None,
     "tie_word_embeddings": False, "max_position_embeddings": 1024,
 }
-TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16)}   # name -> (config, seed, page size)
+# A fourth one of awkward sizes: a width that is no multiple of four (the kernels' scalar forms, and
+# products whose inner size the tensor-core kernel refuses), heads of 48 in groups of three, a
+# feed-forward width and a vocabulary that are multiples of nothing, other constants everywhere.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 102, "num_hidden_layers": 2,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 48, "intermediate_size": 166,
+    "vocab_size": 1003, "rms_norm_eps": 1e-4, "rope_theta": 1234.5,
+    "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 2.0, "high_freq_factor": 8.0,
+                     "original_max_position_embeddings": 32},
+    "tie_word_embeddings": False, "max_position_embeddings": 160,
+}
+TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16), "D": (TINY_D, 3, 4)}   # name -> (config, seed, page size)
 
 
 def tensor_table(cfg: dict) -> List[tuple]:

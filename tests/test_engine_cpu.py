@@ -13,7 +13,8 @@ from plain_llama import PlainModel
 from torch_ops import TorchOps
 from torchllms_b200.engine.replay import Replayer
 
-LENGTHS = {"A": [1, 7, 33, 64, 97, 50, 120, 20, 3, 70], "B": [2, 5, 17, 40, 100, 65, 129, 30, 90]}
+LENGTHS = {"A": [1, 7, 33, 64, 97, 50, 120, 20, 3, 70], "B": [2, 5, 17, 40, 100, 65, 129, 30, 90],
+           "D": [3, 50, 131, 64, 17, 90, 2, 120, 77, 101]}
 # The plain implementation itself sits about 1.3e-5 from a float64 evaluation of these
 # (deliberately peaked) models, so float32 paths that sum in another order differ by a few 1e-5.
 ATOL = 1e-4
@@ -22,7 +23,7 @@ ATOL = 1e-4
 @pytest.fixture(scope="module")
 def setups(tmp_path_factory):
     out = {}
-    for name in ("A", "B"):                      # the third configuration is for GPU kernels
+    for name in ("A", "B", "D"):                 # the third configuration is for GPU kernels
         cfg, seed, page = TINY[name]
         folder = tiny_folder(tmp_path_factory.mktemp(name), name)
         rng = random.Random(seed)
@@ -32,7 +33,7 @@ def setups(tmp_path_factory):
     return out
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 @pytest.mark.parametrize("mode", ["whole", "tail_one_by_one", "portions", "mixed"])
 def test_cuts_agree_with_plain(setups, name, mode):
     folder, page, reqs, ref = setups[name]

@@ -32,7 +32,7 @@ def rand(shape, dtype, seed, scale=1.0):
 # ------------------------------------------------------------------------------ elementwise
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("vocab,dim,n", [(37, 24, 5), (1000, 96, 64), (50, 4100, 3), (300, 4096, 70), (9, 8, 2)])
+@pytest.mark.parametrize("vocab,dim,n", [(37, 24, 5), (1000, 96, 64), (50, 4100, 3), (300, 4096, 70), (9, 8, 2), (1003, 102, 9), (11, 7, 3)])
 def test_embed(ops, dtype, vocab, dim, n):
     table = rand((vocab, dim), dtype, 1)
     ids = torch.randint(0, vocab, (n,), dtype=torch.int32).cuda()
@@ -43,7 +43,7 @@ def test_embed(ops, dtype, vocab, dim, n):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n,dim", [(1, 16), (7, 96), (33, 4096), (3, 5000), (2, 20000)])
+@pytest.mark.parametrize("n,dim", [(1, 16), (7, 96), (33, 4096), (3, 5000), (2, 20000), (5, 102), (4, 7)])
 @pytest.mark.parametrize("eps", [1e-5, 1e-2])
 def test_rmsnorm_with_and_without_delta(ops, dtype, n, dim, eps):
     h = rand((n, dim), torch.float32, 2, 3.0)
@@ -73,7 +73,7 @@ def test_rmsnorm_rows_leaves_stream_alone(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n,hidden", [(1, 8), (5, 192), (64, 1000), (3, 14336)])
+@pytest.mark.parametrize("n,hidden", [(1, 8), (5, 192), (64, 1000), (3, 14336), (7, 166), (3, 5)])
 def test_swiglu(ops, dtype, n, hidden):
     x = rand((n, 2 * hidden), dtype, 8, 3.0)
     got, want = ops.swiglu(x), TWIN.swiglu(x)
@@ -103,7 +103,7 @@ def test_gemm_simt_bfloat16_operands(ops, M, N, K, out_dtype):
     torch.testing.assert_close(got.float(), want.float(), atol=tol(out_dtype, 1e-4, 5e-2), rtol=tol(out_dtype, 1e-5, 1e-2))
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 1000, 96), (5, 128, 64), (300, 200, 264)])
+@pytest.mark.parametrize("M,N,K", [(1, 1000, 96), (5, 128, 64), (300, 200, 264), (5, 166, 102), (70, 1003, 102), (3, 9, 7)])
 def test_linear_bfloat16(ops, M, N, K):
     x, w = rand((M, K), torch.bfloat16, 13), rand((N, K), torch.bfloat16, 14)
     for out_dtype in DTYPES:

@@ -15,7 +15,7 @@ from plain_llama import PlainModel, to_bfloat16_and_back
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [1, 7, 33, 64, 97, 120, 50], "B": [2, 5, 17, 40, 100, 200, 65, 129],
-           "C": [300, 97, 513, 130, 700, 64, 260]}
+           "C": [300, 97, 513, 130, 700, 64, 260], "D": [3, 50, 131, 64, 17, 90, 2, 158]}
 # configuration C is there for long portions (the tcgen05 prefill kernel takes 96 tokens and more,
 # 256 to a CTA): its cuttings include them
 MODE_ARGS = {("C", "portions"): dict(sizes=(2, 130, 5, 257, 96, 31, 300, 3, 128, 17)),
@@ -84,7 +84,7 @@ def compare(got, places, ref, tol):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("mode", ["whole", "tail_one_by_one", "portions", "mixed"])
 def test_replay(setups, tmp_path, name, dtype, mode):
     folder, reqs, ref, tol = setups[(name, dtype)]

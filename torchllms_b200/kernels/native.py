@@ -250,7 +250,7 @@ class NativeOps:
                 self._mm_out_dtype = True
             except (TypeError, RuntimeError):
                 self._mm_out_dtype = False
-        if self._mm_out_dtype:
+        if self._mm_out_dtype and K % 8 == 0:              # (rows the library can address 16 bytes at a time)
             return torch.mm(x, w.t(), out_dtype=torch.float32)
         return self.gemm_simt(x, w, torch.float32)
 
