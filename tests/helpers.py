@@ -1,4 +1,5 @@
-"""Shared fixtures of the tests: two tiny configurations that differ in every size and option,
+"""Shared fixtures of the tests: tiny configurations that differ in every size and option (two for
+everything, a third for the kernels that want heads of 64, a fourth of awkward sizes),
 model folders with random weights, and traces for the replay program."""
 
 from __future__ import annotations
