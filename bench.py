@@ -182,13 +182,13 @@ def serving_workload(args):
     rng = random.Random(0)
     gen = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, cfg.vocab_size, (rng.randint(lo, hi),), generator=gen).tolist() for _ in range(w["requests"])]
-    llm.generate(prompt_token_ids=[p[:64] for p in prompts[:4]], max_new_tokens=4)      # warm the path
+    llm.generate(prompt_token_ids=[p[:64] for p in prompts[:4]], max_new_tokens=4, disable_tqdm=True)      # warm the path
     ops = llm.model.ops
     launches0 = ops.launches
     with ClockSampler() as clocks:
         torch.cuda.synchronize()
         t0 = time.time()
-        out = llm.generate(prompt_token_ids=prompts, max_new_tokens=w["new_tokens"], temperature=w["temperature"], seed=1)
+        out = llm.generate(prompt_token_ids=prompts, max_new_tokens=w["new_tokens"], temperature=w["temperature"], seed=1, disable_tqdm=True)
         torch.cuda.synchronize()
         t1 = time.time()
         clocks.mark(t0, t1)
@@ -388,8 +388,8 @@ def main():
     # ------------------------------------------------------------------ end to end through LLM.generate
     n_new = args.warmup + args.steps
     llm.warmup(range(1, args.batch + 1))                                            # decode graphs, as at server start
-    llm.generate(prompt_token_ids=prompts(args.batch, 64), max_new_tokens=4)        # warm the path
-    llm.generate(prompt_token_ids=prompts(args.batch, ctx_len), max_new_tokens=n_new)
+    llm.generate(prompt_token_ids=prompts(args.batch, 64), max_new_tokens=4, disable_tqdm=True)        # warm the path
+    llm.generate(prompt_token_ids=prompts(args.batch, ctx_len), max_new_tokens=n_new, disable_tqdm=True)
     st = llm.last_stats
     e2e_tok_s = st.decode_step_tokens / st.decode_seconds if st.decode_seconds > 0 else None
     h2d = engine._buf.uploaded_bytes                 # the last decode step's one upload (positions, slots, block tables)

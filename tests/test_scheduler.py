@@ -227,3 +227,17 @@ def test_chat_command_line_takes_the_references_options():
     assert a.model_kwargs == {"max_seq_len": 64}
     with pytest.raises(SystemExit):
         parse_args([])                      # a model folder is required
+
+
+def test_progress_bar_counts_finished_requests_unless_disabled(folder, capsys):
+    """``disable_tqdm`` as in the reference (torchllms/inference/llm.py:1081, :1126-1130): a bar on
+    standard error unless disabled; here it counts requests, those without a budget included."""
+    llm = make_llm(folder)
+    capsys.readouterr()
+    shown = llm.generate(prompt_token_ids=PROMPTS + [[4] * 128], max_new_tokens=3)      # the last one has no room
+    err = capsys.readouterr().err
+    n = len(PROMPTS) + 1
+    assert f"{n}/{n}" in err and "generate" in err
+    quiet = llm.generate(prompt_token_ids=PROMPTS + [[4] * 128], max_new_tokens=3, disable_tqdm=True)
+    assert capsys.readouterr().err == ""
+    assert [r.token_ids for r in shown] == [r.token_ids for r in quiet]

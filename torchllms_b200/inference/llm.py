@@ -168,14 +168,15 @@ class LLM:
         temperature: float = 0.0,
         max_new_tokens: Optional[int] = None,
         batch_size: int = 0,
-        disable_tqdm: bool = True,
+        disable_tqdm: bool = False,
         *,
         prompt_token_ids: Optional[List[List[int]]] = None,
         top_k: Optional[int] = None,
         seed: Optional[int] = None,
     ) -> List[GenerationResult]:
         """One result per input, in input order.  ``temperature`` 0 is greedy.  ``batch_size``
-        bounds how many requests run at once (0: ``max_bsz``)."""
+        bounds how many requests run at once (0: ``max_bsz``).  Unless ``disable_tqdm``, a progress
+        bar on standard error counts the finished requests (torchllms/inference/llm.py:1126-1130; there it counts static batches)."""
         given = [x is not None for x in (prompts, conversations, prompt_token_ids)]
         if sum(given) != 1:
             raise ValueError("give exactly one of prompts, conversations and prompt_token_ids")
@@ -197,9 +198,25 @@ class LLM:
                               max_num_seqs=min(batch_size, self.max_bsz) if batch_size else self.max_bsz,
                               max_num_batched_tokens=self.max_num_batched_tokens,
                               prefill_chunk=self.prefill_chunk, eos_ids=self.eos_set, look_ahead=self.look_ahead)
+        bar = None
+        if not disable_tqdm and len(requests) > 1:
+            try:
+                from tqdm import tqdm
+                bar = tqdm(total=len(requests), desc="generate", unit="req")
+            except ImportError:
+                bar = None
         try:
-            scheduler.run(requests)
+            for r in requests:
+                scheduler.add(r)
+            if bar is not None:
+                bar.update(sum(1 for r in requests if r.finished))      # nothing to generate, or refused
+            while scheduler.has_work():
+                done = scheduler.step()
+                if bar is not None and done:
+                    bar.update(len(done))
         finally:
+            if bar is not None:
+                bar.close()
             for r in requests:                      # whatever happened, give the pages back
                 if r.handle is not None:
                     self.engine.release(r.handle)
