@@ -241,3 +241,15 @@ def test_progress_bar_counts_finished_requests_unless_disabled(folder, capsys):
     quiet = llm.generate(prompt_token_ids=PROMPTS + [[4] * 128], max_new_tokens=3, disable_tqdm=True)
     assert capsys.readouterr().err == ""
     assert [r.token_ids for r in shown] == [r.token_ids for r in quiet]
+
+
+def test_entry_point_takes_the_references_arguments_in_their_order(folder):
+    """torchllms/inference/llm.py:95-109: positional use must mean the same here."""
+    import inspect
+    names = list(inspect.signature(LLM.__init__).parameters)[1:13]
+    assert names == ["ckpt_paths", "template_config", "eos_ids", "max_len", "max_bsz", "device", "precision",
+                     "model_kwargs", "batched", "prefix_cache", "page_size", "kv_memory_gb"]
+    names = list(inspect.signature(LLM.generate).parameters)[1:7]
+    assert names == ["prompts", "conversations", "temperature", "max_new_tokens", "batch_size", "disable_tqdm"]
+    with pytest.raises(ValueError, match="prefix cache"):
+        make_llm(folder, prefix_cache=object())

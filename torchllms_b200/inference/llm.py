@@ -2,7 +2,7 @@
 
 Reference: ``LLM`` (torchllms/inference/llm.py:80-1152).  Argument names and meanings follow
 its ``__init__`` (:95-109: ``ckpt_paths, template_config, eos_ids, max_len, max_bsz, device,
-precision, model_kwargs, page_size, kv_memory_gb``) and ``generate`` (:693-700, :1074-1083:
+precision, model_kwargs, batched, prefix_cache, page_size, kv_memory_gb``) and ``generate`` (:693-700, :1074-1083:
 ``prompts`` or ``conversations``, ``temperature``, ``max_new_tokens``, ``batch_size``,
 ``disable_tqdm``), and results are its ``GenerationResult`` (:63-77).  Differences: every call
 runs through the continuous-batching scheduler (the reference's ``batched`` switch chose between
@@ -52,6 +52,7 @@ class LLM:
         precision: Optional[str] = "bfloat16",
         model_kwargs: Optional[Dict[str, Any]] = None,
         batched: bool = True,
+        prefix_cache: Any = None,
         page_size: int = 16,
         kv_memory_gb: Optional[float] = None,
         kv_memory_fraction: Optional[float] = None,
@@ -71,6 +72,9 @@ class LLM:
         that may run at once; the cache holds ``max_bsz * max_len`` tokens unless ``kv_memory_fraction``
         (a share of the device memory that is free once the weights are loaded) or ``kv_memory_gb``
         gives its size in GiB (torchllms/models/networks.py:872-884)."""
+        if prefix_cache is not None:
+            # the reference's argument at its place in the list; this engine keeps no cache of prefixes
+            raise ValueError("prefix_cache: this engine has no prefix cache; leave it None")
         ops = ops or get_ops()
         precision = precision or "bfloat16"
         self.dtype = parse_dtype(precision)
