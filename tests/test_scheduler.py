@@ -253,3 +253,60 @@ def test_entry_point_takes_the_references_arguments_in_their_order(folder):
     assert names == ["prompts", "conversations", "temperature", "max_new_tokens", "batch_size", "disable_tqdm"]
     with pytest.raises(ValueError, match="prefix cache"):
         make_llm(folder, prefix_cache=object())
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_arrivals_pools_and_budgets_change_no_token(folder, seed):
+    """Random prompts, budgets, stop ids, pool sizes, token budgets, portion sizes, numbers of
+    running requests and arrival times, with and without launching ahead: every request gets the
+    tokens it gets when it runs alone in a roomy engine, the cache is sound after every step, and
+    nothing is left behind.  A request that cannot fit the pool at all gets an error, not tokens."""
+    import random
+    rng = random.Random(1000 + seed)
+    n = rng.randint(3, 7)
+    prompts = [[rng.randrange(512) for _ in range(rng.choice([1, 2, 5, 17, 33, 60]))] for _ in range(n)]
+    budgets = [rng.choice([0, 1, 2, 7, 12]) for _ in range(n)]
+    sampling = SamplingParams(rng.choice([0.0, 0.8]), rng.choice([None, 20]), rng.randrange(100))
+    alone = []
+    for i, (p, b) in enumerate(zip(prompts, budgets)):
+        s = make_scheduler(folder, pool_tokens=512)
+        r = Request(i, list(p), b, sampling)
+        s.run([r])
+        alone.append(list(r.generated))
+    # a stop id that some request meets on its way
+    met = [t for g in alone for t in g[:-1]]
+    eos = (rng.choice(met),) if met and rng.random() < 0.7 else ()
+    def cut(g):
+        for k, t in enumerate(g):
+            if t in eos:
+                return g[:k + 1]
+        return g
+    want = [cut(g) for g in alone]
+    pool = rng.choice([48, 80, 112, 512])
+    s = make_scheduler(folder, pool_tokens=pool, eos=eos, look_ahead=rng.random() < 0.5,
+                       max_num_seqs=rng.randint(1, 4), max_num_batched_tokens=rng.choice([4, 9, 48]),
+                       prefill_chunk=rng.choice([2, 5, 24]))
+    reqs = [Request(i, list(p), b, sampling) for i, (p, b) in enumerate(zip(prompts, budgets))]
+    late = list(reqs)
+    rng.shuffle(late)
+    first, late = late[:2], late[2:]
+    for r in sorted(first, key=lambda r: r.index):
+        s.add(r)
+    steps = 0
+    while s.has_work() or late:
+        if late and (not s.has_work() or rng.random() < 0.3):
+            s.add(late.pop())
+        s.step()
+        s.engine.cache.check_invariants()
+        steps += 1
+        assert steps < 2000, "the scheduler does not come to an end"
+    for r, w, p, b in zip(reqs, want, prompts, budgets):
+        assert r.finished
+        need = len(p) + b - 1
+        if b > 0 and -(-need // 16) * 16 > pool:
+            assert r.error and r.generated == []
+        else:
+            assert r.error is None and r.generated == w, (r.index, r.generated, w)
+            assert r.stop_reason == (w[-1] if w and w[-1] in eos else None)
+    assert s.engine.cache.n_live() == 0
+    assert s.engine.cache.free_pages() == s.engine.cache.groups[0].allocator.n_pages
