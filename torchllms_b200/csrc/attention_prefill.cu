@@ -282,7 +282,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
     const int qpos_base = kl - ql;
     // Keys the CTA walks: from the window's start of its first row to its last row's own position, in
     // tiles of 128 counted from k_start.  Each query tile takes part in the key tiles it can see.
-    const int k_start = (p.window > 0 ? max(0, qpos_base + tok0 - p.window + 1) : 0) & ~(BN - 1);
+    const int k_lo = p.window > 0 ? max(0, qpos_base + tok0 - p.window + 1) : 0;      // the first key anybody here sees
+    const int k_start = k_lo & ~(BN - 1);
     TileRange range[QT];
     int n_tiles = 0;
 #pragma unroll
@@ -330,9 +331,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
                     for (int c = lane; c < n_boxes; c += 32) {
                         const int kpos = k0 + c * p.box_rows;
                         // boxes past the last key start outside the tensor: the copy writes the zero fill,
-                        // so that what is multiplied by probability 0 there is finite
+                        // so that what is multiplied by probability 0 there is finite.  So do boxes that
+                        // end before the first key of a window: their pages may have been given back
+                        // (the table then holds no page for them), and every score there is masked.
                         int row = p.total_rows;
-                        if (kpos < k_hi) {
+                        if (kpos < k_hi && kpos + p.box_rows > k_lo) {
                             const int page = table[kpos >> p.page_shift];
                             row = (page * p.n_kv_heads + kvh) * p.page_size + (kpos & (p.page_size - 1));
                         }
