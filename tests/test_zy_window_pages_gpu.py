@@ -3,7 +3,7 @@ may look them up.  Here the block tables hold no page (-1) for every block that 
 the first key the step can see, and every page that no table names is filled with NaN, so that a
 kernel that fetched one (even to multiply it by a probability of zero) would show it.
 
-(The file sorts late on purpose: it was added after the other kernel tests had run on a GPU.)"""
+(The file sorts late, so that a run that stops at the first failure has seen the older tests.)"""
 
 import pytest
 import torch
