@@ -52,7 +52,7 @@ def load_peaks():
             return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
                     "bf16_tflops_sustained": float(raw.get("bf16_tflops_sustained", raw["bf16_tflops"])),
                     "source": "measured"}
-        except (ValueError, KeyError):
+        except (ValueError, KeyError, TypeError):
             pass
     return dict(FALLBACK_PEAKS)
 
