@@ -169,7 +169,7 @@ def serving_workload(args):
     import random
 
     import torch
-    from torchllms_b200.config import LlamaConfig, RopeScaling
+    from torchllms_b200.models.llama_config import LlamaConfig, RopeScaling
     from torchllms_b200.inference import LLM
 
     w = SERVE[args.workload]
@@ -241,7 +241,7 @@ def main():
     args.warmup = max(args.warmup, 3)
 
     import torch
-    from torchllms_b200.config import LlamaConfig, RopeScaling
+    from torchllms_b200.models.llama_config import LlamaConfig, RopeScaling
     from torchllms_b200.engine.step import StepEntry
     from torchllms_b200.inference import LLM
 

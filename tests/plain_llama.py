@@ -126,9 +126,11 @@ def block(x, w: Dict[str, torch.Tensor], prefix: str, cfg, cos, sin, stored=_sam
     return h + stored(act @ g("feed_forward.w2.weight").T)
 
 
-def forward_logits(w: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int], stored=_same) -> torch.Tensor:
+def forward_logits(w: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int], stored=_same,
+                   rows: Optional[Sequence[int]] = None) -> torch.Tensor:
     """torchllms/models/networks.py:1017-1047: embed, blocks, final norm, head (tied :806-809).
-    Returns [len(tokens), vocab] logits for the whole sequence.
+    Returns [len(tokens), vocab] logits for the whole sequence (with ``rows``: the head is applied
+    to those positions only, :1030-1045 keeps rows the same way).
 
     With ``stored=to_bfloat16_and_back`` (and bfloat16-valued weights) this is the arithmetic of
     the engine's bfloat16 mode: float32 residual stream, norms, rotation, softmax and sums, with
@@ -139,6 +141,8 @@ def forward_logits(w: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int],
     cos, sin = rope_angles(inv, torch.arange(len(ids)))
     for i in range(cfg["n_layers"]):
         x = block(x, w, f"layers.{i}", cfg, cos, sin, stored)
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long)]
     x = stored(rms_norm(x, w["norm.weight"], cfg["eps"]))
     head = w["tok_embeddings.weight"] if cfg["tie"] else w["output.weight"]
     return x @ head.T
@@ -200,8 +204,8 @@ class PlainModel:
         self.weights = read_weights(folder, self.cfg, dtype)
 
     @torch.no_grad()
-    def logits(self, tokens: Sequence[int], stored=_same) -> torch.Tensor:
-        return forward_logits(self.weights, self.cfg, tokens, stored).float()
+    def logits(self, tokens: Sequence[int], stored=_same, rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+        return forward_logits(self.weights, self.cfg, tokens, stored, rows).float()
 
     @torch.no_grad()
     def greedy(self, prompt: Sequence[int], n_new: int) -> List[int]:

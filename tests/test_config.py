@@ -5,7 +5,8 @@ import json
 import pytest
 
 from helpers import TINY_A, TINY_B
-from torchllms_b200.config import ConfigError, LlamaConfig, RopeScaling, get_architecture, load_config
+from torchllms_b200.config import ConfigError, get_architecture, load_config
+from torchllms_b200.models.llama_config import LlamaConfig, RopeScaling
 
 
 def write(tmp_path, raw, name="config.json"):
@@ -90,13 +91,19 @@ def test_overrides_like_model_kwargs(tmp_path):
         cfg.with_overrides({"n_experts": 8})
 
 
+def test_another_activation_is_refused():
+    assert LlamaConfig.from_hf(dict(TINY_A, hidden_act="silu")) == LlamaConfig.from_hf(TINY_A)
+    with pytest.raises(ConfigError, match="hidden_act"):
+        LlamaConfig.from_hf(dict(TINY_A, hidden_act="gelu"))
+
+
 def test_spec_is_data_and_takes_its_numbers_from_the_config():
     arch = get_architecture("LlamaForCausalLM")
     cfg = LlamaConfig.from_hf(TINY_B)
     spec = arch.build_spec(cfg)
     assert len(spec.layers) == 3 and [r.layer for r in spec.run_order] == [0, 1, 2]
-    mixer = spec.layers[0].mixer
+    mixer = spec.layers[0].block["mixer"]
     assert (mixer.kind, mixer["n_heads"], mixer["n_kv_heads"], mixer["head_dim"]) == ("attention", 3, 1, 32)
     assert mixer["scale"] == 32 ** -0.5 and mixer["position"]["theta"] == 500000.0
-    assert spec.layers[1].feed_forward["hidden"] == 256 and spec.layers[2].ffn_norm["eps"] == 1e-6
+    assert spec.layers[1].block["feed_forward"]["hidden"] == 256 and spec.layers[2].block["ffn_norm"]["eps"] == 1e-6
     assert spec.tie_head

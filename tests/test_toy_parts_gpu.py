@@ -56,8 +56,10 @@ def toy_spec(dim, H, KV, hd, hidden, vocab):
     mean = part("toy_running_mean", dim=dim)
     ffn = part("swiglu", dim=dim, hidden=hidden)
     norm = part("rmsnorm", dim=dim, eps=1e-5)
-    blk = part("prenorm", mixer_prefix="mixer", ffn_prefix="ffn", mixer_norm_prefix="norm1", ffn_norm_prefix="norm2")
-    layers = (LayerSpec("blocks.0", blk, attn, ffn, norm, norm), LayerSpec("blocks.1", blk, mean, ffn, norm, norm))
+    def blk(mixer):
+        return part("prenorm", mixer=mixer, feed_forward=ffn, mixer_norm=norm, ffn_norm=norm,
+                    mixer_prefix="mixer", ffn_prefix="ffn", mixer_norm_prefix="norm1", ffn_norm_prefix="norm2")
+    layers = (LayerSpec("blocks.0", blk(attn)), LayerSpec("blocks.1", blk(mean)))
     # attention, running mean, the attention layer again with a cache of its own, and once more
     # reading the first run's cache
     order = (RunEntry(0), RunEntry(1), RunEntry(0), RunEntry(0, cache_of=0), RunEntry(1))
@@ -227,7 +229,9 @@ def test_toy_routed_feed_forward_and_other_position_encodings():
     try:
         dim, H, KV, hd, vocab, E = 64, 4, 2, 16, 97, 3
         norm = part("rmsnorm", dim=dim, eps=1e-5)
-        blk = part("prenorm", mixer_prefix="mixer", ffn_prefix="ffn", mixer_norm_prefix="norm1", ffn_norm_prefix="norm2")
+        def blk(mixer, feed_forward):
+            return part("prenorm", mixer=mixer, feed_forward=feed_forward, mixer_norm=norm, ffn_norm=norm,
+                        mixer_prefix="mixer", ffn_prefix="ffn", mixer_norm_prefix="norm1", ffn_norm_prefix="norm2")
         attn_learned = part("attention", dim=dim, n_heads=H, n_kv_heads=KV, head_dim=hd, scale=hd ** -0.5, window=None,
                             position=part("toy_learned_offsets", head_dim=hd, max_positions=128))
         attn_half = part("attention", dim=dim, n_heads=H, n_kv_heads=KV, head_dim=hd, scale=hd ** -0.5, window=None,
@@ -235,8 +239,7 @@ def test_toy_routed_feed_forward_and_other_position_encodings():
         routed = part("toy_routed", dim=dim, hidden=40, n_experts=E)
         dense = part("swiglu", dim=dim, hidden=72)
         spec = ModelSpec(dim=dim, vocab_size=vocab, max_positions=128, embedding_tensor="embed.weight",
-                         layers=(LayerSpec("l0", blk, attn_learned, routed, norm, norm),
-                                 LayerSpec("l1", blk, attn_half, dense, norm, norm)),
+                         layers=(LayerSpec("l0", blk(attn_learned, routed)), LayerSpec("l1", blk(attn_half, dense))),
                          run_order=(RunEntry(0), RunEntry(1)), final_norm=norm, final_norm_prefix="final_norm",
                          head_tensor="head.weight")
         model = Model(spec, dtype=torch.float32, device="cuda", ops=get_ops())

@@ -8,7 +8,7 @@ import torch
 from helpers import TINY, TINY_A, TINY_B, make_tensors, write_model_folder
 from plain_llama import PlainModel
 from torch_ops import TorchOps
-from torchllms_b200.config import LlamaConfig
+from torchllms_b200.models.llama_config import LlamaConfig
 from torchllms_b200.engine.loading import load_model
 from torchllms_b200.models.llama import interleave_rotary_rows, split_rotary_rows
 from torchllms_b200.weights.loader import WeightError

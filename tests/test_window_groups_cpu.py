@@ -23,9 +23,10 @@ def spec():
     near = part("attention", dim=DIM, n_heads=H, n_kv_heads=KV, head_dim=HD, scale=HD ** -0.5, window=WINDOW, position=rope)
     ffn = part("swiglu", dim=DIM, hidden=HIDDEN)
     norm = part("rmsnorm", dim=DIM, eps=1e-5)
-    blk = part("prenorm", mixer_prefix="mixer", ffn_prefix="ffn", mixer_norm_prefix="norm1", ffn_norm_prefix="norm2")
-    layers = (LayerSpec("blocks.0", blk, full, ffn, norm, norm), LayerSpec("blocks.1", blk, near, ffn, norm, norm),
-              LayerSpec("blocks.2", blk, near, ffn, norm, norm))
+    def blk(mixer):
+        return part("prenorm", mixer=mixer, feed_forward=ffn, mixer_norm=norm, ffn_norm=norm,
+                    mixer_prefix="mixer", ffn_prefix="ffn", mixer_norm_prefix="norm1", ffn_norm_prefix="norm2")
+    layers = (LayerSpec("blocks.0", blk(full)), LayerSpec("blocks.1", blk(near)), LayerSpec("blocks.2", blk(near)))
     return ModelSpec(dim=DIM, vocab_size=VOCAB, max_positions=256, embedding_tensor="embed.weight", layers=layers,
                      run_order=(RunEntry(0), RunEntry(1), RunEntry(2)), final_norm=norm, final_norm_prefix="final_norm",
                      head_tensor="head.weight")
@@ -48,12 +49,51 @@ def plain_forward(w, tokens):
     return plain_llama.rms_norm(x, w["final_norm.weight"], 1e-5) @ w["head.weight"].T
 
 
-def test_full_and_windowed_layers_keep_pages_of_their_own():
+def loaded_model():
     model = Model(spec(), dtype=torch.float32, device="cpu", ops=TorchOps())
     g = torch.Generator().manual_seed(5)
     w = {name: (1 + 0.1 * torch.randn(e.shape, generator=g) if "norm" in name else torch.randn(e.shape, generator=g) * 0.3)
          for name, e in model.expected_tensors().items()}
     model.load(w)
+    return model, w
+
+
+def test_the_scheduler_admits_a_request_longer_than_the_window_groups_pool():
+    """The window group has far fewer pages than a long request has tokens; it gives them back as
+    the request grows, so the scheduler must take the request (and only refuse what the group that
+    keeps every key cannot hold)."""
+    from torchllms_b200.engine.scheduler import Request, Scheduler
+    from torchllms_b200.sampling.sampler import Sampler
+    model, w = loaded_model()
+    engine = Engine(model, page_size=PAGE, pool_tokens=400, max_num_seqs=2, max_len=256, max_step_tokens=16)
+    kinds = {g.need.kind: g for g in engine.cache.groups}
+    window_tokens = kinds["window"].allocator.n_pages * PAGE
+    rng = random.Random(3)
+    prompts = [[rng.randrange(VOCAB) for _ in range(n)] for n in (150, 40)]
+    assert window_tokens < 150 + 6                        # the old bound (smallest pool of any group) refused this
+    sched = Scheduler(engine, Sampler(TorchOps(), "cpu"), max_num_batched_tokens=16, prefill_chunk=12)
+    reqs = [Request(index=i, prompt=p, budget=6) for i, p in enumerate(prompts)]
+    sched.run(reqs)
+    for r, p in zip(reqs, prompts):
+        assert r.error is None and len(r.generated) == 6
+        seq = list(p)
+        for tok in r.generated:                            # greedy against the plain forward
+            assert tok == int(torch.argmax(plain_forward(w, seq)[-1]))
+            seq.append(tok)
+    engine.cache.check_invariants()
+    assert engine.cache.n_live() == 0
+    too_long = Request(index=2, prompt=[1] * 250, budget=10)     # 259 cached tokens: beyond max_len
+    sched.add(too_long)
+    assert too_long.finished and "at most 256" in too_long.error
+    small = Engine(model, page_size=PAGE, pool_tokens=100, max_num_seqs=2, max_len=256, max_step_tokens=16)
+    sched = Scheduler(small, Sampler(TorchOps(), "cpu"), max_num_batched_tokens=16, prefill_chunk=12)
+    refused = Request(index=0, prompt=[1] * 120, budget=4)       # the group that keeps every key holds 100
+    sched.add(refused)
+    assert refused.finished and "at most 100" in refused.error
+
+
+def test_full_and_windowed_layers_keep_pages_of_their_own():
+    model, w = loaded_model()
     # The full group gets the pool it is asked for; the windowed group is sized by the manager for a
     # window and a step's tokens per request, far fewer pages than the requests' tokens need in all.
     engine = Engine(model, page_size=PAGE, pool_tokens=352, max_num_seqs=3, max_len=256, max_step_tokens=64)

@@ -6,14 +6,17 @@ device-wide synchronisation an allocation implies, a plug-in working inside anot
 stream.  For them ``tl_paged_attention_static_scratch`` keeps the split-KV partial results in an
 8 MiB array that is part of the library itself.  This test calls it the way such a user would,
 through the exported C symbol with raw device pointers, twice in a row on different inputs (the
-array is shared and keeps the previous call's contents), and compares with the ordinary entry
-point, which is given a workspace.  It sits last in the collection order on purpose.
+array is shared and keeps the previous call's contents), and compares with the plain PyTorch twin
+of the attention kernels and with the ordinary entry point, which is given a workspace.  It sits
+last in the collection order on purpose.
 """
 
 import ctypes
 
 import pytest
 import torch
+
+from torch_ops import TorchOps
 
 pytestmark = pytest.mark.gpu
 
@@ -68,9 +71,11 @@ def test_static_scratch_entry_point_matches_the_ordinary_one_twice_in_a_row(dtyp
         out = torch.full_like(a["q"], float("nan"))
         rc = _call_static(lib, a, out, hd ** -0.5, code)
         assert rc == 0, lib.tl_static_scratch_strerror(rc).decode()
-        want = ops.paged_attention(**a, scale=hd ** -0.5, window=None, impl="general")
+        ordinary = ops.paged_attention(**a, scale=hd ** -0.5, window=None, impl="general")
         torch.cuda.synchronize()
-        torch.testing.assert_close(out.float(), want.float(), atol=tol, rtol=tol)
+        twin = TorchOps().paged_attention(**a, scale=hd ** -0.5, window=None)     # plain PyTorch, no kernel of ours
+        torch.testing.assert_close(out.float(), twin.float(), atol=tol, rtol=tol)
+        torch.testing.assert_close(out.float(), ordinary.float(), atol=tol, rtol=tol)
 
 
 def test_static_scratch_refuses_what_does_not_fit():

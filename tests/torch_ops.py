@@ -125,6 +125,9 @@ class TorchOps:
         T, H, hd = q.shape
         KV = k_pages.shape[1]
         group = H // KV
+        # the same contract as the kernels' front end: the step's bounds cover its requests and fit the table
+        assert block_table.shape[1] * page_size >= max_kv_len, "block_table is too narrow for max_kv_len"
+        assert int(kv_len[:n_seqs].max()) <= max_kv_len and n_seqs <= block_table.shape[0]
         out = torch.zeros_like(q) if out is None else out
         qs = q_start.tolist()
         kl = kv_len.tolist()

@@ -17,7 +17,10 @@ Places = Dict[int, List[Tuple[str, int]]]
 
 
 class _Builder:
-    def __init__(self):
+    def __init__(self, thin: int = 0):
+        # thin > 0: of the places a builder wants, keep a portion's first and last and every
+        # position that is a multiple of ``thin`` (wide vocabularies make every row expensive)
+        self.thin = int(thin)
         self.steps: Steps = []
         self.places: Places = {}
         self.fed: Dict[str, int] = {}
@@ -29,6 +32,8 @@ class _Builder:
         entries, places = [], []
         for rid, toks, want in feeds:
             start = self.fed.get(rid, 0)
+            if self.thin:
+                want = [w for w in want if w in (0, len(toks) - 1) or (start + w) % self.thin == 0]
             entries.append({"id": rid, "tokens": list(toks), "want": list(want)})
             places += [(rid, start + w) for w in want]
             self.fed[rid] = start + len(toks)
@@ -43,17 +48,17 @@ class _Builder:
         return self.steps, self.places, self.peak
 
 
-def whole(reqs: Dict[str, List[int]]):
+def whole(reqs: Dict[str, List[int]], thin: int = 0):
     """Each request alone and whole, one step each, every position wanted."""
-    b = _Builder()
+    b = _Builder(thin)
     for rid, toks in reqs.items():
         b.step([(rid, toks, list(range(len(toks))))], end=[rid])
     return b.result()
 
 
-def tail_one_by_one(reqs: Dict[str, List[int]], tail: int = 32):
+def tail_one_by_one(reqs: Dict[str, List[int]], tail: int = 32, thin: int = 0):
     """Most of each request in one step, the last ``tail`` tokens one by one."""
-    b = _Builder()
+    b = _Builder(thin)
     for rid, toks in reqs.items():
         head = max(len(toks) - tail, 0)
         if head:
@@ -63,9 +68,9 @@ def tail_one_by_one(reqs: Dict[str, List[int]], tail: int = 32):
     return b.result()
 
 
-def portions(reqs: Dict[str, List[int]], sizes=(2, 3, 5, 24, 7, 2, 16, 9, 2, 31, 4)):
+def portions(reqs: Dict[str, List[int]], sizes=(2, 3, 5, 24, 7, 2, 16, 9, 2, 31, 4), thin: int = 0):
     """Each request in portions of changing size, down to two tokens."""
-    b = _Builder()
+    b = _Builder(thin)
     k = 0
     for rid, toks in reqs.items():
         i = 0
@@ -79,11 +84,11 @@ def portions(reqs: Dict[str, List[int]], sizes=(2, 3, 5, 24, 7, 2, 16, 9, 2, 31,
 
 
 def mixed(reqs: Dict[str, List[int]], seed: int = 0, live_max: int = 4, tail: int = 12,
-          chunks=(2, 3, 5, 8, 13, 24, 40)):
+          chunks=(2, 3, 5, 8, 13, 24, 40), thin: int = 0):
     """Up to ``live_max`` live requests: portions of some beside single decoded tokens of others,
     requests now and then left out of a step; finished requests end, new ones take their pages."""
     rng = random.Random(seed)
-    b = _Builder()
+    b = _Builder(thin)
     waiting = list(reqs.items())
     live: List[Tuple[str, List[int]]] = []
     while waiting or live:

@@ -1,5 +1,5 @@
-from .model_config import ConfigError, LlamaConfig, RopeScaling, read_raw_config
+from .model_config import ConfigError, ModelConfig, read_raw_config
 from .registry import ARCHITECTURES, Architecture, get_architecture, load_config, register_architecture
 
-__all__ = ["ConfigError", "LlamaConfig", "RopeScaling", "read_raw_config", "ARCHITECTURES", "Architecture",
+__all__ = ["ConfigError", "ModelConfig", "read_raw_config", "ARCHITECTURES", "Architecture",
            "get_architecture", "load_config", "register_architecture"]

@@ -29,6 +29,9 @@ class Architecture:
     ``build_spec(config)`` returns the model as data.  ``adapt_tensors(config,
     tensors)`` maps foreign tensor names (and layouts) to the native ones.
     ``random_tensors(config, seed)`` yields ``(name, tensor)`` in a fixed order.
+    ``chat_template`` names the template that conversations are rendered with when the caller
+    gives none.  The configuration class derives from
+    :class:`~torchllms_b200.config.model_config.ModelConfig`.
     """
 
     name: str
@@ -80,9 +83,27 @@ def load_config(model_dir, overrides: Optional[Mapping[str, Any]] = None):
 
 _builtin_loaded = False
 
+PLUGINS_ENV = "TORCHLLMS_B200_PLUGINS"
+
 
 def _ensure_builtin() -> None:
+    """Import every module under ``models/`` (each registers its architecture when imported), then
+    the modules that ``TORCHLLMS_B200_PLUGINS`` names (comma separated, importable names): an
+    architecture that lives outside the package reaches the command-line programs that way.  A
+    program that imports such a module itself needs neither."""
     global _builtin_loaded
-    if not _builtin_loaded:
-        _builtin_loaded = True
-        from ..models import llama  # noqa: F401  (registers itself)
+    if _builtin_loaded:
+        return
+    _builtin_loaded = True
+    import importlib
+    import os
+    import pkgutil
+
+    from .. import models
+    for info in pkgutil.iter_modules(models.__path__):
+        importlib.import_module(f"{models.__name__}.{info.name}")
+    for name in filter(None, (n.strip() for n in os.environ.get(PLUGINS_ENV, "").split(","))):
+        try:
+            importlib.import_module(name)
+        except ImportError as e:
+            raise ConfigError(f"{PLUGINS_ENV} names module {name!r}, which cannot be imported: {e}") from None

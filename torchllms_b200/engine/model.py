@@ -16,7 +16,7 @@ import torch
 
 from ..parts import attention, block, ffn, norm, rope  # noqa: F401  (register the built-in parts)
 from ..parts.base import BLOCKS, NORMS, BuildEnv, CacheNeed, Residual, StateNeed, as_compute
-from ..parts.spec import ModelSpec, PartSpec
+from ..parts.spec import ModelSpec
 from ..weights.loader import ExpectedTensor
 
 
@@ -31,12 +31,7 @@ class Model:
         self.max_positions = int(max_positions or spec.max_positions)
         self.env = BuildEnv(dim=spec.dim, dtype=dtype, device=self.device,
                             max_positions=self.max_positions, ops=ops)
-        self.blocks = []
-        for layer in spec.layers:
-            params = dict(layer.block.params)
-            params.update(mixer=layer.mixer, feed_forward=layer.feed_forward,
-                          mixer_norm=layer.mixer_norm, ffn_norm=layer.ffn_norm)
-            self.blocks.append(BLOCKS.build(PartSpec(layer.block.kind, params), self.env))
+        self.blocks = [BLOCKS.build(layer.block, self.env) for layer in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm, self.env)
         self.graph_safe = self.final_norm.graph_safe and all(b.graph_safe for b in self.blocks)
         self.embedding: Optional[torch.Tensor] = None

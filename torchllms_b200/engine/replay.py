@@ -44,7 +44,7 @@ class Replayer:
         _arch, config = load_config(model_dir)
         # The pool is made for max_tokens, so the position table must reach as far as one
         # request could grow inside it, whatever the configuration's own limit says.
-        max_positions = max(int(getattr(config, "max_seq_len", 0)), round_up(max_tokens, page_size))
+        max_positions = max(int(config.max_seq_len), round_up(max_tokens, page_size))
         _, self.config, model = load_model(model_dir, dtype=dtype, device=device, ops=ops,
                                            max_positions=max_positions)
         self.engine = Engine(model, page_size=page_size, pool_tokens=round_up(max_tokens, page_size),

@@ -114,15 +114,31 @@ class Scheduler:
         if request.budget <= 0:
             request.finished = True          # nothing to generate: an empty result at once
             return
-        page = self.engine.cache.page_size
         need = len(request.prompt) + request.budget - 1   # the last sampled token is never fed
-        pool = min(g.allocator.n_pages for g in self.engine.cache.groups) * page if self.engine.cache.groups else need
-        if need > self.engine.max_len or -(-need // page) * page > pool:
+        most = min(self.engine.max_len, self._most_cached_tokens(need))
+        if need > most:
             request.finished = True
             request.error = (f"request needs {need} cached tokens but the engine holds at most "
-                             f"{min(self.engine.max_len, pool)} for one request")
+                             f"{most} for one request")
             return
         self.waiting.append(request)
+
+    def _most_cached_tokens(self, need: int) -> int:
+        """How long a request that has the pool to itself may grow, given that it wants ``need``.
+        A group that keeps every key holds its page count times the page size.  A window group
+        gives pages back as the request grows: it only has to hold the window and the portion
+        being fed (plus a page for where they start and end), however long the request gets."""
+        cache = self.engine.cache
+        page = cache.page_size
+        most = need
+        for g in cache.groups:
+            held = g.allocator.n_pages * page
+            if g.need.kind == "window":
+                portion = min(self.prefill_chunk, self.max_num_batched_tokens)
+                if (-(-(g.need.window + portion) // page) + 1) * page <= held:
+                    continue                      # it never holds more than that: no limit from this group
+            most = min(most, held)
+        return most
 
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)

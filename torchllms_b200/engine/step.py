@@ -18,6 +18,7 @@ have fixed addresses, which is what CUDA-graph replay of decode steps needs.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence, Tuple
 
@@ -47,12 +48,13 @@ class StepEntry:
 class PreparedStep:
     """What :meth:`Engine.prepare` decided: everything of a step but the token values."""
 
-    handles: List[int]
+    handles: List[int]       # in batch order (see ``order``)
     q_lens: List[int]
     starts: List[int]        # each request's length before the step
     kv_lens: List[int]
     slots: List[int]
     n_want: int
+    order: Optional[List[int]] = None   # batch place -> index among the caller's entries; None: as given
 
 
 @dataclass
@@ -77,6 +79,7 @@ class StepContext:
     q_lens: List[int] = field(default_factory=list)
     kv_lens: List[int] = field(default_factory=list)
     slots: List[int] = field(default_factory=list)
+    decode_kv_bound: int = 0     # the context length that the one-token rows of a mixed step plan their attention for
 
 
 class _StepBuffers:
@@ -178,6 +181,8 @@ class Engine:
         self._graph_pool = None
         self.graph_replays = 0
         self._forced_bound: Optional[int] = None      # capture_decode_graphs: record for this context bound
+        # TORCHLLMS_B200_DEBUG=1: range-check every index array of a step on the host before it is uploaded
+        self.debug = os.environ.get("TORCHLLMS_B200_DEBUG", "") not in ("", "0")
 
     # ----------------------------------------------------------------- requests
     def claim(self) -> int:
@@ -194,7 +199,7 @@ class Engine:
         (while fewer than ``max_prompt_graphs`` of those exist); later steps replay.  The logits
         buffer of a shape is reused: its contents hold until the next step of that shape."""
         key = self._shape_key(ctx.n_tokens, ctx.n_seqs, ctx.n_want, ctx.max_q_len, ctx.n_decode,
-                              ctx.max_kv_len if ctx.max_q_len <= 16 else 0)
+                              ctx.max_kv_len if ctx.max_q_len <= 16 else 0, ctx.decode_kv_bound)
         entry = self._graphs.get(key)
         if entry is None:
             seen = self._graph_seen.get(key, 0)
@@ -218,8 +223,9 @@ class Engine:
         return self._replay(entry)
 
     @staticmethod
-    def _shape_key(n_tokens: int, n_seqs: int, n_want: int, max_q_len: int, n_decode: int, kv_bound: int):
-        return (n_tokens, n_seqs, n_want, max_q_len, n_decode, kv_bound)
+    def _shape_key(n_tokens: int, n_seqs: int, n_want: int, max_q_len: int, n_decode: int, kv_bound: int,
+                   decode_bound: int = 0):
+        return (n_tokens, n_seqs, n_want, max_q_len, n_decode, kv_bound, decode_bound)
 
     BOUND_BELOW = 16     # steps of fewer requests plan for a bound of their longest context, others for max_len
 
@@ -297,56 +303,114 @@ class Engine:
         the next step while the device still runs the current one, then :meth:`run_prepared` once
         the tokens are known, or :meth:`discard` if the step will not happen after all.  Only one
         prepared step can exist at a time."""
-        handles = [h for h, _n, _w in shape]
-        q_lens = [int(n) for _h, n, _w in shape]
-        T, B = sum(q_lens), len(shape)
-        if B == 0 or min(q_lens) <= 0:
+        shape = [(h, int(n), w) for h, n, w in shape]
+        T, B = sum(n for _h, n, _w in shape), len(shape)
+        if B == 0 or min(n for _h, n, _w in shape) <= 0:
             raise StepError("every entry of a step must bring at least one token")
         if T > self.max_step_tokens:
             raise StepError(f"a step may bring at most {self.max_step_tokens} tokens, got {T}")
         if B > self.cache.max_num_seqs:
             raise StepError(f"a step may hold at most {self.cache.max_num_seqs} requests, got {B}")
-        want_rows: List[int] = []
-        base = 0
-        for (h, _n, want), n in zip(shape, q_lens):
-            for w in ([n - 1] if want is None else want):
+        for h, n, want in shape:
+            for w in (want or ()):
                 if not 0 <= w < n:
                     raise StepError(f"request {h}: wanted place {w} is outside its {n} tokens")
-                want_rows.append(base + w)
-            base += n
+            if want is not None and len(set(want)) != len(want):
+                raise StepError(f"request {h}: a place is wanted twice")
+        # Inside the batch, requests that bring one token stand before those that bring more (each kind
+        # in the caller's order): the mixer sends the two kinds to kernels made for them.  The wanted
+        # rows keep the caller's order, so nothing of this shows outside.
+        order = sorted(range(B), key=lambda i: shape[i][1] != 1)
+        identity = order == list(range(B))
+        handles = [shape[i][0] for i in order]
+        q_lens = [shape[i][1] for i in order]
+        base_of = [0] * B                       # caller's entry -> its first row in the batch
+        base = 0
+        for i in order:
+            base_of[i] = base
+            base += shape[i][1]
+        want_rows: List[int] = []
+        for i, (_h, n, want) in enumerate(shape):
+            want_rows += [base_of[i] + w for w in ([n - 1] if want is None else want)]
 
         cache = self.cache
         starts = cache.extend_many(list(zip(handles, q_lens)))  # may raise OutOfPages
-        buf = self._buf
-        buf.wait_host_free()
-        buf.lay_out(T, B)
-        lens = np.asarray(q_lens, dtype=np.int64)
-        first = np.asarray(starts, dtype=np.int64)
-        q_start = np.zeros(B + 1, dtype=np.int64)
-        np.cumsum(lens, out=q_start[1:])
-        kv_lens = (first + lens).tolist()
-        slots = [cache.slot(h) for h in handles]
-        # per token: which request it belongs to and its absolute position (no loop over requests)
-        seq_of = np.repeat(np.arange(B, dtype=np.int64), lens)
-        pos_all = np.arange(T, dtype=np.int64) - q_start[seq_of] + first[seq_of]
-        buf.host_view("positions")[:T] = pos_all
-        buf.host_view("seq_of_token")[:T] = seq_of
-        buf.host_view("q_start")[:B + 1] = q_start
-        buf.host_view("kv_len")[:B] = kv_lens
-        buf.host_view("state_slot")[:B] = slots
-        buf.host_view("fresh")[:B] = first == 0
-        buf.host_view("want_rows")[:len(want_rows)] = want_rows
-        page = cache.page_size
-        for g in range(len(cache.groups)):
-            rows = cache.block_table_rows(g, slots)                       # [B, max_blocks]
-            pages = rows[seq_of, pos_all // page]
-            if (pages < 0).any():
-                for h, s0 in zip(handles, starts):
-                    cache.truncate(h, s0)
-                raise StepError("a token of this step falls on a page that was already given back")
-            buf.host_view(f"slot_mapping{g}")[:T] = pages * page + pos_all % page
-            buf.host_view(f"block_table{g}")[:B * buf.NB].reshape(B, buf.NB)[:] = rows
-        return PreparedStep(handles, q_lens, starts, kv_lens, slots, len(want_rows))
+        try:
+            buf = self._buf
+            buf.wait_host_free()
+            buf.lay_out(T, B)
+            lens = np.asarray(q_lens, dtype=np.int64)
+            first = np.asarray(starts, dtype=np.int64)
+            q_start = np.zeros(B + 1, dtype=np.int64)
+            np.cumsum(lens, out=q_start[1:])
+            kv_lens = (first + lens).tolist()
+            slots = [cache.slot(h) for h in handles]
+            # per token: which request it belongs to and its absolute position (no loop over requests)
+            seq_of = np.repeat(np.arange(B, dtype=np.int64), lens)
+            pos_all = np.arange(T, dtype=np.int64) - q_start[seq_of] + first[seq_of]
+            buf.host_view("positions")[:T] = pos_all
+            buf.host_view("seq_of_token")[:T] = seq_of
+            buf.host_view("q_start")[:B + 1] = q_start
+            buf.host_view("kv_len")[:B] = kv_lens
+            buf.host_view("state_slot")[:B] = slots
+            buf.host_view("fresh")[:B] = first == 0
+            buf.host_view("want_rows")[:len(want_rows)] = want_rows
+            page = cache.page_size
+            for g in range(len(cache.groups)):
+                rows = cache.block_table_rows(g, slots)                       # [B, max_blocks]
+                pages = rows[seq_of, pos_all // page]
+                if (pages < 0).any():
+                    raise StepError("a token of this step falls on a page that was already given back")
+                buf.host_view(f"slot_mapping{g}")[:T] = pages * page + pos_all % page
+                buf.host_view(f"block_table{g}")[:B * buf.NB].reshape(B, buf.NB)[:] = rows
+            if self.debug:
+                self._check_packed(T, B, len(want_rows))
+        except BaseException:
+            for h, s0 in zip(handles, starts):      # whatever went wrong, the cache is as the step found it
+                cache.truncate(h, s0)
+            raise
+        return PreparedStep(handles, q_lens, starts, kv_lens, slots, len(want_rows), None if identity else order)
+
+    @staticmethod
+    def _in_batch_order(prepared: "PreparedStep", per_token: Sequence) -> Sequence:
+        """Per-token values given in the caller's order of entries, in the batch's order."""
+        if prepared.order is None:
+            return per_token
+        B = len(prepared.order)
+        given_len = [0] * B
+        for place, i in enumerate(prepared.order):
+            given_len[i] = prepared.q_lens[place]
+        offset = [0] * (B + 1)
+        for i in range(B):
+            offset[i + 1] = offset[i] + given_len[i]
+        out: list = []
+        for i in prepared.order:
+            out.extend(per_token[offset[i]:offset[i + 1]])
+        return out
+
+    def _check_packed(self, T: int, B: int, n_want: int) -> None:
+        """Debug mode: every index the kernels will trust lies where it must (the reference checks
+        its layout on the host too, torchllms/models/paged_kv.py:797-843)."""
+        buf, cache = self._buf, self.cache
+
+        def within(name: str, values: np.ndarray, lo: int, hi: int) -> None:
+            bad = np.nonzero((values < lo) | (values >= hi))[0]
+            if bad.size:
+                raise StepError(f"debug check: {name}[{int(bad[0])}] = {int(values[bad[0]])} is outside {lo}..{hi - 1}")
+
+        within("positions", buf.host_view("positions")[:T], 0, self.max_len)
+        within("seq_of_token", buf.host_view("seq_of_token")[:T], 0, B)
+        within("want_rows", buf.host_view("want_rows")[:n_want], 0, T)
+        within("state_slot", buf.host_view("state_slot")[:B], 0, cache.max_num_seqs)
+        within("kv_len", buf.host_view("kv_len")[:B], 1, self.max_len + 1)
+        q_start = buf.host_view("q_start")[:B + 1]
+        if q_start[0] != 0 or q_start[B] != T or (np.diff(q_start) <= 0).any():
+            raise StepError(f"debug check: q_start {q_start.tolist()} does not cut {T} tokens into {B} portions")
+        for g, group in enumerate(cache.groups):
+            n_pages = group.allocator.n_pages
+            within(f"slot_mapping{g}", buf.host_view(f"slot_mapping{g}")[:T], 0, n_pages * cache.page_size)
+            table = buf.host_view(f"block_table{g}")[:B * buf.NB]
+            within(f"block_table{g}", table, -1, n_pages)      # -1: no page (never allocated, or given back)
 
     def discard(self, prepared: "PreparedStep") -> None:
         """Undo :meth:`prepare`: the cache is as it was before (requests released meanwhile are skipped)."""
@@ -372,13 +436,14 @@ class Engine:
                 rows = list(range(T)) if rows is None else list(rows)
                 if len(rows) != T or min(rows) < 0 or max(rows) >= tokens.shape[0]:
                     raise StepError(f"the prepared step holds {T} tokens; rows {rows} of {tokens.shape[0]} ids do not give them")
+                rows = self._in_batch_order(prepared, rows)
                 buf.host_view("token_src")[:T] = rows      # the gather's index rides in the step's one upload
                 buf.upload(skip_tokens=True)
                 torch.index_select(tokens, 0, buf.dev_view("token_src", T), out=buf.dev_view("token_ids", T))
             elif len(tokens) != T:
                 raise StepError(f"the prepared step holds {T} tokens, got {len(tokens)}")
             else:
-                flat = np.asarray(tokens, dtype=np.int64)
+                flat = np.asarray(self._in_batch_order(prepared, tokens), dtype=np.int64)
                 if flat.min() < 0 or flat.max() >= self.vocab_size:
                     bad = int(flat[(flat < 0) | (flat >= self.vocab_size)][0])
                     raise StepError(f"token id {bad} is outside the vocabulary (0..{self.vocab_size - 1})")
@@ -392,14 +457,17 @@ class Engine:
             # longest context, so that their launch shapes change only when a request outgrows it
             short = max_q <= 16
             bound = (self._forced_bound or self.kv_bound(max(kv_lens), B)) if short else 0
-            recorded = self._graphs.get(self._shape_key(T, B, n_want, max_q, n_decode, bound)) if self.use_graphs else None
+            # a mixed step's one-token rows go to the decode kernel apart from the portions: their own bound
+            decode_bound = self.kv_bound(max(kv_lens[:n_decode]), n_decode) if 0 < n_decode < B else 0
+            recorded = (self._graphs.get(self._shape_key(T, B, n_want, max_q, n_decode, bound, decode_bound))
+                        if self.use_graphs else None)
             if recorded is not None:
                 # the graph reads the buffers uploaded above at their fixed addresses: nothing else to build
                 logits = self._replay(recorded)
             else:
                 ctx = StepContext(
                     n_tokens=T, n_seqs=B, n_want=n_want, max_q_len=max_q, n_decode=n_decode,
-                    max_kv_len=bound if short else max(kv_lens),
+                    max_kv_len=bound if short else max(kv_lens), decode_kv_bound=decode_bound,
                     token_ids=buf.dev_view("token_ids", T), positions=buf.dev_view("positions", T),
                     seq_of_token=buf.dev_view("seq_of_token", T), q_start=buf.dev_view("q_start", B + 1),
                     kv_len=buf.dev_view("kv_len", B), state_slot=buf.dev_view("state_slot", B),

@@ -123,6 +123,11 @@ class LLM:
         self._tokenizer = None
         if self.template is not None and self.template.stop_token_ids:
             eos_ids = list(self.template.stop_token_ids)           # the template's stop ids win (:188-189)
+        elif self.template is None and self.arch.chat_template and self._load_tokenizer(required=False) is not None:
+            # no template named: a folder with a tokenizer gets its architecture's; the caller's stop ids stand
+            self.template = get_template(self.arch.chat_template)
+            if eos_ids is None and self.template.stop_token_ids:
+                eos_ids = list(self.template.stop_token_ids)
         if eos_ids is None:
             tok = self._load_tokenizer(required=False)
             eos_ids = [tok.eos_token_id] if tok is not None and tok.eos_token_id is not None else []

@@ -14,7 +14,7 @@ from typing import Any, Dict, Iterator, Mapping, Tuple
 
 import torch
 
-from ..config.model_config import LlamaConfig
+from .llama_config import LlamaConfig
 from ..config.registry import Architecture, register_architecture
 from ..parts.spec import LayerSpec, ModelSpec, RunEntry, part
 from ..weights.loader import LazyTensor
@@ -34,10 +34,10 @@ def build_spec(cfg: LlamaConfig) -> ModelSpec:
                  head_dim=cfg.head_dim, scale=cfg.head_dim ** -0.5, position=position, window=None)
     ffn = part("swiglu", dim=cfg.dim, hidden=cfg.ffn_hidden)
     norm = part("rmsnorm", dim=cfg.dim, eps=cfg.norm_eps)
-    block = part("prenorm", mixer_prefix="attention", ffn_prefix="feed_forward",
+    block = part("prenorm", mixer=mixer, feed_forward=ffn, mixer_norm=norm, ffn_norm=norm,
+                 mixer_prefix="attention", ffn_prefix="feed_forward",
                  mixer_norm_prefix="attention_norm", ffn_norm_prefix="ffn_norm")
-    layers = tuple(LayerSpec(name=f"layers.{i}", block=block, mixer=mixer, feed_forward=ffn,
-                             mixer_norm=norm, ffn_norm=norm) for i in range(cfg.n_layers))
+    layers = tuple(LayerSpec(name=f"layers.{i}", block=block) for i in range(cfg.n_layers))
     return ModelSpec(
         dim=cfg.dim,
         vocab_size=cfg.vocab_size,

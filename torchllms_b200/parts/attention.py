@@ -73,7 +73,7 @@ class PagedAttention(Mixer):
             # shape made for it, both writing into one output
             o = torch.empty_like(q)
             ops.paged_attention(q, cache.k_pages, cache.v_pages, cache.block_table[:nd], ctx.q_start[:nd + 1],
-                                ctx.kv_len[:nd], n_seqs=nd, max_q_len=1, max_kv_len=self.env.max_positions,
+                                ctx.kv_len[:nd], n_seqs=nd, max_q_len=1, max_kv_len=ctx.decode_kv_bound,
                                 n_tokens=nd, out=o, **common)
             ops.paged_attention(q, cache.k_pages, cache.v_pages, cache.block_table[nd:], ctx.q_start[nd:],
                                 ctx.kv_len[nd:], n_seqs=B - nd, max_q_len=ctx.max_q_len, max_kv_len=ctx.max_kv_len,

@@ -41,18 +41,14 @@ def part(kind: str, **params: Any) -> PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer's own weights: a block arrangement over a mixer and a feed-forward.
-
-    ``name`` is the prefix of the layer's tensors (``layers.3``).  The block
-    kind decides where the norms sit and how the residual is carried.
-    """
+    """One layer's own weights: ``name`` is the prefix of the layer's tensors (``layers.3``),
+    ``block`` the arrangement.  The block's parameters carry everything inside it as nested
+    specs (mixers, feed-forwards, norms, however many and wherever the block kind puts them),
+    just as a mixer carries its position encoding; nothing outside the block kind knows what a
+    layer is made of."""
 
     name: str
     block: PartSpec
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    ffn_norm: PartSpec
 
 
 @dataclass(frozen=True)

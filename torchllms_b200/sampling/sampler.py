@@ -80,7 +80,8 @@ class Sampler:
             host = host.pin_memory()        # a copy from pageable memory would wait for the device
         dev = host.to(self.device, non_blocking=True)
         temperature = dev[:, 0].contiguous().view(torch.float32)
-        top_k = dev[:, 1].contiguous()
+        # without a rank filter in the batch the kernel library may spread a row over many CTAs
+        top_k = dev[:, 1].contiguous() if any((p.top_k or 0) > 0 for p in params) else None
         row_keys = dev[:, 2:4].contiguous().view(torch.int64).reshape(n)
         return self.ops.sample(logits, temperature, top_k, row_keys)
 
