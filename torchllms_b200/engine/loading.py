@@ -56,7 +56,8 @@ def load_model(path, *, dtype="bfloat16", device="cuda", overrides: Optional[Map
         source = TensorSource(p if p.is_file() and p.suffix == ".safetensors" else model_dir_of(p))
         found.update(arch.adapt_tensors(config, source_tensors(source)))
     expected = model.expected_tensors()
-    if spec.tie_head and spec.head_tensor in found and spec.embedding_tensor in found:
+    if (spec.tie_head and spec.head_tensor != spec.embedding_tensor
+            and spec.head_tensor in found and spec.embedding_tensor in found):
         # A tied model stores one table.  A second copy is tolerated only if it is the same table.
         head, table = found[spec.head_tensor], found[spec.embedding_tensor]
         same = tuple(head.shape) == tuple(table.shape) and torch.equal(head.materialize(), table.materialize())
