@@ -87,6 +87,28 @@ def make_tensors(cfg: dict, seed: int, *, std: float = 0.02, qk_std: Optional[fl
     return out
 
 
+_TO_HF_LAYER = {"attention.wq.weight": "self_attn.q_proj.weight", "attention.wk.weight": "self_attn.k_proj.weight",
+                "attention.wv.weight": "self_attn.v_proj.weight", "attention.wo.weight": "self_attn.o_proj.weight",
+                "feed_forward.w1.weight": "mlp.gate_proj.weight", "feed_forward.w3.weight": "mlp.up_proj.weight",
+                "feed_forward.w2.weight": "mlp.down_proj.weight", "attention_norm.weight": "input_layernorm.weight",
+                "ffn_norm.weight": "post_attention_layernorm.weight"}
+_TO_HF_TOP = {"tok_embeddings.weight": "model.embed_tokens.weight", "norm.weight": "model.norm.weight",
+              "output.weight": "lm_head.weight"}
+
+
+def hugging_face_names(tensors: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    """The same tensors under Hugging Face names, values untouched (so the rows of q and k now
+    stand in Hugging Face's order: a head's first halves, then its second halves)."""
+    out = {}
+    for name, t in tensors.items():
+        if name.startswith("layers."):
+            _, i, rest = name.split(".", 2)
+            out[f"model.layers.{i}.{_TO_HF_LAYER[rest]}"] = t
+        else:
+            out[_TO_HF_TOP[name]] = t
+    return out
+
+
 def write_model_folder(folder, cfg: dict, tensors: Dict[str, torch.Tensor], dtype=torch.float32) -> Path:
     """Tests write their folders with the ``safetensors`` package, not with the engine's writer."""
     from safetensors.torch import save_file
@@ -108,7 +130,7 @@ def round_up(n: int, m: int) -> int:
 
 
 def run_trace(model_dir, dtype: str, steps: Sequence[dict], out_dir, max_tokens: int, *, timeout=900,
-              user: Optional[int] = None, cwd=None) -> Dict[int, np.ndarray]:
+              user: Optional[int] = None, cwd=None, vocab: Optional[int] = None) -> Dict[int, np.ndarray]:
     """Run bin/trace_run as a child process; returns {step: logits [wanted, vocab]}."""
     out_dir = Path(out_dir)
     out_dir.mkdir(parents=True, exist_ok=True)
@@ -122,7 +144,8 @@ def run_trace(model_dir, dtype: str, steps: Sequence[dict], out_dir, max_tokens:
         raise RuntimeError(f"trace_run exited {proc.returncode}\nstdout:\n{proc.stdout[-2000:]}\nstderr:\n{proc.stderr[-4000:]}")
     done = [l for l in proc.stdout.splitlines() if l.startswith("done ")]
     assert [int(l.split()[1]) for l in done] == [s["step"] for s in steps], "one 'done' line per step, in order"
-    vocab = json.loads((Path(model_dir) / "config.json").read_text())["vocab_size"]
+    if vocab is None:
+        vocab = json.loads((Path(model_dir) / "config.json").read_text())["vocab_size"]
     result = {}
     for s in steps:
         n_want = sum(len(e.get("want", [])) for e in s["entries"])

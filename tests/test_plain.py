@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import plain_llama
-from helpers import TINY, make_tensors, write_model_folder
+from helpers import TINY, hugging_face_names, make_tensors, write_model_folder
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
@@ -27,6 +27,33 @@ def test_plain_reproduces_the_reference_model(tmp_path, name):
         assert (rows - torch.tensor(p["logits_head"])).abs().max() < 1e-5
         assert (logits.double().sum(-1) - torch.tensor(p["logit_sum"], dtype=torch.float64)).abs().max() < 1e-3
         assert logits.argmax(-1).tolist() == p["argmax"]
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_hugging_face_row_order_is_the_reference_converters(tmp_path, name):
+    """The same tensors under Hugging Face names mean another model (their q and k rows are then
+    in half-split order).  The record's ``hf`` entry is what the reference computes after its own
+    converter has permuted them (torchllms/models/checkpoint_converter.py:96-108, :172-178); the
+    plain implementation, with a permutation written on its own, and the engine, with its
+    ``adapt_tensors``, must both land there."""
+    from torch_ops import TorchOps
+    from torchllms_b200.engine.replay import Replayer
+    rec = json.loads((GOLDEN / f"tiny_{name}.json").read_text())
+    cfg, seed, page = TINY[name]
+    assert rec["hf"]["max_diff_to_plain"] < 1e-5
+    folder = write_model_folder(tmp_path, cfg, hugging_face_names(make_tensors(cfg, seed, std=rec["std"], qk_std=rec["qk_std"])))
+    plain = plain_llama.PlainModel(folder)
+    engine = Replayer(folder, "float32", 256, page_size=page, device="cpu", ops=TorchOps())
+    for i, (p, native) in enumerate(zip(rec["hf"]["prompts"], rec["prompts"])):
+        toks = p["tokens"]
+        got = engine.run_step({"step": i, "entries": [{"id": str(i), "tokens": toks, "want": list(range(len(toks)))}], "end": [str(i)]})
+        for logits in (plain.logits(toks), torch.from_numpy(got)):
+            rows = logits[[0, len(toks) // 2, -1]][:, :len(p["logits_head"][0])]
+            assert (rows - torch.tensor(p["logits_head"])).abs().max() < 2e-5
+            assert (logits.double().sum(-1) - torch.tensor(p["logit_sum"], dtype=torch.float64)).abs().max() < 2e-3
+            assert logits.argmax(-1).tolist() == p["argmax"]
+        if len(toks) > 1:
+            assert p["logit_sum"][-1] != native["logit_sum"][-1]      # not the model the native names give
 
 
 def test_rope_frequencies_agree_with_the_engines_table():

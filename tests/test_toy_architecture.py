@@ -111,7 +111,7 @@ def test_replays_through_trace_run_on_the_gpu(tmp_path, dtype, which):
     try:
         for mode, kw in (("whole", {}), ("portions", {}), ("mixed", dict(chunks=(2, 5, 24, 96, 150, 40)))):
             steps, places, peak = getattr(traces, mode)(reqs, **kw)
-            got = run_trace(folder, dtype, steps, tmp_path / mode, max_tokens=peak)
+            got = run_trace(folder, dtype, steps, tmp_path / mode, max_tokens=peak, vocab=cfg.vocab)
             for step, rows in places.items():
                 want = np.stack([ref[rid][pos] for rid, pos in rows])
                 err = np.abs(got[step] - want).max(axis=1)
