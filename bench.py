@@ -126,22 +126,49 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    """The unmodified reference through its own public API, if it is installed under baseline/_ref
-    (pip install --no-index --no-build-isolation --no-deps --target baseline/_ref <reference>)."""
+    """The unmodified reference through its own public API, installed under baseline/_ref
+    (pip install --no-index --no-build-isolation --no-deps --target baseline/_ref <reference>, plus its
+    data folder torchllms/messages/configs, which the wheel leaves out).  It runs in a process of its
+    own (``baseline/reference_arm.py``) so that nothing of this package is on its path; this process
+    only samples the clocks meanwhile and passes the line on.  Anything that keeps it from running is
+    reported as ``unavailable``."""
     ref = ROOT / "baseline" / "_ref"
+    script = ROOT / "baseline" / "reference_arm.py"
     if not (ref / "torchllms").is_dir():
-        why = "reference not installed under baseline/_ref"
-    else:
-        sys.path.insert(0, str(ref))
-        os.environ.setdefault("HF_HUB_OFFLINE", "1")
-        os.environ.setdefault("TRANSFORMERS_OFFLINE", "1")
+        print(json.dumps({"impl": "reference", "unavailable": "reference not installed under baseline/_ref"}))
+        return 0
+    if not (ref / "torchllms" / "messages" / "configs").is_dir():
+        print(json.dumps({"impl": "reference", "unavailable": "installed reference lacks torchllms/messages/configs (data the wheel leaves out)"}))
+        return 0
+    cmd = [sys.executable, str(script), "--steps", str(args.steps), "--warmup", str(args.warmup),
+           "--batch", str(args.batch), "--layers", str(args.layers)]
+    env = {k: v for k, v in os.environ.items() if k != "PYTHONPATH"}
+    with ClockSampler() as clocks:
         try:
-            from torchllms.inference import LLM  # noqa: F401
-            why = ("the reference's LLM needs a tokenizer folder and a consolidated.00.pth checkpoint of the 8B "
-                   "shape (neither exists offline) and takes text prompts only; not driven")
-        except Exception as e:   # the installed package does not import
-            why = f"installed reference does not import: {type(e).__name__}: {str(e)[:160]}"
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+            proc = subprocess.run(cmd, capture_output=True, text=True, timeout=1500, env=env, cwd=str(ROOT / "baseline"))
+        except subprocess.TimeoutExpired:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference run did not finish within 1500 s"}))
+            return 0
+        time.sleep(0.15)
+    sys.stderr.write(proc.stderr[-4000:])
+    line = None
+    for text in reversed(proc.stdout.strip().splitlines()):
+        if text.startswith("{"):
+            try:
+                line = json.loads(text)
+                break
+            except ValueError:
+                continue
+    if proc.returncode != 0 or line is None or "value" not in line:
+        tail = " | ".join(l.strip() for l in proc.stderr.strip().splitlines()[-3:])[-300:]
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference run exited {proc.returncode}: {tail}"}))
+        return 0
+    window = line.pop("timed_window", None)
+    if window:
+        clocks.mark(window[0], window[1])
+    line["clocks"] = clocks.summary()
+    line["gpu_launches"] = 0          # this arm launches none of this repository's kernels
+    print(json.dumps(line))
     return 0
 
 
@@ -278,6 +305,7 @@ def main():
     for _ in range(3):
         prefill_once()
     pre_ms = sorted(prefill_once() for _ in range(5))[2]
+    ops.check_status()
     # 2 flops per weight per token; q, k, v, o projections: dim * hd * (2 H + 2 KV) weights; gate, up, down:
     # 3 * dim * hidden; the head runs on one row; causal attention: QK^T and PV, each 2 * H * hd * T^2 / 2
     lin = PROMPT_LEN * (args.layers * (2 * cfg.dim * cfg.head_dim * (2 * cfg.n_heads + 2 * cfg.n_kv_heads)
@@ -316,6 +344,9 @@ def main():
             clocks.mark(t_start, time.time())
             time.sleep(0.15)
             clocks.__exit__()
+        ops.check_status()                                  # a kernel that gave up a wait has said so by now
+        if not bool(torch.isfinite(logits).all()):
+            raise RuntimeError(f"decode at batch {batch}: the last step's logits are not finite")
         ms = a.elapsed_time(b) / steps
         for h in handles:
             engine.release(h)
@@ -389,8 +420,17 @@ def main():
     n_new = args.warmup + args.steps
     llm.warmup(range(1, args.batch + 1))                                            # decode graphs, as at server start
     llm.generate(prompt_token_ids=prompts(args.batch, 64), max_new_tokens=4, disable_tqdm=True)        # warm the path
-    llm.generate(prompt_token_ids=prompts(args.batch, ctx_len), max_new_tokens=n_new, disable_tqdm=True)
+    e2e_prompts = prompts(args.batch, ctx_len)
+    e2e_out = llm.generate(prompt_token_ids=e2e_prompts, max_new_tokens=n_new, disable_tqdm=True)
     st = llm.last_stats
+    ops.check_status()
+    # the timed run launches each decode step before it has read the tokens of the step before: the
+    # step-by-step way must give the same greedy tokens
+    llm.look_ahead = False
+    check = llm.generate(prompt_token_ids=e2e_prompts, max_new_tokens=8, disable_tqdm=True)
+    llm.look_ahead = True
+    if [r.token_ids[:8] for r in e2e_out] != [r.token_ids for r in check] or any(r.error for r in e2e_out):
+        raise RuntimeError("end to end: launching ahead and the step-by-step way disagree on the first 8 greedy tokens")
     e2e_tok_s = st.decode_step_tokens / st.decode_seconds if st.decode_seconds > 0 else None
     h2d = engine._buf.uploaded_bytes                 # the last decode step's one upload (positions, slots, block tables)
     e2e = {"value": round(e2e_tok_s, 1) if e2e_tok_s else None, "unit": "tokens/s",

@@ -103,25 +103,48 @@ def to_bfloat16_and_back(t: torch.Tensor) -> torch.Tensor:
     return t.to(torch.bfloat16).to(t.dtype)
 
 
-def attention_layer(x, wq, wk, wv, wo, cfg, cos, sin, stored=_same):
+def attention_layer(x, wq, wk, wv, wo, cfg, cos, sin, stored=_same, scale=None):
     """torchllms/models/networks.py:513-558: project, view as heads, rope q and k, attend, project.
-    ``stored`` is applied wherever the engine keeps an intermediate in its activation dtype."""
+    ``stored`` is applied wherever the engine keeps an intermediate in its activation dtype.
+    ``scale`` ([S, 1], see :func:`weighted_rows`): ``x`` is not normalised yet and the projections
+    are multiplied by it."""
     S = x.shape[0]
-    q = stored(x @ wq.T).view(S, cfg["n_heads"], cfg["head_dim"])
-    k = stored(x @ wk.T).view(S, cfg["n_kv_heads"], cfg["head_dim"])
-    v = stored(x @ wv.T).view(S, cfg["n_kv_heads"], cfg["head_dim"])
+    q, k, v = stored(x @ wq.T), stored(x @ wk.T), stored(x @ wv.T)
+    if scale is not None:
+        q, k, v = q * scale, k * scale, stored(v * scale)
+    q, k, v = (q.view(S, cfg["n_heads"], cfg["head_dim"]), k.view(S, cfg["n_kv_heads"], cfg["head_dim"]),
+               v.view(S, cfg["n_kv_heads"], cfg["head_dim"]))
     q, k = stored(apply_rope(q, cos, sin)), stored(apply_rope(k, cos, sin))
     return stored(stored(causal_attention(q, k, v)) @ wo.T)
 
 
+def weighted_rows(x: torch.Tensor, weight: torch.Tensor, eps: float):
+    """The same norm (torchllms/models/networks.py:195-200) in the order the engine's bfloat16 mode
+    takes it when a matrix product follows: the rows are stored as ``x * weight`` and the factor
+    ``rsqrt(mean(x^2) + eps)`` is applied to the product instead (a product is linear in its input).
+    Returns the weighted rows and the factor ``[S, 1]``."""
+    xf = x.float()
+    return xf * weight, torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+
+
 def block(x, w: Dict[str, torch.Tensor], prefix: str, cfg, cos, sin, stored=_same):
-    """torchllms/models/networks.py:635-644: pre-norm residual block."""
+    """torchllms/models/networks.py:635-644: pre-norm residual block.  With a ``stored`` that rounds
+    (the emulation of the engine's bfloat16 mode) the two norms are taken in the engine's order
+    (:func:`weighted_rows`); in float32 both orders are the same numbers up to rounding and the
+    reference's is kept."""
     g = lambda n: w[f"{prefix}.{n}"]
-    h = x + attention_layer(stored(rms_norm(x, g("attention_norm.weight"), cfg["eps"])),
-                            g("attention.wq.weight"), g("attention.wk.weight"),
-                            g("attention.wv.weight"), g("attention.wo.weight"), cfg, cos, sin, stored)
-    n = stored(rms_norm(h, g("ffn_norm.weight"), cfg["eps"]))
-    gate, up = stored(n @ g("feed_forward.w1.weight").T), stored(n @ g("feed_forward.w3.weight").T)
+    if stored is _same:
+        h = x + attention_layer(rms_norm(x, g("attention_norm.weight"), cfg["eps"]),
+                                g("attention.wq.weight"), g("attention.wk.weight"),
+                                g("attention.wv.weight"), g("attention.wo.weight"), cfg, cos, sin)
+        n = rms_norm(h, g("ffn_norm.weight"), cfg["eps"])
+        return h + swiglu_ffn(n, g("feed_forward.w1.weight"), g("feed_forward.w2.weight"), g("feed_forward.w3.weight"))
+    n, scale = weighted_rows(x, g("attention_norm.weight"), cfg["eps"])
+    h = x + attention_layer(stored(n), g("attention.wq.weight"), g("attention.wk.weight"),
+                            g("attention.wv.weight"), g("attention.wo.weight"), cfg, cos, sin, stored, scale)
+    n, scale = weighted_rows(h, g("ffn_norm.weight"), cfg["eps"])
+    n = stored(n)
+    gate, up = stored(n @ g("feed_forward.w1.weight").T) * scale, stored(n @ g("feed_forward.w3.weight").T) * scale
     act = stored(torch.nn.functional.silu(gate) * up)           # :604-605
     return h + stored(act @ g("feed_forward.w2.weight").T)
 

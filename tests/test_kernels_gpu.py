@@ -181,6 +181,121 @@ def test_gemm_tcgen05_rows_do_not_depend_on_the_batch(ops):
     torch.testing.assert_close(total(full)[5], total(one)[0], atol=1e-4, rtol=1e-5)
 
 
+# ------------------------------------------------- deferred normalisation and the product into the stream
+
+from torchllms_b200.kernels.lazy import PendingProduct, RowScaled
+
+
+def random_row_scale(T, parts, dim, seed):
+    g = torch.Generator().manual_seed(seed)
+    ssq = (torch.rand((T, parts), generator=g) * dim / parts * 4 + 0.01).cuda()
+    return ssq, dim, 1e-5
+
+
+@pytest.mark.parametrize("n,dim", [(1, 16), (7, 96), (33, 4096), (5, 102), (300, 128)])
+def test_rmsnorm_deferred_leaves_weighted_rows_and_their_sums_of_squares(ops, n, dim):
+    h = rand((n, dim), torch.float32, 2, 3.0)
+    w = 1 + 0.1 * rand((dim,), torch.float32, 4)
+    parts = rand((3, n, dim), torch.float32, 5)
+    for delta in (None, rand((n, dim), torch.bfloat16, 3), parts):
+        h1, h2 = h.clone(), h.clone()
+        got = ops.rmsnorm(h1, delta, w, 1e-5, out_dtype=torch.bfloat16, deferred=True)
+        want = TWIN.rmsnorm(h2, delta, w, 1e-5, out_dtype=torch.bfloat16, deferred=True)
+        assert isinstance(got, RowScaled) and got.x.dtype == torch.bfloat16 and got.ssq.shape == (n, 1) and got.dim == dim
+        torch.testing.assert_close(h1, h2, atol=1e-6, rtol=1e-6)
+        torch.testing.assert_close(got.x.float(), want.x.float(), atol=1e-2, rtol=1e-2)
+        torch.testing.assert_close(got.ssq, want.ssq, atol=1e-3, rtol=1e-5)
+        # resolved, it is the ordinary norm
+        plain = TWIN.rmsnorm(h.clone(), delta, w, 1e-5, out_dtype=torch.float32)
+        torch.testing.assert_close(got.resolve(torch.float32), plain, atol=3e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("M", [1, 8, 16, 17, 40, 64])
+@pytest.mark.parametrize("N,K", [(128, 64), (132, 72), (4096, 4096), (4096, 14336), (300, 8), (1000, 200)])
+def test_product_added_to_the_stream_in_its_own_kernel(ops, M, N, K):
+    """h += bf16(x @ w^T), bf16(h * weight) and the parts of sum(h^2) from one kernel, in which the CTA
+    that finishes a column slab last adds up the K splits: against the twin, against product + norm
+    kernel, twice in a row (the slab counters return to zero), and bit for bit whatever the timing."""
+    x, w = rand((M, K), torch.bfloat16, 60 + M), rand((N, K), torch.bfloat16, 61, K ** -0.5)
+    h0 = rand((M, N), torch.float32, 62, 2.0)
+    nw = 1 + 0.1 * rand((N,), torch.float32, 63)
+    pending = PendingProduct(x, w)
+    assert ops.can_fuse_residual(pending, h0)
+    first = None
+    for _ in range(3):
+        h1, h2, h3 = h0.clone(), h0.clone(), h0.clone()
+        got = ops.linear_residual_norm(pending, h1, nw, 1e-5)
+        ops.check_status()
+        want = TWIN.linear_residual_norm(pending, h2, nw, 1e-5)
+        two = ops.rmsnorm(h3, ops.linear(x, w), nw, 1e-5, out_dtype=torch.bfloat16, deferred=True)   # product, then norm kernel
+        assert got.x.shape == (M, N) and got.ssq.shape == (M, -(-N // 128)) and got.dim == N
+        # the product is rounded to bfloat16 on its way into the stream: where the float32 sums of two
+        # orders fall on different sides of a rounding step, h differs by that step
+        step = 2.0 ** -8 * (x.float() @ w.float().t()).abs().max().item()
+        assert (h1 - h2).abs().max().item() <= step and (h1 - h3).abs().max().item() <= step
+        assert ((h1 - h2).abs() > 1e-6).float().mean().item() < 0.02
+        torch.testing.assert_close(got.x.float(), (h1 * nw).to(torch.bfloat16).float(), atol=0, rtol=0)
+        torch.testing.assert_close(got.ssq.sum(-1), h1.pow(2).sum(-1), atol=1e-3, rtol=1e-5)
+        torch.testing.assert_close(got.scale(), want.scale(), atol=1e-6, rtol=1e-4)
+        torch.testing.assert_close(got.scale(), two.scale(), atol=1e-6, rtol=1e-4)
+        if first is None:
+            first = (h1.clone(), got.x.clone(), got.ssq.clone())
+        else:
+            assert torch.equal(h1, first[0]) and torch.equal(got.x, first[1]) and torch.equal(got.ssq, first[2])
+    assert not ops.can_fuse_residual(PendingProduct(rand((65, K), torch.bfloat16, 1), w), torch.zeros(65, N, device="cuda"))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KV,hd,P,interleaved", [(4, 2, 16, 16, True), (5, 5, 48, 4, False), (32, 8, 128, 16, True)])
+@pytest.mark.parametrize("parts", [1, 32, 5])
+def test_rope_applies_a_deferred_row_scale(ops, dtype, H, KV, hd, P, interleaved, parts):
+    T, n_pages, max_pos = 19, 8, 100
+    row = (H + 2 * KV) * hd
+    pos = torch.randint(0, max_pos, (T,), dtype=torch.int32).cuda()
+    ang = torch.arange(max_pos).float()[:, None] * (1.0 / 100 ** (torch.arange(hd // 2).float() / (hd // 2)))[None, :]
+    table = torch.stack([ang.cos(), ang.sin()], -1).contiguous().cuda()
+    slots = torch.randperm(n_pages * P)[:T].to(torch.int32).cuda()
+    ssq, dim, eps = random_row_scale(T, parts, 256, 7)
+    kw = dict(n_heads=H, n_kv_heads=KV, head_dim=hd, interleaved=interleaved, slot_mapping=slots, page_size=P, out_dtype=dtype)
+    for qkv in (rand((T, row), dtype, 15), rand((4, T, row), torch.float32, 16)):
+        pages = [torch.zeros((n_pages, KV, P, hd), dtype=dtype).cuda() for _ in range(4)]
+        q1 = ops.rope_kv_write(RowScaled(qkv, ssq, dim, eps), pos, table, k_pages=pages[0], v_pages=pages[1], **kw)
+        q2 = TWIN.rope_kv_write(RowScaled(qkv, ssq, dim, eps), pos, table, k_pages=pages[2], v_pages=pages[3], **kw)
+        a = tol(dtype, 2e-5, 2e-2)
+        torch.testing.assert_close(q1.float(), q2.float(), atol=a, rtol=a)
+        torch.testing.assert_close(pages[0].float(), pages[2].float(), atol=a, rtol=a)
+        torch.testing.assert_close(pages[1].float(), pages[3].float(), atol=a, rtol=a)
+        unscaled = ops.rope_kv_write(qkv, pos, table, k_pages=None, v_pages=None, **kw)
+        assert not torch.allclose(unscaled.float(), q1.float(), atol=a)
+
+
+@pytest.mark.parametrize("M,hidden,K", [(1, 64, 64), (8, 192, 264), (16, 14336, 128), (33, 128, 4096), (64, 1024, 520), (9, 83, 40), (200, 256, 128)])
+@pytest.mark.parametrize("parts", [1, 32])
+def test_swiglu_applies_a_deferred_row_scale(ops, M, hidden, K, parts):
+    """Gate and up of rows whose normalisation was deferred: the scale goes on before the activation,
+    in the product's epilogue where there is one, in the SwiGLU kernel else; both against the twin."""
+    torch.manual_seed(M + hidden)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w13 = (torch.randn(2 * hidden, K, device="cuda") * K ** -0.5).to(torch.bfloat16)
+    ssq, dim, eps = random_row_scale(M, parts, K, 9)
+    rs = RowScaled(x, ssq, dim, eps)
+    want = TWIN.linear_swiglu(rs, w13)
+    got = ops.linear_swiglu(rs, w13)
+    ops.check_status()
+    assert got.dtype == torch.bfloat16 and got.shape == (M, hidden)
+    torch.testing.assert_close(got.float(), want.float(), atol=3e-2, rtol=3e-2)
+    can_fuse = M <= 64 and hidden % 64 == 0 and K % 8 == 0
+    if can_fuse:
+        one, two = ops.linear_swiglu(rs, w13, fused=True), ops.linear_swiglu(rs, w13, fused=False)
+        torch.testing.assert_close(one.float(), two.float(), atol=2e-2, rtol=2e-2)
+        torch.testing.assert_close(one.float(), want.float(), atol=3e-2, rtol=3e-2)
+    # and it is the activation of the scaled product, not the scaled activation
+    s = rs.scale()[:, None]
+    gu = (x.float() @ w13.float().t()) * s
+    ref = gu[:, :hidden] / (1 + torch.exp(-gu[:, :hidden])) * gu[:, hidden:]
+    torch.testing.assert_close(got.float(), ref, atol=5e-2, rtol=5e-2)
+
+
 # ------------------------------------------------------------------------------------ rope
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -7,6 +7,7 @@ import pytest
 import torch
 
 import plain_llama
+from torchllms_b200.kernels.lazy import PendingProduct, RowScaled
 from torchllms_b200.cache.manager import RunCacheView
 from torchllms_b200.engine.step import StepContext
 from torchllms_b200.parts import attention, block, ffn, norm, rope  # noqa: F401
@@ -100,6 +101,8 @@ def test_feed_forward_part(dtype):
     f.load(w)
     x = torch.randn(11, 72).to(dtype)
     got = f.forward(x.cuda(), None)
+    assert isinstance(got, PendingProduct)            # the down projection is left to the norm that follows
+    got = got.take(env.ops)
     got = got.sum(0) if got.dim() == 3 else got
     want = plain_llama.swiglu_ffn(x.float(), w["w1.weight"], w["w2.weight"], w["w3.weight"])
     torch.testing.assert_close(got.float().cpu(), want, **tol(dtype))
@@ -132,7 +135,7 @@ def test_attention_mixer_part_in_two_portions(dtype, H, KV, hd, P):
     for start, n in ((0, cut), (cut, S - cut)):
         ctx, table, slots = ctx_for([n], [start], P, n_pages)
         view = RunCacheView(k_pages, v_pages, table, slots, P, True, None)
-        outs.append(m.forward(x[start:start + n].cuda(), ctx, view))
+        outs.append(m.forward(x[start:start + n].cuda(), ctx, view).take(env.ops))    # (a pending output projection)
     got = torch.cat([(o.sum(0) if o.dim() == 3 else o).float() for o in outs]).cpu()
     cfg = {"n_heads": H, "n_kv_heads": KV, "head_dim": hd}
     cos, sin = plain_llama.rope_angles(plain_llama.rope_frequencies(hd, 500.0, None), torch.arange(S))
@@ -167,7 +170,7 @@ def test_prenorm_block_part(dtype):
     view = RunCacheView(k_pages, torch.zeros_like(k_pages), table, slots, P, True, None)
     res = Residual(x.cuda().clone())
     blk.forward(res, ctx, view)
-    delta = res.delta.float()
+    delta = res.delta.take(env.ops).float()
     got = (res.h + (delta.sum(0) if delta.dim() == 3 else delta)).cpu()
     ren = {"mix.": "attention.", "ff.": "feed_forward.", "n1.": "attention_norm.", "n2.": "ffn_norm."}
     pw = {}
@@ -180,6 +183,36 @@ def test_prenorm_block_part(dtype):
     stored = plain_llama._same if dtype == torch.float32 else plain_llama.to_bfloat16_and_back
     want = plain_llama.block(x, pw, "L", cfg, cos, sin, stored)
     torch.testing.assert_close(got, want, **tol(dtype))
+
+
+def test_norm_part_defers_its_scale_and_folds_a_pending_product_into_the_stream():
+    """In bfloat16, for a reader that takes row-scaled input: the rows leave weighted, the scale beside
+    them; a pending product is added to the stream by its own kernel when it has few rows, by product
+    and norm kernel otherwise, with the same result."""
+    dim, K = 256, 136
+    env = env_for(dim, torch.bfloat16)
+    n = NORMS.build(part("rmsnorm", dim=dim, eps=1e-5), env)
+    w = 1 + 0.2 * torch.randn(dim)
+    n.load({"weight": w})
+    for rows in (9, 100):
+        h = torch.randn(rows, dim, device="cuda") * 2
+        x = torch.randn(rows, K, device="cuda").to(torch.bfloat16)
+        wo = (torch.randn(dim, K, device="cuda") * 0.1).to(torch.bfloat16)
+        product = (x.float() @ wo.float().t()).to(torch.bfloat16).float()
+        res = Residual(h.clone(), PendingProduct(x, wo))
+        got = n.forward(res, deferred_ok=True)
+        assert isinstance(got, RowScaled) and res.delta is None and got.ssq.shape[1] == (2 if rows <= 64 else 1)
+        assert (res.h - (h + product)).abs().max().item() <= 2.0 ** -7 * product.abs().max().item()
+        want = plain_llama.rms_norm(res.h.cpu(), w, 1e-5)
+        torch.testing.assert_close(got.resolve(torch.float32).cpu(), want, atol=3e-2, rtol=2e-2)
+        plain_way = n.forward(Residual(h.clone(), PendingProduct(x, wo)))      # not deferred: the ordinary norm
+        assert isinstance(plain_way, torch.Tensor)
+        torch.testing.assert_close(plain_way.float().cpu(), want, atol=3e-2, rtol=2e-2)
+    env32 = env_for(dim, torch.float32)
+    n32 = NORMS.build(part("rmsnorm", dim=dim, eps=1e-5), env32)
+    n32.load({"weight": w})
+    out = n32.forward(Residual(torch.randn(4, dim, device="cuda")), deferred_ok=True)
+    assert isinstance(out, torch.Tensor)                  # 32-bit mode keeps the reference's order
 
 
 def test_unknown_kinds_are_named():

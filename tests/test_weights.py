@@ -200,3 +200,32 @@ def test_random_weights_command_line_writes_a_loadable_folder(tmp_path):
     assert outs[0] == outs[1] and outs[0] != outs[2]            # the seed decides, and nothing else
     _, config, model = load_model(tmp_path / "a", dtype="float32", device="cpu", ops=TorchOps())
     assert config.n_layers == TINY_B["num_hidden_layers"] and config.vocab_size == TINY_B["vocab_size"]
+
+
+def test_the_references_own_checkpoint_folder_loads(tmp_path):
+    """``params.json`` beside ``consolidated.00.pth`` (what the reference's converter writes and its
+    loader reads, torchllms/models/utils.py:42-43, :107-111): same model as the safetensors folder,
+    same strict check."""
+    cfg, seed, _ = TINY["A"]
+    t = make_tensors(cfg, seed)
+    native = load(write_model_folder(tmp_path / "st", cfg, t))[2]
+    folder = tmp_path / "pth"
+    folder.mkdir()
+    (folder / "params.json").write_text(json.dumps({
+        "dim": 64, "n_layers": 2, "n_heads": 4, "n_kv_heads": 2, "head_dim": 16, "vocab_size": 512, "multiple_of": 192,
+        "ffn_dim_multiplier": 3.0 - 1e-9, "norm_eps": 1e-5, "rope_theta": 10000.0, "max_seq_len": 128}))
+    torch.save({k: v.to(torch.bfloat16) for k, v in t.items()}, str(folder / "consolidated.00.pth"))
+    for path in (folder, folder / "consolidated.00.pth"):
+        got = load(path)[2]
+        for a, b in zip(native.blocks, got.blocks):
+            assert torch.equal(a.mixer.wqkv.to(torch.bfloat16), b.mixer.wqkv.to(torch.bfloat16))
+        assert torch.equal(native.head.to(torch.bfloat16), got.head.to(torch.bfloat16))
+    broken = dict(t)
+    del broken["norm.weight"]
+    torch.save(broken, str(folder / "consolidated.00.pth"))
+    with pytest.raises(WeightError) as e:
+        load(folder)
+    assert e.value.missing == ["norm.weight"]
+    (folder / "consolidated.00.pth").write_bytes(b"not a checkpoint")
+    with pytest.raises(Exception, match="not a checkpoint"):
+        load(folder)

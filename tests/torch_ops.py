@@ -14,6 +14,8 @@ from typing import Optional
 import numpy as np
 import torch
 
+from torchllms_b200.kernels.lazy import PendingProduct, RowScaled      # two value types, no kernels
+
 MASK64 = (1 << 64) - 1
 
 
@@ -58,7 +60,9 @@ class TorchOps:
     def embed(self, token_ids, table):
         return table[token_ids.long()].float()
 
-    def rmsnorm(self, h, delta, weight, eps, out_dtype, rows=None):
+    def rmsnorm(self, h, delta, weight, eps, out_dtype, rows=None, deferred=False):
+        if isinstance(delta, PendingProduct):
+            delta = delta.take(self)
         if delta is not None and delta.dim() == 3:
             delta = delta.float().sum(0)
         x = h if delta is None else h + delta.float()
@@ -67,21 +71,48 @@ class TorchOps:
                 h.copy_(x)
         else:
             x = x[rows.long()]
+        if deferred:
+            assert rows is None
+            return RowScaled((x * weight).to(out_dtype), x.pow(2).sum(-1, keepdim=True), x.shape[1], float(eps))
         y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight
         return y.to(out_dtype)
 
+    fuse_residual = True      # tests switch it off to compare the two ways
+
+    def can_fuse_residual(self, pending, h):
+        return (self.fuse_residual and isinstance(pending, PendingProduct) and pending.x.dtype == torch.bfloat16
+                and pending.x.shape[0] <= 64 and pending.w.shape[0] % 4 == 0 and pending.x.shape[1] % 8 == 0)
+
+    def linear_residual_norm(self, pending, h, weight, eps, slab=128):
+        """h += bf16(x @ w.T) (float32, in place); rows bf16(h * weight) and the sum of squares in parts
+        of ``slab`` columns, as the kernel leaves them."""
+        h += (pending.x.float() @ pending.w.float().t()).to(torch.bfloat16).float()
+        N = h.shape[1]
+        parts = [h[:, c:c + slab].pow(2).sum(-1) for c in range(0, N, slab)]
+        return RowScaled((h * weight).to(torch.bfloat16), torch.stack(parts, 1), N, float(eps))
+
     def swiglu(self, gate_up, out_dtype=None):
+        scale = None
+        if isinstance(gate_up, RowScaled):
+            scale, gate_up = gate_up.scale(), gate_up.x
         out_dtype = out_dtype or gate_up.dtype
         if gate_up.dim() == 3:
             gate_up = gate_up.float().sum(0)
         hidden = gate_up.shape[1] // 2
         g, u = gate_up[:, :hidden].float(), gate_up[:, hidden:].float()
+        if scale is not None:
+            g, u = g * scale[:, None], u * scale[:, None]
         return (g / (1 + torch.exp(-g)) * u).to(out_dtype)
 
     def linear_swiglu(self, x, w13, fused=None):
+        if isinstance(x, RowScaled):
+            # gate and up pass through the activation dtype unscaled, as between the product and its epilogue
+            return self.swiglu(x.follow(self.linear(x.x, w13)), out_dtype=x.x.dtype)
         return self.swiglu(self.linear(x, w13), out_dtype=x.dtype)
 
     def linear(self, x, w, out_dtype=None, partials_ok=False):
+        if isinstance(x, RowScaled):
+            return x.follow(self.linear(x.x, w, out_dtype, partials_ok))
         out_dtype = out_dtype or x.dtype
         if x.dtype == torch.float32:
             return (x @ w.t()).to(out_dtype)
@@ -92,11 +123,16 @@ class TorchOps:
 
     def rope_kv_write(self, qkv, positions, table, *, n_heads, n_kv_heads, head_dim, interleaved,
                       k_pages, v_pages, slot_mapping, page_size, out_dtype=None):
+        scale = None
+        if isinstance(qkv, RowScaled):
+            scale, qkv = qkv.scale(), qkv.x
         out_dtype = out_dtype or qkv.dtype
         if qkv.dim() == 3:
             qkv = qkv.float().sum(0)
         T = qkv.shape[0]
         x = qkv.float().view(T, n_heads + 2 * n_kv_heads, head_dim)
+        if scale is not None:
+            x = x * scale[:, None, None]
         cs = table[positions.long()]            # [T, hd/2, 2]
         c, s = cs[:, None, :, 0], cs[:, None, :, 1]
         rot = x[:, : n_heads + n_kv_heads]

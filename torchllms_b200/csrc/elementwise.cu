@@ -4,9 +4,26 @@
 // rmsnorm:  x = h[row] (+ delta[row]);  y = x * rsqrt(mean(x^2) + eps) * w   -- all in float32,
 //           rounded once to the output dtype; with `write_back` the sum x replaces h[row].
 //           The reference normalises in float32 too (torchllms/models/networks.py:195-200).
+//           Deferred form: y = x * w without the rsqrt, and ssq_out[row] = sum(x^2): the kernels that
+//           consume the product of y with a weight matrix apply rsqrt(ssq / dim + eps) to the product's
+//           rows instead (a matrix product is linear in its input, so the scale commutes with it).
 // swiglu:   out[t, f] = silu(in[t, f]) * in[t, F + f],  silu(g) = g / (1 + exp(-g)), in float32
-//           (torchllms/models/networks.py:604-605).
+//           (torchllms/models/networks.py:604-605).  With a row scale (see above) gate and up are
+//           multiplied by it first.
 #include "common.cuh"
+
+// One scale per row whose normalisation was deferred: rsqrt(sum_p ssq[row, p] * inv_dim + eps); 1 without ssq.
+struct RowScale {
+    const float* ssq;
+    int parts;
+    float inv_dim, eps;
+};
+__device__ __forceinline__ float row_scale(const RowScale& rs, long long row) {
+    if (rs.ssq == nullptr) return 1.f;
+    float v = 0.f;
+    for (int q = 0; q < rs.parts; ++q) v += __ldg(rs.ssq + row * rs.parts + q);
+    return rsqrtf(v * rs.inv_dim + rs.eps);
+}
 
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
@@ -64,7 +81,8 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
 template <typename TD, typename TO, int VEC>
 __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta, int splits, long long plane,
                                const float* __restrict__ weight, TO* __restrict__ out,
-                               const int* __restrict__ rows, int dim, float eps, int write_back) {
+                               const int* __restrict__ rows, int dim, float eps, int write_back,
+                               float* __restrict__ ssq_out) {
     extern __shared__ __align__(16) float row_buf[];  // the summed row, kept for the second pass
     __shared__ float warp_part[32];
     grid_launch_dependents();
@@ -113,7 +131,9 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
         if (lane == 0) warp_part[0] = v;
     }
     __syncthreads();
-    const float rstd = rsqrtf(warp_part[0] / (float)dim + eps);
+    // deferred form: the rows leave weighted but not normalised, with their sum of squares beside them
+    const float rstd = ssq_out ? 1.f : rsqrtf(warp_part[0] / (float)dim + eps);
+    if (ssq_out && threadIdx.x == 0) ssq_out[o] = warp_part[0];
     TO* orow = out + (size_t)o * dim;
     if (VEC == 4) {
         for (int d = threadIdx.x * 4; d < dim; d += blockDim.x * 4) {   // each thread re-reads what it wrote
@@ -135,13 +155,14 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
 // VEC = 4: hidden is a multiple of 4 and rows are 16-byte aligned: four gates and four ups per thread.
 template <typename TI, typename T, int VEC>
 __global__ void swiglu_kernel(const TI* __restrict__ in, int splits, long long plane, T* __restrict__ out,
-                              int hidden, int n_tokens) {
+                              int hidden, int n_tokens, const RowScale rs) {
     grid_launch_dependents();
     grid_dependency_wait();
     const int per_row = hidden / VEC;
     for (int t = blockIdx.y; t < n_tokens; t += gridDim.y) {
         const TI* row = in + (size_t)t * 2 * hidden;
         T* orow = out + (size_t)t * hidden;
+        const float sc = row_scale(rs, t);
         for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < per_row; c += gridDim.x * blockDim.x) {
             const int f = c * VEC;
             if (VEC == 4) {
@@ -151,6 +172,8 @@ __global__ void swiglu_kernel(const TI* __restrict__ in, int splits, long long p
                     g.x += g2.x; g.y += g2.y; g.z += g2.z; g.w += g2.w;
                     u.x += u2.x; u.y += u2.y; u.z += u2.z; u.w += u2.w;
                 }
+                g.x *= sc; g.y *= sc; g.z *= sc; g.w *= sc;
+                u.x *= sc; u.y *= sc; u.z *= sc; u.w *= sc;
                 store4(orow + f, make_float4(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y,
                                              g.z / (1.f + expf(-g.z)) * u.z, g.w / (1.f + expf(-g.w)) * u.w));
             } else {
@@ -159,6 +182,8 @@ __global__ void swiglu_kernel(const TI* __restrict__ in, int splits, long long p
                     g += to_float(row[sp * plane + f]);
                     u += to_float(row[sp * plane + hidden + f]);
                 }
+                g *= sc;
+                u *= sc;
                 orow[f] = from_float<T>(g / (1.f + expf(-g)) * u);
             }
         }
@@ -186,7 +211,7 @@ extern "C" int tl_embed(const int* ids, const void* table, int table_dtype, floa
 
 template <typename TD, typename TO>
 static int launch_rmsnorm(float* h, const void* delta, int splits, long long plane, const float* w, void* out,
-                          const int* rows, int n_out, int dim, float eps, int write_back, cudaStream_t s) {
+                          const int* rows, int n_out, int dim, float eps, int write_back, float* ssq_out, cudaStream_t s) {
     const size_t smem = (size_t)dim * sizeof(float);
     if (smem > 200 * 1024) return TL_TOO_LARGE;
     const bool vec = dim % 4 == 0 && plane % 4 == 0 && aligned16(h) && aligned16(w) && aligned16(out) &&
@@ -201,25 +226,27 @@ static int launch_rmsnorm(float* h, const void* delta, int splits, long long pla
     threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
     if (n_out >= 512 && threads > 256) threads = 256;   // many rows: smaller CTAs, more of them resident
     return (int)tl_launch(kern, dim3(n_out), dim3(threads), smem, s, h, (const TD*)delta, splits, plane, w, (TO*)out, rows,
-                          dim, eps, write_back);
+                          dim, eps, write_back, ssq_out);
 }
 
 // delta may be null (then nothing is added); it may hold `delta_splits` planes of [rows of h, dim],
 // `delta_plane` elements apart, which are summed.  rows may be null (then row o is row o of h).
+// ssq_out may be null; else [n_out] floats receive the rows' sums of squares and the rows are
+// written weighted but not normalised (the deferred form).
 extern "C" int tl_rmsnorm(float* h, const void* delta, int delta_dtype, int delta_splits, long long delta_plane,
                           const float* weight, void* out, int out_dtype, const int* rows, int n_out, int dim,
-                          float eps, int write_back, void* stream) {
+                          float eps, int write_back, float* ssq_out, void* stream) {
     if (n_out <= 0) return TL_OK;
     if (dim <= 0 || delta_splits < 1) return TL_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (delta_dtype == TL_F32 && out_dtype == TL_F32)
-        return launch_rmsnorm<float, float>(h, delta, delta_splits, delta_plane, weight, out, rows, n_out, dim, eps, write_back, s);
+        return launch_rmsnorm<float, float>(h, delta, delta_splits, delta_plane, weight, out, rows, n_out, dim, eps, write_back, ssq_out, s);
     if (delta_dtype == TL_BF16 && out_dtype == TL_BF16)
-        return launch_rmsnorm<__nv_bfloat16, __nv_bfloat16>(h, delta, delta_splits, delta_plane, weight, out, rows, n_out, dim, eps, write_back, s);
+        return launch_rmsnorm<__nv_bfloat16, __nv_bfloat16>(h, delta, delta_splits, delta_plane, weight, out, rows, n_out, dim, eps, write_back, ssq_out, s);
     if (delta_dtype == TL_F32 && out_dtype == TL_BF16)
-        return launch_rmsnorm<float, __nv_bfloat16>(h, delta, delta_splits, delta_plane, weight, out, rows, n_out, dim, eps, write_back, s);
+        return launch_rmsnorm<float, __nv_bfloat16>(h, delta, delta_splits, delta_plane, weight, out, rows, n_out, dim, eps, write_back, ssq_out, s);
     if (delta_dtype == TL_BF16 && out_dtype == TL_F32)
-        return launch_rmsnorm<__nv_bfloat16, float>(h, delta, delta_splits, delta_plane, weight, out, rows, n_out, dim, eps, write_back, s);
+        return launch_rmsnorm<__nv_bfloat16, float>(h, delta, delta_splits, delta_plane, weight, out, rows, n_out, dim, eps, write_back, ssq_out, s);
     return TL_BAD_DTYPE;
 }
 
@@ -230,13 +257,14 @@ __device__ __forceinline__ float silu_mul_fast(float g, float u) { return __fdiv
 
 // bfloat16 in and out, hidden a multiple of 8, one plane: eight gates and eight ups per thread (16-byte accesses)
 __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
-                                     int hidden, long long n_chunks) {
+                                     int hidden, long long n_chunks, const RowScale rs) {
     grid_launch_dependents();
     grid_dependency_wait();
     const int per_row = hidden >> 3;
     for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < n_chunks; c += (long long)gridDim.x * blockDim.x) {
         const long long t = c / per_row;
         const int f = (int)(c - t * per_row) << 3;
+        const float sc = row_scale(rs, t);
         const uint4 graw = *reinterpret_cast<const uint4*>(in + t * 2 * hidden + f);
         const uint4 uraw = *reinterpret_cast<const uint4*>(in + t * 2 * hidden + hidden + f);
         const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
@@ -246,14 +274,14 @@ __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __nv_
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float2 g = __bfloat1622float2(g2[i]), u = __bfloat1622float2(u2[i]);
-            o2[i] = __floats2bfloat162_rn(silu_mul_fast(g.x, u.x), silu_mul_fast(g.y, u.y));
+            o2[i] = __floats2bfloat162_rn(silu_mul_fast(g.x * sc, u.x * sc), silu_mul_fast(g.y * sc, u.y * sc));
         }
         *reinterpret_cast<uint4*>(out + t * hidden + f) = oraw;
     }
 }
 
 template <typename TI, typename T>
-static int launch_swiglu(const void* in, int splits, void* out, int n_tokens, int hidden, cudaStream_t s) {
+static int launch_swiglu(const void* in, int splits, void* out, int n_tokens, int hidden, const RowScale& rs, cudaStream_t s) {
     const long long plane = 2LL * n_tokens * hidden;
     const bool vec = hidden % 4 == 0 && aligned16(in) && aligned16(out) && sizeof(T) * hidden % 8 == 0;
     const int per_row = vec ? hidden / 4 : hidden;
@@ -263,27 +291,30 @@ static int launch_swiglu(const void* in, int splits, void* out, int n_tokens, in
     int by = n_tokens < 4096 ? n_tokens : 4096;
     const dim3 grid(bx, by), block(threads);
     if (vec)
-        return (int)tl_launch(swiglu_kernel<TI, T, 4>, grid, block, 0, s, (const TI*)in, splits, plane, (T*)out, hidden, n_tokens);
-    return (int)tl_launch(swiglu_kernel<TI, T, 1>, grid, block, 0, s, (const TI*)in, splits, plane, (T*)out, hidden, n_tokens);
+        return (int)tl_launch(swiglu_kernel<TI, T, 4>, grid, block, 0, s, (const TI*)in, splits, plane, (T*)out, hidden, n_tokens, rs);
+    return (int)tl_launch(swiglu_kernel<TI, T, 1>, grid, block, 0, s, (const TI*)in, splits, plane, (T*)out, hidden, n_tokens, rs);
 }
 
-// in: [splits, n_tokens, 2 * hidden] of in_dtype (splits > 1 only for float32 partial sums); out: [n_tokens, hidden]
+// in: [splits, n_tokens, 2 * hidden] of in_dtype (splits > 1 only for float32 partial sums); out: [n_tokens, hidden].
+// in_ssq may be null; else [n_tokens, in_parts] floats: gate and up of a token are multiplied by
+// rsqrt(sum_p in_ssq[token, p] * in_inv_dim + in_eps) before the activation.
 extern "C" int tl_swiglu(const void* in, int in_dtype, int splits, void* out, int dtype, int n_tokens, int hidden,
-                         void* stream) {
+                         const float* in_ssq, int in_parts, float in_inv_dim, float in_eps, void* stream) {
     if ((long long)n_tokens * hidden <= 0) return TL_OK;
-    if (splits < 1) return TL_BAD_SIZE;
+    if (splits < 1 || (in_ssq != nullptr && in_parts < 1)) return TL_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    if (in_dtype == TL_F32 && dtype == TL_F32) return launch_swiglu<float, float>(in, splits, out, n_tokens, hidden, s);
+    const RowScale rs = {in_ssq, in_parts, in_inv_dim, in_eps};
+    if (in_dtype == TL_F32 && dtype == TL_F32) return launch_swiglu<float, float>(in, splits, out, n_tokens, hidden, rs, s);
     if (in_dtype == TL_BF16 && dtype == TL_BF16) {
         if (splits == 1 && hidden % 8 == 0 && aligned16(in) && aligned16(out)) {
             const long long n_chunks = (long long)n_tokens * (hidden / 8);
             long long blocks = (n_chunks + 255) / 256;
             if (blocks > 148 * 16) blocks = 148 * 16;
             return (int)tl_launch(swiglu_bf16x8_kernel, dim3((unsigned)blocks), dim3(256), 0, s, (const __nv_bfloat16*)in,
-                                  (__nv_bfloat16*)out, hidden, n_chunks);
+                                  (__nv_bfloat16*)out, hidden, n_chunks, rs);
         }
-        return launch_swiglu<__nv_bfloat16, __nv_bfloat16>(in, splits, out, n_tokens, hidden, s);
+        return launch_swiglu<__nv_bfloat16, __nv_bfloat16>(in, splits, out, n_tokens, hidden, rs, s);
     }
-    if (in_dtype == TL_F32 && dtype == TL_BF16) return launch_swiglu<float, __nv_bfloat16>(in, splits, out, n_tokens, hidden, s);
+    if (in_dtype == TL_F32 && dtype == TL_BF16) return launch_swiglu<float, __nv_bfloat16>(in, splits, out, n_tokens, hidden, rs, s);
     return TL_BAD_DTYPE;
 }

@@ -19,6 +19,21 @@
 //   warps 2-5        : epilogue - tcgen05.ld of their 32 TMEM lanes, convert, coalesced stores
 // Every mbarrier wait is bounded: on a time-out the CTA records a code in the status word, drains,
 // frees its TMEM and returns.
+//
+// Three forms of the epilogue:
+//   plain     partial sums (or, with one split, the product itself) as described above;
+//   gated     SwiGLU of a stacked gate/up weight (below);
+//   residual  the product is added to the float32 residual stream and prepared for the RMS norm that
+//             follows (TransformerBlock, torchllms/models/networks.py:635-644: h = x + attn(..),
+//             then ffn_norm(h)): the splits still write partial sums, count themselves off on a
+//             counter of their slab, and whichever CTA of a slab arrives last adds the slab's
+//             partial sums in the order of the splits (so the result does not depend on who was
+//             last), rounds the sum to bfloat16 as a product that passes through memory is, adds it
+//             to h, and writes h, the weighted but not yet normalised activations
+//             bf16(h * norm_weight), and the slab's share of sum(h^2) per token.  The kernels that
+//             consume the next product (rotary encoding, the gated epilogue here) multiply by
+//             rsqrt(sum / dim + eps): a product is linear in its input, so the scale may follow it.
+//             No separate norm kernel runs and the sum never makes a round trip as a kernel of its own.
 #include "common.cuh"
 #include <cuda.h>
 
@@ -134,12 +149,26 @@ struct GemmParams {
     int k_blocks_per_split; // stages each split walks
     int out_is_f32;
     int hidden;             // gated form: W is [2 * hidden, K], gate rows above up rows; out is [M, hidden] bfloat16
+    // gated form, optional: the input rows were not normalised yet; gate and up are multiplied by
+    // rsqrt(sum_p in_ssq[tok, p] * in_inv_dim + in_eps) before the activation
+    const float* in_ssq;
+    int in_parts;
+    float in_inv_dim, in_eps;
+    // residual form
+    int splits;
+    int* counters;          // [slabs], zero between launches
+    float* h;               // [M, N] residual stream, updated in place
+    const float* norm_w;    // [N]
+    __nv_bfloat16* xw;      // [M, N]: bf16(h * norm_w)
+    float* ssq;             // [M, slabs]: this slab's share of sum(h^2)
 };
+
+enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_RESID = 2 };
 
 // GATED: the slab is 64 rows of the gate projection and the 64 matching rows of the up projection
 // (two TMA boxes per stage), and the epilogue writes silu(gate) * up in bfloat16: the SwiGLU costs
 // no kernel and no round trip of the projections through memory.  One K split only.
-template <int BQ, int STAGES, bool GATED>
+template <int BQ, int STAGES, int MODE>
 __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_a,
                                                                 const GemmParams p) {
@@ -154,6 +183,9 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
     __shared__ __align__(8) unsigned long long accum_bar;
     __shared__ unsigned tmem_base_slot;
     __shared__ int abort_flag;
+    __shared__ int last_flag;
+    __shared__ float rstd_s[BQ];
+    constexpr bool GATED = MODE == MODE_GATED;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slab = blockIdx.x, split = blockIdx.y;
@@ -242,6 +274,21 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
         const int quarter = warp & 3;
         const int w_row = slab * BP + quarter * 32 + lane;
         bool ok = true;
+        if (GATED) {
+            // the scale of every token's row, while the products run
+            if (p.in_ssq != nullptr) {
+                grid_dependency_wait();
+                for (int tok = quarter; tok < BQ; tok += 4) {
+                    float v = 0.f;
+                    if (tok < p.M)
+                        for (int q = lane; q < p.in_parts; q += 32) v += __ldcg(p.in_ssq + (size_t)tok * p.in_parts + q);
+                    v = warp_sum(v);
+                    if (lane == 0) rstd_s[tok] = rsqrtf(v * p.in_inv_dim + p.in_eps);
+                }
+            } else {
+                for (int tok = quarter * 32 + lane; tok < BQ; tok += 128) rstd_s[tok] = 1.f;
+            }
+        }
         if (n_kb > 0) {
             ok = mbar_wait(&accum_bar, 0, aborted);
             if (!ok && lane == 0) {
@@ -287,8 +334,9 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
                             if (tok < p.M) {
                                 // (rounded to bfloat16 first, as they are when they pass through memory:
                                 // this form and the two-kernel form give the same numbers)
-                                const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j])));
-                                const float u = __bfloat162float(__float2bfloat16_rn(n_kb > 0 ? xch[row * (BQ + 1) + tok] : 0.f));
+                                const float sc = rstd_s[tok];
+                                const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j]))) * sc;
+                                const float u = __bfloat162float(__float2bfloat16_rn(n_kb > 0 ? xch[row * (BQ + 1) + tok] : 0.f)) * sc;
                                 reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)tok * p.hidden + f] =
                                     __float2bfloat16_rn(__fdividef(g, 1.f + __expf(-g)) * u);
                             }
@@ -319,6 +367,71 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
                             else reinterpret_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(v);
                         }
                     }
+                }
+            }
+        }
+        if (MODE == MODE_RESID) {
+            // Count this CTA off on its slab's counter; the CTA that arrives last finds every split's
+            // partial sums in memory (each wrote, fenced, then counted).  All four warps keep the two
+            // appointments at the barrier whether their waits held or not; a CTA that failed does not
+            // count itself off, so nobody adds up what is not there (the status word says so).
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (quarter == 0 && lane == 0) {
+                int last = 0;
+                if (!abort_flag) {
+                    last = atomicAdd(p.counters + slab, 1) == p.splits - 1 ? 1 : 0;
+                    if (last) p.counters[slab] = 0;          // ready for the next launch
+                }
+                last_flag = last;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (last_flag) {
+                __threadfence();
+                const size_t plane = (size_t)p.M * p.N;
+                const int col = slab * BP + 4 * lane;        // a lane takes four columns, a warp the slab's 128
+                const bool in_range = col < p.N;             // N is a multiple of 4: all four or none
+                float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (in_range) w = *reinterpret_cast<const float4*>(p.norm_w + col);
+                const float* parts = reinterpret_cast<const float*>(p.out);
+                for (int tok = quarter; tok < p.M; tok += 4) {
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    float4 hv = acc;
+                    if (in_range) {
+                        const float* src = parts + (size_t)tok * p.N + col;
+                        hv = *reinterpret_cast<const float4*>(p.h + (size_t)tok * p.N + col);
+                        int sp = 0;
+                        for (; sp + 4 <= p.splits; sp += 4) {           // four loads in flight, added in order
+                            const float4 a = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * plane));
+                            const float4 b = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + 1) * plane));
+                            const float4 c = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + 2) * plane));
+                            const float4 d = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + 3) * plane));
+                            acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+                            acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+                            acc.x += c.x; acc.y += c.y; acc.z += c.z; acc.w += c.w;
+                            acc.x += d.x; acc.y += d.y; acc.z += d.z; acc.w += d.w;
+                        }
+                        for (; sp < p.splits; ++sp) {
+                            const float4 a = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * plane));
+                            acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+                        }
+                        // the product enters the stream as it does when it passes through memory in
+                        // bfloat16 (prompt portions, whose products the library takes): one arithmetic
+                        // however a request is cut into steps
+                        hv.x += __bfloat162float(__float2bfloat16_rn(acc.x));
+                        hv.y += __bfloat162float(__float2bfloat16_rn(acc.y));
+                        hv.z += __bfloat162float(__float2bfloat16_rn(acc.z));
+                        hv.w += __bfloat162float(__float2bfloat16_rn(acc.w));
+                        *reinterpret_cast<float4*>(p.h + (size_t)tok * p.N + col) = hv;
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(hv.x * w.x, hv.y * w.y);
+                        __nv_bfloat162 hi = __floats2bfloat162_rn(hv.z * w.z, hv.w * w.w);
+                        uint2 raw;
+                        raw.x = *reinterpret_cast<unsigned*>(&lo);
+                        raw.y = *reinterpret_cast<unsigned*>(&hi);
+                        *reinterpret_cast<uint2*>(p.xw + (size_t)tok * p.N + col) = raw;
+                    }
+                    const float ss = warp_sum(hv.x * hv.x + hv.y * hv.y + hv.z * hv.z + hv.w * hv.w);
+                    if (lane == 0) p.ssq[(size_t)tok * gridDim.x + slab] = ss;
                 }
             }
         }
@@ -364,11 +477,11 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, in
     return rc == CUDA_SUCCESS ? TL_OK : TL_BAD_SIZE;
 }
 
-template <int BQ, int STAGES, bool GATED = false>
+template <int BQ, int STAGES, int MODE = MODE_PLAIN>
 int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, int slabs, int splits, cudaStream_t s) {
     constexpr size_t smem = (size_t)STAGES * (BP * BK * 2 + BQ * BK * 2) + 1024;
-    static_assert(!GATED || (size_t)64 * (BQ + 1) * 4 <= (size_t)STAGES * (BP * BK * 2 + BQ * BK * 2), "the ups pass through the stages' memory");
-    auto kern = gemm_tcgen05_kernel<BQ, STAGES, GATED>;
+    static_assert(MODE != MODE_GATED || (size_t)64 * (BQ + 1) * 4 <= (size_t)STAGES * (BP * BK * 2 + BQ * BK * 2), "the ups pass through the stages' memory");
+    auto kern = gemm_tcgen05_kernel<BQ, STAGES, MODE>;
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -429,15 +542,58 @@ extern "C" int tl_gemm_tcgen05(const void* A, const void* W, void* out, int out_
     if (rc != TL_OK) return rc;
     rc = make_map(&ma, A, M, K, bq);
     if (rc != TL_OK) return rc;
-    GemmParams p;
+    GemmParams p = {};
     p.out = out; p.status = status; p.M = M; p.N = N; p.K = K;
     p.k_blocks_per_split = (k_blocks + splits - 1) / splits;
     p.out_is_f32 = out_is_f32;
     p.hidden = 0;
+    p.splits = splits;
     cudaStream_t s = (cudaStream_t)stream;
     if (bq == 16) return launch<16, 6>(mw, ma, p, slabs, splits, s);
     if (bq == 32) return launch<32, 5>(mw, ma, p, slabs, splits, s);
     return launch<64, 4>(mw, ma, p, slabs, splits, s);
+}
+
+// How many 128-row slabs of W the kernels cut N into (the width of the residual form's `ssq` and `counters`).
+extern "C" int tl_gemm_tcgen05_slabs(int N) { return (N + BP - 1) / BP; }
+
+// 1 if the residual form takes this problem: what tl_gemm_tcgen05 takes, and N a multiple of 4
+// (the CTA that finishes a slab reads and writes four columns at a time).
+extern "C" int tl_gemm_tcgen05_residual_supports(int M, int N, int K) {
+    return (tl_gemm_tcgen05_supports(M, N, K) && N % 4 == 0) ? 1 : 0;
+}
+
+// h[M, N] += A[M, K] . W[N, K]^T (float32, in place); xw[M, N] = bf16(h * norm_w);
+// ssq[M, slabs] = every slab's share of sum over the row of h^2.  partial: [splits, M, N] float32 scratch
+// with splits = tl_gemm_tcgen05_splits(M, N, K); counters: [slabs] ints, zero before the first launch
+// (every launch leaves them zero).  Launches that share `counters` must not overlap on the device.
+extern "C" int tl_gemm_tcgen05_residual(const void* A, const void* W, float* partial, int* counters, float* h,
+                                        const float* norm_w, void* xw, float* ssq, int M, int N, int K, int splits,
+                                        int* status, void* stream) {
+    if (M <= 0 || N <= 0) return TL_OK;
+    if (!tl_gemm_tcgen05_residual_supports(M, N, K)) return TL_BAD_SIZE;
+    if (!aligned16(A) || !aligned16(W) || !aligned16(partial) || !aligned16(h) || !aligned16(norm_w) || !aligned16(xw) ||
+        status == nullptr || counters == nullptr || ssq == nullptr)
+        return TL_BAD_ALIGN;
+    if (splits != tl_gemm_tcgen05_splits(M, N, K)) return TL_BAD_SIZE;
+    const int slabs = (N + BP - 1) / BP;
+    const int k_blocks = (K + BK - 1) / BK;
+    const int bq = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    CUtensorMap mw, ma;
+    int rc = make_map(&mw, W, N, K, BP);
+    if (rc != TL_OK) return rc;
+    rc = make_map(&ma, A, M, K, bq);
+    if (rc != TL_OK) return rc;
+    GemmParams p = {};
+    p.out = partial; p.status = status; p.M = M; p.N = N; p.K = K;
+    p.k_blocks_per_split = (k_blocks + splits - 1) / splits;
+    p.out_is_f32 = 1;
+    p.splits = splits;
+    p.counters = counters; p.h = h; p.norm_w = norm_w; p.xw = (__nv_bfloat16*)xw; p.ssq = ssq;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (bq == 16) return launch<16, 6, MODE_RESID>(mw, ma, p, slabs, splits, s);
+    if (bq == 32) return launch<32, 5, MODE_RESID>(mw, ma, p, slabs, splits, s);
+    return launch<64, 4, MODE_RESID>(mw, ma, p, slabs, splits, s);
 }
 
 // 1 if the gated form takes this problem (W is [2 * hidden, K]) and is the better choice: what
@@ -449,10 +605,13 @@ extern "C" int tl_gemm_tcgen05_gated_supports(int M, int hidden, int K) {
     return tl_gemm_tcgen05_splits(M, 2 * hidden, K) == 1 ? 1 : 0;
 }
 
-// out[M, hidden] (bfloat16) = silu(A . W[:hidden]^T) * (A . W[hidden:]^T), A: [M, K] bf16, W: [2 * hidden, K] bf16.
+// out[M, hidden] (bfloat16) = silu(s . A . W[:hidden]^T) * (s . A . W[hidden:]^T), A: [M, K] bf16, W: [2 * hidden, K] bf16.
+// s is one scale per row of A: 1 when in_ssq is null, else rsqrt(sum_p in_ssq[row, p] * in_inv_dim + in_eps)
+// (rows that were weighted for an RMS norm but not normalised yet).
 // Any hidden that is a multiple of 64 is computed correctly; tl_gemm_tcgen05_gated_supports says when
 // it is also the faster way.
-extern "C" int tl_gemm_tcgen05_gated(const void* A, const void* W, void* out, int M, int hidden, int K, int* status,
+extern "C" int tl_gemm_tcgen05_gated(const void* A, const void* W, void* out, int M, int hidden, int K,
+                                     const float* in_ssq, int in_parts, float in_inv_dim, float in_eps, int* status,
                                      void* stream) {
     if (M <= 0 || hidden <= 0) return TL_OK;
     if (hidden % (BP / 2) != 0 || !tl_gemm_tcgen05_supports(M, 2 * hidden, K)) return TL_BAD_SIZE;
@@ -464,13 +623,16 @@ extern "C" int tl_gemm_tcgen05_gated(const void* A, const void* W, void* out, in
     if (rc != TL_OK) return rc;
     rc = make_map(&ma, A, M, K, bq);
     if (rc != TL_OK) return rc;
-    GemmParams p;
+    if (in_ssq != nullptr && in_parts < 1) return TL_BAD_SIZE;
+    GemmParams p = {};
     p.out = out; p.status = status; p.M = M; p.N = 2 * hidden; p.K = K;
     p.k_blocks_per_split = (K + BK - 1) / BK;
     p.out_is_f32 = 0;
     p.hidden = hidden;
+    p.splits = 1;
+    p.in_ssq = in_ssq; p.in_parts = in_parts; p.in_inv_dim = in_inv_dim; p.in_eps = in_eps;
     cudaStream_t s = (cudaStream_t)stream;
-    if (bq == 16) return launch<16, 6, true>(mw, ma, p, slabs, 1, s);
-    if (bq == 32) return launch<32, 5, true>(mw, ma, p, slabs, 1, s);
-    return launch<64, 4, true>(mw, ma, p, slabs, 1, s);
+    if (bq == 16) return launch<16, 6, MODE_GATED>(mw, ma, p, slabs, 1, s);
+    if (bq == 32) return launch<32, 5, MODE_GATED>(mw, ma, p, slabs, 1, s);
+    return launch<64, 4, MODE_GATED>(mw, ma, p, slabs, 1, s);
 }

@@ -7,7 +7,23 @@
 // (2i, 2i+1); otherwise lanes (i, i + head_dim/2) are paired.
 //
 // Pages are laid out [page, kv_head, slot_in_page, head_dim]; slot_mapping[t] = page * page_size + slot.
+//
+// The projection's input may have been weighted for an RMS norm but not normalised yet; then every
+// value of a token's row is first multiplied by rsqrt(sum_p ssq[token, p] * inv_dim + eps)
+// (the norm of torchllms/models/networks.py:195-200, applied after the product instead of before it).
 #include "common.cuh"
+
+struct RowScale {
+    const float* ssq;
+    int parts;
+    float inv_dim, eps;
+};
+__device__ __forceinline__ float row_scale(const RowScale& rs, long long row) {
+    if (rs.ssq == nullptr) return 1.f;
+    float v = 0.f;
+    for (int q = 0; q < rs.parts; ++q) v += __ldcg(rs.ssq + row * rs.parts + q);
+    return rsqrtf(v * rs.inv_dim + rs.eps);
+}
 
 // qkv holds `splits` planes `plane` elements apart (partial sums of a split-K product), summed first
 template <typename TI, typename T>
@@ -16,10 +32,11 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int splits, lon
                                      const float* __restrict__ table, const int* __restrict__ slot_mapping,
                                      T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                      int n_heads, int n_kv_heads, int head_dim, int page_size,
-                                     int table_rows, int interleaved) {
+                                     int table_rows, int interleaved, const RowScale rs) {
     grid_launch_dependents();
     grid_dependency_wait();
     const int t = blockIdx.x;
+    const float sc = row_scale(rs, t);
     const int half = head_dim >> 1;
     const int heads_per_cta = (n_heads + 2 * n_kv_heads + gridDim.y - 1) / gridDim.y;
     const int head_lo = blockIdx.y * heads_per_cta;
@@ -49,6 +66,8 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int splits, lon
             x0 += to_float(src[sp * plane + head * head_dim + l0]);
             x1 += to_float(src[sp * plane + head * head_dim + l1]);
         }
+        x0 *= sc;
+        x1 *= sc;
         if (p < n_rot_pairs) {
             const float c = cs[2 * i], s = cs[2 * i + 1];
             const float y0 = x0 * c - x1 * s;
@@ -105,7 +124,7 @@ __global__ void rope_kv_write_vec_kernel(const TI* __restrict__ qkv, int splits,
                                          const int* __restrict__ positions, const float* __restrict__ table,
                                          const int* __restrict__ slot_mapping, T* __restrict__ q_out,
                                          T* __restrict__ k_pages, T* __restrict__ v_pages, int n_heads, int n_kv_heads,
-                                         int head_dim, int page_size, int table_rows) {
+                                         int head_dim, int page_size, int table_rows, const RowScale rs) {
     grid_launch_dependents();
     // positions, cache slots and the rotation table do not come from the kernel before this one (the
     // step's index data were uploaded before its first kernel): they are fetched before waiting for it
@@ -128,6 +147,7 @@ __global__ void rope_kv_write_vec_kernel(const TI* __restrict__ qkv, int splits,
     if (c_first < heads * per_head && c_first / per_head < n_heads + n_kv_heads)
         load8(cs + ((c_first - (c_first / per_head) * per_head) << 3), r_first);
     grid_dependency_wait();
+    const float sc = row_scale(rs, t);
     for (int c = c_first; c < heads * per_head; c += gridDim.y * blockDim.x) {
         const int head = c / per_head;
         const int off = (c - head * per_head) << 3;
@@ -139,6 +159,8 @@ __global__ void rope_kv_write_vec_kernel(const TI* __restrict__ qkv, int splits,
 #pragma unroll
             for (int i = 0; i < 8; ++i) x[i] += y[i];
         }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] *= sc;
         if (head < n_heads + n_kv_heads) {
             float r[8];
             if (c == c_first) {
@@ -167,11 +189,15 @@ __global__ void rope_kv_write_vec_kernel(const TI* __restrict__ qkv, int splits,
 
 // k_pages / v_pages may both be null: then only q is produced (a run that reads another run's cache).
 // qkv: [splits, n_tokens, row] of in_dtype (splits > 1 only for float32 partial sums); q, pages: dtype.
+// in_ssq may be null; else [n_tokens, in_parts] floats give every token's row scale (see the top of the file).
 extern "C" int tl_rope_kv_write(const void* qkv, int in_dtype, int splits, const int* positions, const float* table,
                                 const int* slot_mapping, void* q_out, void* k_pages, void* v_pages,
                                 int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                                int page_size, int table_rows, int interleaved, void* stream) {
+                                int page_size, int table_rows, int interleaved,
+                                const float* in_ssq, int in_parts, float in_inv_dim, float in_eps, void* stream) {
     if (n_tokens <= 0) return TL_OK;
+    if (in_ssq != nullptr && in_parts < 1) return TL_BAD_SIZE;
+    const RowScale rs = {in_ssq, in_parts, in_inv_dim, in_eps};
     if (head_dim <= 0 || (head_dim & 1) || n_heads <= 0 || n_kv_heads <= 0 || page_size <= 0 || table_rows <= 0 || splits < 1)
         return TL_BAD_SIZE;
     if ((k_pages == nullptr) != (v_pages == nullptr)) return TL_BAD_SIZE;
@@ -193,7 +219,7 @@ extern "C" int tl_rope_kv_write(const void* qkv, int in_dtype, int splits, const
 #define TL_ROPE_VEC(TI, T)                                                                                      \
     tl_launch(rope_kv_write_vec_kernel<TI, T>, dim3(n_tokens, by), dim3(vthreads), 0, s,                        \
               (const TI*)qkv, splits, plane, positions, table, slot_mapping, (T*)q_out, (T*)k_pages, (T*)v_pages, \
-              n_heads, n_kv_heads, head_dim, page_size, table_rows)
+              n_heads, n_kv_heads, head_dim, page_size, table_rows, rs)
         if (in_dtype == TL_F32 && dtype == TL_F32) return (int)TL_ROPE_VEC(float, float);
         if (in_dtype == TL_BF16 && dtype == TL_BF16) return (int)TL_ROPE_VEC(__nv_bfloat16, __nv_bfloat16);
         if (in_dtype == TL_F32 && dtype == TL_BF16) return (int)TL_ROPE_VEC(float, __nv_bfloat16);
@@ -203,7 +229,7 @@ extern "C" int tl_rope_kv_write(const void* qkv, int in_dtype, int splits, const
 #define TL_ROPE_LAUNCH(TI, T)                                                                                   \
     tl_launch(rope_kv_write_kernel<TI, T>, dim3(n_tokens, chunks), dim3(threads), 0, s,                         \
               (const TI*)qkv, splits, plane, positions, table, slot_mapping, (T*)q_out, (T*)k_pages, (T*)v_pages, \
-              n_heads, n_kv_heads, head_dim, page_size, table_rows, interleaved)
+              n_heads, n_kv_heads, head_dim, page_size, table_rows, interleaved, rs)
     if (in_dtype == TL_F32 && dtype == TL_F32) return (int)TL_ROPE_LAUNCH(float, float);
     if (in_dtype == TL_BF16 && dtype == TL_BF16) return (int)TL_ROPE_LAUNCH(__nv_bfloat16, __nv_bfloat16);
     if (in_dtype == TL_F32 && dtype == TL_BF16) return (int)TL_ROPE_LAUNCH(float, __nv_bfloat16);

@@ -15,7 +15,7 @@ import torch
 from ..config.registry import Architecture, get_architecture, load_config
 from ..kernels import get_ops
 from ..weights.loader import LazyTensor, WeightError, check_tensors, materialize, source_tensors
-from ..weights.safetensors_io import TensorSource
+from ..weights.safetensors_io import TORCH_SUFFIXES, TensorSource
 from .model import Model
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -41,7 +41,8 @@ def model_dir_of(path) -> Path:
 
 def load_model(path, *, dtype="bfloat16", device="cuda", overrides: Optional[Mapping[str, Any]] = None,
                max_positions: Optional[int] = None, ops=None) -> Tuple[Architecture, Any, Model]:
-    """``path`` is a model folder, a safetensors file, or a list of them: tensors of later
+    """``path`` is a model folder, a safetensors file, a ``torch.save``d checkpoint of plain tensors
+    (the reference's ``consolidated.00.pth`` beside its ``params.json``), or a list of them: tensors of later
     entries replace those of earlier ones (the reference loads several checkpoint paths in order,
     torchllms/models/utils.py:102-130); the configuration is read beside the first."""
     paths = [path] if isinstance(path, (str, Path)) else list(path)
@@ -53,7 +54,7 @@ def load_model(path, *, dtype="bfloat16", device="cuda", overrides: Optional[Map
     found: Dict[str, LazyTensor] = {}
     for p in paths:
         p = Path(p)
-        source = TensorSource(p if p.is_file() and p.suffix == ".safetensors" else model_dir_of(p))
+        source = TensorSource(p if p.is_file() and p.suffix in (".safetensors",) + TORCH_SUFFIXES else model_dir_of(p))
         found.update(arch.adapt_tensors(config, source_tensors(source)))
     expected = model.expected_tensors()
     if (spec.tie_head and spec.head_tensor != spec.embedding_tensor

@@ -17,6 +17,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from .build import ALL_LIBRARIES, build_libraries, load_library
+from .lazy import PendingProduct, RowScaled
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -68,6 +69,16 @@ def _cuda_contig(t: torch.Tensor, name: str, dtype=None) -> None:
         _need(t.dtype == dtype, f"{name} must be {dtype}, got {t.dtype}")
 
 
+def _scale_args(rs: Optional[RowScaled], n_rows: int):
+    """The four trailing arguments by which a kernel learns of rows whose normalisation was deferred."""
+    if rs is None:
+        return ctypes.c_void_p(0), 0, ctypes.c_float(0.0), ctypes.c_float(0.0)
+    ssq = rs.ssq
+    _need(ssq.is_cuda and ssq.dtype == torch.float32 and ssq.dim() == 2 and ssq.is_contiguous() and ssq.shape[0] >= n_rows,
+          "row scale: ssq must be a contiguous float32 [rows, parts] tensor on the GPU")
+    return _ptr(ssq), int(ssq.shape[1]), ctypes.c_float(1.0 / rs.dim), ctypes.c_float(rs.eps)
+
+
 def _timed(fn):
     """While a profile is being taken, bracket the call with CUDA events."""
     name = fn.__name__
@@ -108,6 +119,9 @@ class NativeOps:
         self._status = torch.zeros(4, dtype=torch.int32).pin_memory()
         self._mm_out_dtype: Optional[bool] = None
         self._profile = None
+        # the product that adds itself to the residual stream counts its K splits off per column slab
+        self._counters: Dict[int, torch.Tensor] = {}
+        self.use_fused_residual = os.environ.get("TORCHLLMS_B200_NO_FUSED_RESIDUAL", "") not in ("1", "true")
 
     def graph_capturable(self, dtype: torch.dtype) -> bool:
         """Whether this library's launches for ``dtype`` may be recorded into a CUDA graph."""
@@ -165,12 +179,18 @@ class NativeOps:
         return out
 
     @_timed
-    def rmsnorm(self, h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
-                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def rmsnorm(self, h: torch.Tensor, delta, weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, deferred: bool = False):
+        """``delta`` may be a tensor, float32 partial sums ``[splits, T, dim]``, or a
+        :class:`PendingProduct` (taken here the ordinary way).  ``deferred``: return the rows
+        weighted but not normalised, as a :class:`RowScaled` (not with ``rows``)."""
+        if isinstance(delta, PendingProduct):
+            delta = delta.take(self)
         _cuda_contig(h, "residual stream", torch.float32)
         _cuda_contig(weight, "norm weight", torch.float32)
         _need(h.dim() == 2 and weight.numel() == h.shape[1], "norm weight must match the stream's width")
         _need(out_dtype in _DT, f"norm output dtype {out_dtype} unsupported")
+        _need(not (deferred and rows is not None), "a deferred norm leaves whole streams, not gathered rows")
         dim = h.shape[1]
         _need(dim * 4 <= 200 * 1024, f"rmsnorm keeps a row in shared memory: width {dim} exceeds 51200")
         splits, plane = 1, 0
@@ -187,18 +207,70 @@ class NativeOps:
             _cuda_contig(rows, "rows", torch.int32)
         n_out = h.shape[0] if rows is None else rows.numel()
         out = torch.empty((n_out, dim), dtype=out_dtype, device=h.device)
+        ssq = torch.empty((n_out, 1), dtype=torch.float32, device=h.device) if deferred else None
         write_back = 1 if (delta is not None and rows is None) else 0
         rc = self._lib("elementwise").tl_rmsnorm(
             _ptr(h), _ptr(delta), _DT[delta.dtype] if delta is not None else 0, splits, ctypes.c_longlong(plane),
-            _ptr(weight), _ptr(out), _DT[out_dtype], _ptr(rows), n_out, dim, ctypes.c_float(eps), write_back, _stream())
+            _ptr(weight), _ptr(out), _DT[out_dtype], _ptr(rows), n_out, dim, ctypes.c_float(eps), write_back,
+            _ptr(ssq), _stream())
         _check(rc, "rmsnorm")
         self.launches += 1
-        return out
+        return RowScaled(out, ssq, dim, float(eps)) if deferred else out
+
+    def can_fuse_residual(self, pending, h: torch.Tensor) -> bool:
+        """Whether :meth:`linear_residual_norm` takes this pending product for this stream."""
+        if not (self.use_fused_residual and self.use_tcgen05 and isinstance(pending, PendingProduct)):
+            return False
+        x, w = pending.x, pending.w
+        if not (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2):
+            return False
+        M, K = x.shape
+        N = w.shape[0]
+        return (h.shape == (M, N) and x.is_contiguous() and w.is_contiguous() and x.data_ptr() % 16 == 0
+                and w.data_ptr() % 16 == 0
+                and self._lib("gemm_tcgen05").tl_gemm_tcgen05_residual_supports(M, N, K) == 1)
 
     @_timed
-    def swiglu(self, gate_up: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    def linear_residual_norm(self, pending: PendingProduct, h: torch.Tensor, weight: torch.Tensor, eps: float) -> RowScaled:
+        """``h += bf16(x @ w.T)`` in place (float32; the product rounded as one that passes through
+        memory is) and the rows ``bf16(h * weight)`` with the parts of their sums of squares: one kernel in which the product's K splits are added up by whichever
+        CTA of a column slab finishes last."""
+        x, w = pending.x, pending.w
+        _cuda_contig(x, "linear input", torch.bfloat16)
+        _cuda_contig(w, "linear weight", torch.bfloat16)
+        _cuda_contig(h, "residual stream", torch.float32)
+        _cuda_contig(weight, "norm weight", torch.float32)
+        M, K = x.shape
+        N = w.shape[0]
+        _need(w.shape[1] == K and h.shape == (M, N) and weight.numel() == N, "linear_residual_norm: shapes disagree")
+        lib = self._lib("gemm_tcgen05")
+        _need(lib.tl_gemm_tcgen05_residual_supports(M, N, K) == 1,
+              "the fused form takes bfloat16, at most 64 rows, K % 8 == 0 and a width that is a multiple of 4")
+        splits = lib.tl_gemm_tcgen05_splits(M, N, K)
+        slabs = lib.tl_gemm_tcgen05_slabs(N)
+        dev = x.device.index or 0
+        counters = self._counters.get(dev)
+        if counters is None or counters.numel() < slabs:
+            if counters is not None:
+                self._retired.append(counters)     # a captured graph may still point at it
+            counters = self._counters[dev] = torch.zeros(max(slabs, 1024), dtype=torch.int32, device=x.device)
+        partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+        xw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        ssq = torch.empty((M, slabs), dtype=torch.float32, device=x.device)
+        rc = lib.tl_gemm_tcgen05_residual(_ptr(x), _ptr(w), _ptr(partial), _ptr(counters), _ptr(h), _ptr(weight), _ptr(xw),
+                                          _ptr(ssq), M, N, K, splits, ctypes.c_void_p(self._status.data_ptr()), _stream())
+        _check(rc, "gemm_tcgen05_residual")
+        self.launches += 1
+        return RowScaled(xw, ssq, N, float(eps))
+
+    @_timed
+    def swiglu(self, gate_up, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """``gate_up`` is ``[tokens, 2 * hidden]``, or float32 partial sums ``[splits, tokens, 2 * hidden]``
-        (then ``out_dtype`` says what to produce)."""
+        (then ``out_dtype`` says what to produce), or a :class:`RowScaled` of either (the scale is
+        applied to gate and up before the activation)."""
+        rs = gate_up if isinstance(gate_up, RowScaled) else None
+        if rs is not None:
+            gate_up = rs.x
         _cuda_contig(gate_up, "gate_up")
         _need(gate_up.dim() in (2, 3) and gate_up.shape[-1] % 2 == 0 and gate_up.dtype in _DT,
               "swiglu input must be [tokens, 2 * hidden] in float32/bfloat16")
@@ -210,7 +282,7 @@ class NativeOps:
         n, hidden = gate_up.shape[-2], gate_up.shape[-1] // 2
         out = torch.empty((n, hidden), dtype=out_dtype, device=gate_up.device)
         rc = self._lib("elementwise").tl_swiglu(_ptr(gate_up), _DT[gate_up.dtype], splits, _ptr(out), _DT[out_dtype],
-                                               n, hidden, _stream())
+                                               n, hidden, *_scale_args(rs, n), _stream())
         _check(rc, "swiglu")
         self.launches += 1
         return out
@@ -225,7 +297,10 @@ class NativeOps:
 
         With ``partials_ok`` the result may be float32 partial sums ``[splits, M, N]`` of a
         split-K product, for callers that hand it to a kernel which adds them up (residual +
-        norm, rope, swiglu)."""
+        norm, rope, swiglu).  A :class:`RowScaled` input gives a :class:`RowScaled` result: the
+        product is taken of the rows as they are and the scale follows it."""
+        if isinstance(x, RowScaled):
+            return x.follow(self.linear(x.x, w, out_dtype, partials_ok))
         _cuda_contig(x, "linear input")
         _cuda_contig(w, "linear weight")
         _need(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], "linear: inner sizes differ")
@@ -258,7 +333,11 @@ class NativeOps:
         """``silu(x @ w13[:H]^T) * (x @ w13[H:]^T)`` for a stacked gate/up weight ``[2 H, K]``, in
         ``x``'s dtype.  Decode-sized bfloat16 inputs whose product needs no K split run as one
         kernel (the activation in the product's epilogue); everything else as product + SwiGLU
-        kernel, with the same numbers.  ``fused`` forces the choice (tests)."""
+        kernel, with the same numbers.  ``fused`` forces the choice (tests).  ``x`` may be a
+        :class:`RowScaled`: gate and up are scaled before the activation."""
+        rs = x if isinstance(x, RowScaled) else None
+        if rs is not None:
+            x = rs.x
         _cuda_contig(x, "linear input")
         _cuda_contig(w13, "linear weight")
         _need(x.dim() == 2 and w13.dim() == 2 and x.shape[1] == w13.shape[1] and w13.shape[0] % 2 == 0,
@@ -272,17 +351,19 @@ class NativeOps:
                      self._lib("gemm_tcgen05").tl_gemm_tcgen05_gated_supports(M, hidden, K) == 1)
         _need(can or not fused, "the fused form takes bfloat16, at most 64 rows, hidden % 64 == 0 and K % 8 == 0")
         if not fused:
-            return self.swiglu(self.linear(x, w13, partials_ok=True), out_dtype=x.dtype)
-        return self.gemm_gated(x, w13)
+            gate_up = self.linear(x, w13, partials_ok=True)
+            return self.swiglu(gate_up if rs is None else rs.follow(gate_up), out_dtype=x.dtype)
+        return self.gemm_gated(x, w13, rs)
 
     @_timed
-    def gemm_gated(self, x: torch.Tensor, w13: torch.Tensor) -> torch.Tensor:
+    def gemm_gated(self, x: torch.Tensor, w13: torch.Tensor, rs: Optional[RowScaled] = None) -> torch.Tensor:
         """The one-kernel form of :meth:`linear_swiglu` (its caller has checked the sizes)."""
         M, K = x.shape
         hidden = w13.shape[0] // 2
         out = torch.empty((M, hidden), dtype=torch.bfloat16, device=x.device)
         rc = self._lib("gemm_tcgen05").tl_gemm_tcgen05_gated(
-            _ptr(x), _ptr(w13), _ptr(out), M, hidden, K, ctypes.c_void_p(self._status.data_ptr()), _stream())
+            _ptr(x), _ptr(w13), _ptr(out), M, hidden, K, *_scale_args(rs, M),
+            ctypes.c_void_p(self._status.data_ptr()), _stream())
         _check(rc, "gemm_tcgen05_gated")
         self.launches += 1
         return out
@@ -313,6 +394,8 @@ class NativeOps:
         code = int(self._status[0])
         if code != 0:
             self._status[0] = 0
+            for counters in self._counters.values():       # a kernel that gave up may have left a count behind
+                counters.zero_()
             raise KernelError(f"a kernel gave up waiting (code {code}); its output is not valid")
 
     def wait_selftest(self, limit_ms: float = 1.0) -> float:
@@ -342,13 +425,17 @@ class NativeOps:
 
     # -------------------------------------------------------------------- rope
     @_timed
-    def rope_kv_write(self, qkv: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, *,
+    def rope_kv_write(self, qkv, positions: torch.Tensor, table: torch.Tensor, *,
                       n_heads: int, n_kv_heads: int, head_dim: int, interleaved: bool,
                       k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
                       slot_mapping: Optional[torch.Tensor], page_size: int,
                       out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """``qkv`` is ``[tokens, row]``, or float32 partial sums ``[splits, tokens, row]`` (then
-        ``out_dtype`` is the dtype of q and of the pages)."""
+        ``out_dtype`` is the dtype of q and of the pages), or a :class:`RowScaled` of either (every
+        row is multiplied by its scale before it is rotated and stored)."""
+        rs = qkv if isinstance(qkv, RowScaled) else None
+        if rs is not None:
+            qkv = rs.x
         _cuda_contig(qkv, "qkv")
         _cuda_contig(positions, "positions", torch.int32)
         _cuda_contig(table, "rotary table", torch.float32)
@@ -374,7 +461,7 @@ class NativeOps:
             _ptr(qkv), _DT[qkv.dtype], splits, _ptr(positions), _ptr(table),
             _ptr(slot_mapping if k_pages is not None else None),
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _DT[out_dtype], T, n_heads, n_kv_heads, head_dim,
-            page_size, table.shape[0], 1 if interleaved else 0, _stream())
+            page_size, table.shape[0], 1 if interleaved else 0, *_scale_args(rs, T), _stream())
         _check(rc, "rope_kv_write")
         self.launches += 1
         return q

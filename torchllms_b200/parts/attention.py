@@ -16,6 +16,7 @@ from typing import Dict, Mapping, Optional
 
 import torch
 
+from ..kernels.lazy import PendingProduct
 from ..weights.loader import ExpectedTensor
 from .base import (POSITION_ENCODINGS, BuildEnv, CacheNeed, Mixer, as_compute, register_mixer)
 from .spec import PartSpec
@@ -33,6 +34,8 @@ class PagedAttention(Mixer):
         self.window = None if window is None else int(window)
         self.position = POSITION_ENCODINGS.build(position, env)
         self.graph_safe = self.position.graph_safe
+        # x only goes into the q/k/v product, whose result the position encoding's kernel may scale
+        self.takes_row_scaled = self.position.takes_row_scaled
         env.ops.check_attention_sizes(self.n_heads, self.n_kv_heads, self.head_dim, env.dtype)
         self.wqkv: Optional[torch.Tensor] = None
         self.wo: Optional[torch.Tensor] = None
@@ -82,5 +85,6 @@ class PagedAttention(Mixer):
             o = ops.paged_attention(
                 q, cache.k_pages, cache.v_pages, cache.block_table, ctx.q_start, ctx.kv_len,
                 n_seqs=B, max_q_len=ctx.max_q_len, max_kv_len=ctx.max_kv_len, **common)
-        # the caller's norm adds up split-K partial sums together with the residual
-        return ops.linear(o.view(o.shape[0], self.n_heads * self.head_dim), self.wo, partials_ok=True)
+        # the output projection is left to the norm that follows: it may add the product to the
+        # residual stream in the product's own kernel, or take it and add up its partial sums
+        return PendingProduct(o.view(o.shape[0], self.n_heads * self.head_dim), self.wo)

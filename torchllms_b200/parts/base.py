@@ -99,7 +99,16 @@ class Norm(Part):
     """``forward(residual, rows=None)``: folds the residual's pending delta into
     the stream (32-bit sum) and returns the normalised rows in the activation
     dtype; with ``rows`` (int32 indices) only those rows are produced and the
-    stream is left as it was."""
+    stream is left as it was.
+
+    The pending delta may be a tensor, float32 partial sums, or a
+    :class:`~torchllms_b200.kernels.lazy.PendingProduct` (``ops.rmsnorm`` takes all three).  A
+    norm with ``can_defer`` also accepts ``deferred_ok=True`` and may then return a
+    :class:`~torchllms_b200.kernels.lazy.RowScaled` (rows weighted but not yet normalised, the
+    scale to be applied by whoever consumes them); a block passes that flag only to such a norm
+    and only when the part that reads the rows has ``takes_row_scaled``."""
+
+    can_defer = False
 
     def forward(self, residual: "Residual", rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
@@ -111,7 +120,10 @@ class PositionEncoding(Part):
 
     ``encode_and_store(qkv, ctx, cache, n_heads, n_kv_heads, head_dim)`` returns
     ``q [T, H, hd]``; it writes K and V at ``cache.slot_mapping`` when
-    ``cache.writes`` is true."""
+    ``cache.writes`` is true.  ``qkv`` may be float32 partial sums ``[splits, T, row]``, and, if the
+    encoding sets ``takes_row_scaled``, a :class:`~torchllms_b200.kernels.lazy.RowScaled`."""
+
+    takes_row_scaled = False
 
     def encode_and_store(self, qkv, ctx, cache, n_heads: int, n_kv_heads: int, head_dim: int):
         raise NotImplementedError
@@ -120,6 +132,12 @@ class PositionEncoding(Part):
 class Mixer(Part):
     """``forward(x [T, dim], ctx, cache) -> [T, dim]`` (activation dtype).
 
+    ``x`` is a tensor unless the mixer sets ``takes_row_scaled`` (then it may be a
+    :class:`~torchllms_b200.kernels.lazy.RowScaled`, which the kernel library's ``linear``,
+    ``rope_kv_write`` and ``linear_swiglu`` accept in a tensor's place).  The result may be a
+    :class:`~torchllms_b200.kernels.lazy.PendingProduct`: a last projection left for the norm that
+    follows to take.
+
     ``cache_need()`` / ``state_need()`` tell the cache manager what one run of
     this mixer wants per request (either may be ``None``).  ``cache`` is the
     :class:`~torchllms_b200.cache.manager.RunCacheView` of the run being
@@ -127,6 +145,8 @@ class Mixer(Part):
     A mixer with state must handle the portions of a request in order;
     ``ctx.fresh`` marks requests whose portion starts at position 0.
     """
+
+    takes_row_scaled = False
 
     def cache_need(self) -> Optional[CacheNeed]:
         return None
@@ -139,7 +159,10 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    """``forward(x [T, dim], ctx) -> [T, dim]`` (activation dtype); tokens do not interact."""
+    """``forward(x [T, dim], ctx) -> [T, dim]`` (activation dtype); tokens do not interact.
+    ``takes_row_scaled`` and a pending last projection as for a mixer."""
+
+    takes_row_scaled = False
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError
@@ -165,7 +188,9 @@ class Residual:
     Keeping the last delta pending lets the next norm kernel do ``h += delta``
     and the normalisation in one pass over the row.  The delta is ``[T, dim]`` in
     the activation dtype, or float32 partial sums ``[splits, T, dim]`` of a
-    split-K product, which the norm kernel adds up as well.
+    split-K product, which the norm kernel adds up as well, or a product not yet
+    taken (:class:`~torchllms_b200.kernels.lazy.PendingProduct`), which the norm may
+    hand to a kernel that adds it to ``h`` in its own epilogue.
     """
 
     __slots__ = ("h", "delta")

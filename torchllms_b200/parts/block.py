@@ -50,7 +50,14 @@ class PreNormBlock(Block):
             sub.load({name: tensors[f"{prefix}.{name}"] for name in sub.expected_tensors()})
 
     def forward(self, residual: Residual, ctx, cache) -> None:
-        x = self.mixer_norm.forward(residual)
+        x = self._normed(self.mixer_norm, self.mixer, residual)
         residual.delta = self.mixer.forward(x, ctx, cache)
-        x = self.ffn_norm.forward(residual)
+        x = self._normed(self.ffn_norm, self.feed_forward, residual)
         residual.delta = self.feed_forward.forward(x, ctx)
+
+    @staticmethod
+    def _normed(norm, reader, residual: Residual):
+        """The rows for ``reader``: with their normalisation deferred where both sides can."""
+        if norm.can_defer and reader.takes_row_scaled:
+            return norm.forward(residual, deferred_ok=True)
+        return norm.forward(residual)

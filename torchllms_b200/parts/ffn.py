@@ -11,6 +11,7 @@ from typing import Dict, Mapping, Optional
 
 import torch
 
+from ..kernels.lazy import PendingProduct
 from ..weights.loader import ExpectedTensor
 from .base import BuildEnv, FeedForward, as_compute, register_feed_forward
 
@@ -18,6 +19,7 @@ from .base import BuildEnv, FeedForward, as_compute, register_feed_forward
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
     graph_safe = True
+    takes_row_scaled = True      # x only goes into the gate/up product, whose activation applies the scale
 
     def __init__(self, env: BuildEnv, *, dim: int, hidden: int):
         self.env = env
@@ -40,4 +42,5 @@ class SwiGLU(FeedForward):
         ops = self.env.ops
         # gate and up in one product over the stacked weight, the activation in its epilogue where the
         # kernel can (decode steps), else product [T, 2 * hidden] + SwiGLU kernel
-        return ops.linear(ops.linear_swiglu(x, self.w13), self.w2, partials_ok=True)
+        # the down projection is left to the norm that follows (see PendingProduct)
+        return PendingProduct(ops.linear_swiglu(x, self.w13), self.w2)

@@ -58,7 +58,7 @@ class RotaryEncoding(PositionEncoding):
     convention) or ``"half"`` (lanes i, i + hd/2: Hugging Face's)."""
 
     graph_safe = True
-
+    takes_row_scaled = True      # the kernel scales every row before it rotates and stores it
 
     def __init__(self, env: BuildEnv, *, head_dim: int, theta: float,
                  scaling: Optional[Mapping[str, Any]] = None, pairing: str = "interleaved"):

@@ -91,8 +91,40 @@ class SafetensorsFile:
         return raw.view(dtype).reshape(shape)
 
 
+class TorchCheckpointFile:
+    """A ``torch.save``d dictionary of tensors (the reference's ``consolidated.00.pth``, which it
+    reads with ``torch.load(mmap=True)``, torchllms/models/utils.py:107-111), offered by name like a
+    safetensors file.  Only tensors are unpickled (``weights_only``); the file is mapped, not read."""
+
+    def __init__(self, path):
+        self.path = Path(path)
+        try:
+            state = torch.load(str(self.path), mmap=True, weights_only=True, map_location="cpu")
+        except Exception as e:          # a pickle that holds more than tensors, a truncated file, ...
+            raise SafetensorsError(f"{self.path}: not a checkpoint of plain tensors ({type(e).__name__}: {e})") from None
+        if not isinstance(state, dict) or not all(isinstance(k, str) and isinstance(v, torch.Tensor) for k, v in state.items()):
+            raise SafetensorsError(f"{self.path}: expected a dictionary from tensor names to tensors")
+        self._state = state
+
+    def names(self) -> List[str]:
+        return list(self._state)
+
+    def shape(self, name: str) -> Tuple[int, ...]:
+        return tuple(self._state[name].shape)
+
+    def dtype(self, name: str) -> torch.dtype:
+        return self._state[name].dtype
+
+    def get(self, name: str) -> torch.Tensor:
+        return self._state[name]
+
+
+TORCH_SUFFIXES = (".pth", ".pt")
+
+
 class TensorSource:
-    """All tensors of a model folder (or a single file), by name."""
+    """All tensors of a model folder (or a single file), by name: safetensors (one file, or shards
+    with their index), or, where a folder holds none, the reference's ``consolidated.*.pth``."""
 
     def __init__(self, path):
         path = Path(path)
@@ -110,13 +142,13 @@ class TensorSource:
             elif single.is_file():
                 paths = [single]
             else:
-                paths = sorted(path.glob("*.safetensors"))
+                paths = sorted(path.glob("*.safetensors")) or sorted(path.glob("consolidated.*.pth"))
             if not paths:
-                raise FileNotFoundError(f"{path}: no model.safetensors (or shards) found")
+                raise FileNotFoundError(f"{path}: no model.safetensors (or shards, or consolidated.*.pth) found")
         for p in paths:
             if not p.is_file():
                 raise FileNotFoundError(f"{p}: listed in the shard index but missing")
-            f = SafetensorsFile(p)
+            f = TorchCheckpointFile(p) if p.suffix in TORCH_SUFFIXES else SafetensorsFile(p)
             self.files.append(f)
             for name in f.names():
                 if name in self._where:
