@@ -189,10 +189,14 @@ SERVE = {
 }
 
 
-def serving_workload(args):
+def serving_workload(args, peaks):
     """A whole serving run through ``LLM.generate`` (continuous batching, prompts cut into portions of
-    2,048 tokens beside decoded tokens): one JSON line with tokens per second, wall clock around the call
-    (host token lists in, host token lists out)."""
+    2,048 tokens beside decoded tokens): the record with tokens per second, wall clock around the call
+    (host token lists in, host token lists out), and how that compares with what the run's arithmetic
+    and memory traffic take at the peaks: ``flop_seconds`` (every token through every weight, causal
+    attention) at the sustained tensor-core peak, ``byte_seconds`` (every step reads the weights once
+    and the cache of the requests it holds) at the copy bandwidth, ``roofline_frac`` the larger of the
+    two over the measured seconds."""
     import random
 
     import torch
@@ -221,10 +225,26 @@ def serving_workload(args):
         clocks.mark(t0, t1)
         time.sleep(0.15)
     st = llm.last_stats
+    ops.check_status()
     n_prompt = sum(len(p) for p in prompts)
     n_new = sum(len(o.token_ids) for o in out)
     secs = t1 - t0
-    print(json.dumps({
+    # what the run had to compute and to read, from the steps the scheduler took
+    per_token_flops = 2 * (cfg.n_layers * (cfg.dim * cfg.head_dim * (2 * cfg.n_heads + 2 * cfg.n_kv_heads) + 3 * cfg.dim * cfg.ffn_hidden))
+    kv_bytes_per_token = cfg.n_layers * 2 * cfg.n_kv_heads * cfg.head_dim * 2
+    weight_bytes = llm.model.weight_bytes()
+    held, flops, byts = {}, 0.0, 0.0
+    for step in llm.last_trace:
+        byts += weight_bytes
+        for idx, n in step:
+            before = held.get(idx, 0)
+            held[idx] = before + n
+            flops += n * per_token_flops + 4 * cfg.n_layers * cfg.n_heads * cfg.head_dim * (n * before + n * (n + 1) / 2)
+            byts += (before + n) * kv_bytes_per_token
+        flops += 2 * cfg.dim * cfg.vocab_size * sum(1 for _ in step)          # the head, on one row per request at most
+    flop_s = flops / (peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]) * 1e12)
+    byte_s = byts / (peaks["hbm_gbs"] * 1e9)
+    return ({
         "metric": f"tokens/s through LLM.generate, {args.workload} (prompt and generated tokens)",
         "value": round((n_prompt + n_new) / secs, 1), "unit": "tokens/s", "n_gpus": 1, "steps": st.steps, "warmup": 1,
         "ms_per_step": round(secs * 1e3 / max(st.steps, 1), 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -236,8 +256,9 @@ def serving_workload(args):
                    "new_tokens": w["new_tokens"], "temperature": w["temperature"], "prefill_chunk": 2048,
                    "page_size": 16, "prompt_tokens": n_prompt, "parallelism": "single-gpu"},
         "gpu_launches": ops.launches - launches0, "preemptions": st.preemptions, "clocks": clocks.summary(),
-    }))
-    return 0
+        "flop_seconds": round(flop_s, 3), "byte_seconds": round(byte_s, 3), "roofline_frac": round(max(flop_s, byte_s) / secs, 4),
+        "peaks": peaks["source"],
+    })
 
 
 def main():
@@ -253,6 +274,10 @@ def main():
                     help="decode_8b: the headline (default); serve_1b, long_3b: whole serving runs through LLM.generate")
     ap.add_argument("--context-len", type=int, default=PROMPT_LEN,
                     help="prompt length of the decode measurements (the headline is 2,048; the prefill figure stays at 2,048)")
+    ap.add_argument("--long-contexts", type=lambda t: [int(x) for x in t.split(",") if x], default=[8192, 32768],
+                    help="context lengths of the extra batch-8 decode points (comma separated; empty: none)")
+    ap.add_argument("--with-secondary", action="store_true",
+                    help="also run the two secondary serving workloads and put their figures under 'secondary'")
     ap.add_argument("--timeline", action="store_true",
                     help="also print, on standard error, start and end of every kernel of one decode step in place")
     ap.add_argument("--profile", action="store_true",
@@ -264,7 +289,8 @@ def main():
     if args.impl == "reference":
         return reference_arm(args)
     if args.workload != "decode_8b":
-        return serving_workload(args)
+        print(json.dumps(serving_workload(args, load_peaks())))
+        return 0
     args.warmup = max(args.warmup, 3)
 
     import torch
@@ -318,14 +344,17 @@ def main():
     # ------------------------------------------------------------------ decode at a batch size
     kv_bytes_per_token = args.layers * 2 * cfg.n_kv_heads * cfg.head_dim * 2
 
-    def decode_run(batch, steps, warmup, with_clocks=False):
+    def decode_run(batch, steps, warmup, with_clocks=False, llm=llm, ctx_len=ctx_len):
+        engine = llm.engine
         clocks = ClockSampler() if with_clocks else None
         if clocks:
             clocks.__enter__()
         handles = [engine.claim() for _ in range(batch)]
         ps = prompts(batch, ctx_len)
-        for h, p in zip(handles, ps):                       # prefill, one prompt per step
-            engine.step([StepEntry(h, p, [])])
+        chunk = min(engine.max_step_tokens, 8192)
+        for h, p in zip(handles, ps):                       # prefill, one prompt after the other, in portions
+            for i in range(0, len(p), chunk):
+                engine.step([StepEntry(h, p[i:i + chunk], [])])
         feed = torch.randint(0, cfg.vocab_size, (warmup + steps, batch), generator=gen).tolist()
         for i in range(warmup):
             logits = engine.step([StepEntry(h, [t]) for h, t in zip(handles, feed[i])])
@@ -356,10 +385,12 @@ def main():
                 "clocks": clocks.summary() if clocks else None}
 
     head = decode_run(args.batch, args.steps, args.warmup, with_clocks=True)
-    points = {}
+    points, point_fracs = {}, {}
     if not args.skip_points:
         for b in (1, 64):
-            points[f"decode_b{b}"] = round(decode_run(b, max(args.steps // 2, 8), 3)["tok_s"], 1)
+            run = decode_run(b, max(args.steps // 2, 8), 3)
+            points[f"decode_b{b}"] = round(run["tok_s"], 1)
+            point_fracs[f"decode_b{b}"] = round(run["bytes"] / (run["ms"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
     achieved = head["bytes"] / (head["ms"] / 1e3) / 1e9
 
     if args.profile:
@@ -436,6 +467,40 @@ def main():
     e2e = {"value": round(e2e_tok_s, 1) if e2e_tok_s else None, "unit": "tokens/s",
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch}
 
+    # ------------------------------------------------------------------ longer contexts, batch 8 (an engine of their own)
+    if not args.skip_points and args.long_contexts:
+        weight_bytes = llm.model.weight_bytes()
+        del llm, engine
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        longest = max(args.long_contexts)
+        long_len = -(-(longest + 3 + 64 + 64) // 16) * 16
+        cfg_long = LlamaConfig(architecture="LlamaForCausalLM", rope_scaling=RopeScaling(**ROPE_8B), max_seq_len=long_len, **shape)
+        llm_long = LLM(config=cfg_long, random_seed=0, precision="bfloat16", max_len=long_len, max_bsz=8,
+                       max_num_batched_tokens=8192, page_size=16)
+        for n_ctx in args.long_contexts:
+            run = decode_run(8, 64, 3, llm=llm_long, ctx_len=n_ctx)
+            points[f"decode_b8_ctx{n_ctx}"] = round(run["tok_s"], 1)
+            point_fracs[f"decode_b8_ctx{n_ctx}"] = round(run["bytes"] / (run["ms"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+        ops.check_status()
+        del llm_long
+        gc.collect()
+        torch.cuda.empty_cache()
+
+    secondary = None
+    if args.with_secondary:
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        secondary = {}
+        for name in sorted(SERVE):
+            args.workload = name
+            line = serving_workload(args, peaks)
+            secondary[name] = {k: line[k] for k in ("value", "generated_tokens_per_s", "seconds", "roofline_frac", "flop_seconds", "byte_seconds")}
+            gc.collect()
+            torch.cuda.empty_cache()
+
     out = {
         "metric": f"decode tok/s at batch {args.batch} (Llama-3.1-8B shape, {ctx_len:,}-token prompts)",
         "value": round(head["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
@@ -450,8 +515,10 @@ def main():
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4), "peaks": peaks["source"]},
-        "points": points,
+        "points": points, "point_roofline_fracs": point_fracs,
     }
+    if secondary is not None:
+        out["secondary"] = secondary
     print(json.dumps(out))
     return 0
 

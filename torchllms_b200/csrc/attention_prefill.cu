@@ -214,7 +214,9 @@ struct TileRange {
     int rows, first, last;
 };
 
-template <int HD, int STAGES>
+// PARTS: 2 = probabilities as value + remainder (two products, 16 bits of every probability kept);
+// 1 = probabilities rounded to bfloat16 once (one product).
+template <int HD, int STAGES, int PARTS>
 __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                        const __grid_constant__ CUtensorMap map_v,
                                                                        const PrefillParams p) {
@@ -398,7 +400,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
                     const unsigned long long vd0 = desc_mn_major(smem_u32(tiles + (STAGES + s) * KV_BYTES), HALF_BYTES);
                     const unsigned acc = j > first ? 1u : 0u;
 #pragma unroll
-                    for (int part = 0; part < 2; ++part)             // value, then remainder
+                    for (int part = 0; part < PARTS; ++part)         // value, then remainder
 #pragma unroll
                         for (int kk = 0; kk < BN / 16; ++kk)         // 16 keys on: 2048 bytes of V, 8 columns of P
                             umma_ts(d_o, d_s + part * (BN / 2) + kk * 8, vd0 + kk * (2048 >> 4), id_o,
@@ -523,12 +525,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
                     la = __fadd2_rn(la, ea);
                     lb = __fadd2_rn(lb, eb);
                     const __nv_bfloat162 ha = __floats2bfloat162_rn(ea.x, ea.y), hb = __floats2bfloat162_rn(eb.x, eb.y);
-                    const float2 ra = __ffma2_rn(__bfloat1622float2(ha), neg1, ea);      // what the rounding left, exactly
-                    const float2 rb = __ffma2_rn(__bfloat1622float2(hb), neg1, eb);
                     hi[i / 2] = *reinterpret_cast<const unsigned*>(&ha);
                     hi[i / 2 + 1] = *reinterpret_cast<const unsigned*>(&hb);
-                    lo[i / 2] = pack_bf16(ra.x, ra.y);
-                    lo[i / 2 + 1] = pack_bf16(rb.x, rb.y);
+                    if (PARTS == 2) {
+                        const float2 ra = __ffma2_rn(__bfloat1622float2(ha), neg1, ea);      // what the rounding left, exactly
+                        const float2 rb = __ffma2_rn(__bfloat1622float2(hb), neg1, eb);
+                        lo[i / 2] = pack_bf16(ra.x, ra.y);
+                        lo[i / 2 + 1] = pack_bf16(rb.x, rb.y);
+                    }
                 }
                 const float l0 = la.x, l1 = la.y, l2 = lb.x, l3 = lb.y;
                 float l_sum = (t ? l_b : l_a);
@@ -551,7 +555,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
                 l_sum += (l0 + l1) + (l2 + l3);
                 if (t) { m_b = m_used; l_b = l_sum; } else { m_a = m_used; l_a = l_sum; }
                 tmem_st<HN / 2>(lane_addr + col_s + half * (HN / 2), hi);
-                tmem_st<HN / 2>(lane_addr + col_s + BN / 2 + half * (HN / 2), lo);
+                if (PARTS == 2) tmem_st<HN / 2>(lane_addr + col_s + BN / 2 + half * (HN / 2), lo);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
@@ -679,10 +683,10 @@ bool takes(int n_heads, int n_kv_heads, int head_dim, int page_size) {
 
 bool p_blocks_too_many(int max_q_len) { return (max_q_len + QT * BM - 1) / (QT * BM) > 65535; }
 
-template <int HD>
+template <int HD, int PARTS>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, dim3 grid, cudaStream_t s) {
     constexpr size_t smem = smem_for<HD>();
-    auto kern = attention_prefill_kernel<HD, stages_for<HD>()>;
+    auto kern = attention_prefill_kernel<HD, stages_for<HD>(), PARTS>;
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -701,13 +705,15 @@ extern "C" int tl_attention_prefill_supports(int n_heads, int n_kv_heads, int he
 
 // q, out: [q_rows, n_heads, head_dim] bfloat16 (q_rows: all rows of the buffer, n_tokens of them in
 // use by the n_seqs requests given); pages: [n_pages, n_kv_heads, page_size, head_dim].
+// parts: 2 multiplies every probability as bfloat16 value + bfloat16 remainder, 1 as one bfloat16.
 extern "C" int tl_paged_attention_prefill(const void* q, const void* k_pages, const void* v_pages, void* out,
                                           const int* block_table, int table_stride, const int* q_start,
                                           const int* kv_len, int* status, long long q_rows, int n_tokens, int n_seqs,
                                           int n_heads, int n_kv_heads, int head_dim, int page_size, long long n_pages,
-                                          int max_q_len, int window, float scale, void* stream) {
+                                          int max_q_len, int window, float scale, int parts, void* stream) {
     if (n_tokens <= 0 || n_seqs <= 0) return TL_OK;
     if (!takes(n_heads, n_kv_heads, head_dim, page_size) || max_q_len <= 0 || n_pages <= 0 || q_rows < n_tokens) return TL_BAD_SIZE;
+    if (parts != 1 && parts != 2) return TL_BAD_SIZE;
     if (n_pages * n_kv_heads * page_size >= (1LL << 31)) return TL_BAD_SIZE;
     if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(out) || status == nullptr) return TL_BAD_ALIGN;
     if (n_seqs > 65535 || p_blocks_too_many(max_q_len)) return TL_BAD_SIZE;
@@ -735,5 +741,6 @@ extern "C" int tl_paged_attention_prefill(const void* q, const void* k_pages, co
 
     dim3 grid(n_heads, p.n_q_blocks, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;
-    return head_dim == 128 ? launch<128>(mk, mv, p, grid, s) : launch<64>(mk, mv, p, grid, s);
+    if (parts == 2) return head_dim == 128 ? launch<128, 2>(mk, mv, p, grid, s) : launch<64, 2>(mk, mv, p, grid, s);
+    return head_dim == 128 ? launch<128, 1>(mk, mv, p, grid, s) : launch<64, 1>(mk, mv, p, grid, s);
 }

@@ -69,6 +69,30 @@ __device__ __forceinline__ float warp_max(float x) {
     return x;
 }
 
+// ---- rows whose RMS normalisation was deferred: the kernel that produced them left the weighted rows
+// and, beside them, the parts of every row's sum of squares (one part per strip of columns that a
+// CTA of the producer owned).  Whoever ends the chain of products multiplies by
+// rsqrt(sum of the parts * inv_dim + eps); ssq == nullptr means there is nothing to apply.
+struct RowScale {
+    const float* ssq;       // [rows, parts]
+    int parts;
+    float inv_dim, eps;
+};
+// every thread on its own (rows that differ from thread to thread)
+__device__ __forceinline__ float row_scale(const RowScale& rs, long long row) {
+    if (rs.ssq == nullptr) return 1.f;
+    float v = 0.f;
+    for (int q = 0; q < rs.parts; ++q) v += __ldcg(rs.ssq + row * rs.parts + q);
+    return rsqrtf(v * rs.inv_dim + rs.eps);
+}
+// all 32 lanes of a warp for the same row: the parts are read side by side
+__device__ __forceinline__ float warp_row_scale(const RowScale& rs, long long row) {
+    if (rs.ssq == nullptr) return 1.f;
+    float v = 0.f;
+    for (int q = threadIdx.x & 31; q < rs.parts; q += 32) v += __ldcg(rs.ssq + row * rs.parts + q);
+    return rsqrtf(warp_sum(v) * rs.inv_dim + rs.eps);
+}
+
 // ---- programmatic dependent launch: a kernel may start while its predecessor in the stream is
 // still running, do what does not depend on it (set-up, prefetching weights), and must call
 // grid_dependency_wait() before it touches anything the predecessor writes or reads.  Every

@@ -12,19 +12,6 @@
 //           multiplied by it first.
 #include "common.cuh"
 
-// One scale per row whose normalisation was deferred: rsqrt(sum_p ssq[row, p] * inv_dim + eps); 1 without ssq.
-struct RowScale {
-    const float* ssq;
-    int parts;
-    float inv_dim, eps;
-};
-__device__ __forceinline__ float row_scale(const RowScale& rs, long long row) {
-    if (rs.ssq == nullptr) return 1.f;
-    float v = 0.f;
-    for (int q = 0; q < rs.parts; ++q) v += __ldg(rs.ssq + row * rs.parts + q);
-    return rsqrtf(v * rs.inv_dim + rs.eps);
-}
-
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                              float* __restrict__ out, int dim, int vocab) {
@@ -162,7 +149,7 @@ __global__ void swiglu_kernel(const TI* __restrict__ in, int splits, long long p
     for (int t = blockIdx.y; t < n_tokens; t += gridDim.y) {
         const TI* row = in + (size_t)t * 2 * hidden;
         T* orow = out + (size_t)t * hidden;
-        const float sc = row_scale(rs, t);
+        const float sc = warp_row_scale(rs, t);        // (t is the same for the whole CTA)
         for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < per_row; c += gridDim.x * blockDim.x) {
             const int f = c * VEC;
             if (VEC == 4) {

@@ -25,15 +25,23 @@
 //   gated     SwiGLU of a stacked gate/up weight (below);
 //   residual  the product is added to the float32 residual stream and prepared for the RMS norm that
 //             follows (TransformerBlock, torchllms/models/networks.py:635-644: h = x + attn(..),
-//             then ffn_norm(h)): the splits still write partial sums, count themselves off on a
-//             counter of their slab, and whichever CTA of a slab arrives last adds the slab's
-//             partial sums in the order of the splits (so the result does not depend on who was
-//             last), rounds the sum to bfloat16 as a product that passes through memory is, adds it
-//             to h, and writes h, the weighted but not yet normalised activations
-//             bf16(h * norm_weight), and the slab's share of sum(h^2) per token.  The kernels that
-//             consume the next product (rotary encoding, the gated epilogue here) multiply by
-//             rsqrt(sum / dim + eps): a product is linear in its input, so the scale may follow it.
-//             No separate norm kernel runs and the sum never makes a round trip as a kernel of its own.
+//             then ffn_norm(h)).  The K splits of a slab form one thread-block cluster; each CTA
+//             sends its partial sums, token by token, into the shared memory of the CTA of the
+//             cluster that owns the token (st.async through distributed shared memory, counted by
+//             an mbarrier there: plain stores between CTAs of this GPU, no multicast), and every CTA
+//             adds up what it receives for its tokens in the order of the splits, rounds the sum to
+//             bfloat16 as a product that passes through memory is, adds it to h, and writes h, the
+//             weighted but not yet normalised activations bf16(h * norm_weight), and its rows' share
+//             of sum(h^2) per token.  The kernels that consume the next product (rotary encoding,
+//             the gated epilogue here) multiply by rsqrt(sum / dim + eps): a product is linear in
+//             its input, so the scale may follow it.  No partial sum passes through global memory
+//             and no norm kernel stands between two products.
+//   rotary    the same cluster sums, for the stacked q/k/v projection: the CTA that owns a token has
+//             128 whole columns of its packed row, i.e. whole rotary pairs (adjacent lanes, 2i and
+//             2i + 1: Attention.forward and RotaryPositionalEmbeddings.forward,
+//             torchllms/models/networks.py:513-553, :332-352), applies the row's deferred scale,
+//             rotates q and k and writes q to its tensor and k, v into their cache pages: no kernel
+//             of its own for the rotation and the cache write.
 #include "common.cuh"
 #include <cuda.h>
 
@@ -45,7 +53,7 @@ constexpr int UMMA_K = 16;
 constexpr int NTHREADS = 192;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000ull * 1000ull * 1000ull;   // two seconds, then give up
 
-enum : int { ERR_TMA_WAIT = 101, ERR_MMA_WAIT = 102, ERR_EPI_WAIT = 103, ERR_SELFTEST_WAIT = 109 };
+enum : int { ERR_TMA_WAIT = 101, ERR_MMA_WAIT = 102, ERR_EPI_WAIT = 103, ERR_REDUCE_WAIT = 104, ERR_SELFTEST_WAIT = 109 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -132,6 +140,27 @@ __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// ---- distributed shared memory: addresses of the same variable in another CTA of the cluster, and
+// a store there that counts its bytes on an mbarrier there when it has landed
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ unsigned map_to_cta(unsigned local_addr, unsigned rank) {
+    unsigned remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ void st_async_f32(unsigned remote_addr, float v, unsigned remote_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+                 ::"r"(remote_addr), "r"(__float_as_uint(v)), "r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 template <int N> struct TmemLoad;
 template <> struct TmemLoad<16> {
     __device__ static __forceinline__ void run(unsigned taddr, unsigned (&r)[16]) {
@@ -155,15 +184,23 @@ struct GemmParams {
     int in_parts;
     float in_inv_dim, in_eps;
     // residual form
-    int splits;
-    int* counters;          // [slabs], zero between launches
+    int splits;             // = CTAs of a cluster
     float* h;               // [M, N] residual stream, updated in place
     const float* norm_w;    // [N]
     __nv_bfloat16* xw;      // [M, N]: bf16(h * norm_w)
-    float* ssq;             // [M, slabs]: this slab's share of sum(h^2)
+    float* ssq;             // [M, 4 * slabs]: the share of sum(h^2) of every 32 columns
+    // rotary form: the product is the packed row [q heads | k heads | v heads] of every token (W is the
+    // stacked q/k/v weight); q leaves rotated, k rotated and v as it is go into their cache pages
+    const int* positions;   // [M]
+    const float* table;     // [table_rows, head_dim / 2, 2] (cos, sin)
+    const int* slot_mapping;  // [M]: page * page_size + slot; unused without pages
+    __nv_bfloat16* q_out;   // [M, n_heads, head_dim]
+    __nv_bfloat16* k_pages; // [pages, n_kv_heads, page_size, head_dim] or null (a run that reads another run's cache)
+    __nv_bfloat16* v_pages;
+    int n_heads, n_kv_heads, head_dim, page_size, table_rows;
 };
 
-enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_RESID = 2 };
+enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_RESID = 2, MODE_ROPE = 3 };
 
 // GATED: the slab is 64 rows of the gate projection and the 64 matching rows of the up projection
 // (two TMA boxes per stage), and the epilogue writes silu(gate) * up in bfloat16: the SwiGLU costs
@@ -183,9 +220,10 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
     __shared__ __align__(8) unsigned long long accum_bar;
     __shared__ unsigned tmem_base_slot;
     __shared__ int abort_flag;
-    __shared__ int last_flag;
+    __shared__ __align__(8) unsigned long long red_bar;      // residual form: counts the bytes other CTAs send here
     __shared__ float rstd_s[BQ];
     constexpr bool GATED = MODE == MODE_GATED;
+    constexpr bool CLUSTERED = MODE == MODE_RESID || MODE == MODE_ROPE;     // the K splits of a slab are one cluster
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slab = blockIdx.x, split = blockIdx.y;
@@ -200,6 +238,7 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
             mbar_init(&empty_bar[s], 1);
         }
         mbar_init(&accum_bar, 1);
+        if (CLUSTERED) mbar_init(&red_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -211,6 +250,16 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_d = tmem_base_slot;
     volatile int* aborted = &abort_flag;
+    // residual form: this CTA is split `rank` of its slab's cluster and owns the tokens rank, rank + S, ..:
+    // n_owned of them, each arriving as one row of 128 floats from every split
+    const int S = CLUSTERED ? p.splits : 1;
+    const int rank = CLUSTERED ? (int)cluster_rank() : 0;
+    const int n_owned = (CLUSTERED && p.M > rank) ? (p.M - rank - 1) / S + 1 : 0;
+    float* red = reinterpret_cast<float*>(tiles + STAGES * STAGE_BYTES);     // [owned token][split][row of the slab]
+    if (CLUSTERED) {
+        if (threadIdx.x == 0) mbar_expect_tx(&red_bar, (unsigned)(n_owned * S * BP * 4));
+        cluster_sync_all();          // every CTA's barrier is set up before anybody sends to it
+    }
     grid_launch_dependents();
 
     if (warp == 0) {
@@ -344,6 +393,142 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
                     }
                 }
             }
+        } else if (CLUSTERED) {
+            // Every token's partial sums go to the CTA of the cluster that owns the token (token mod S),
+            // one row of the slab per thread; the store counts itself on the owner's barrier when it
+            // has landed.  A CTA whose waits did not hold sends nothing: its owners' waits run out in
+            // turn and say so.
+            const int row = quarter * 32 + lane;
+            if (ok) {
+                const unsigned red_addr = smem_u32(red), bar_addr = smem_u32(&red_bar);
+#pragma unroll
+                for (int c0 = 0; c0 < BQ; c0 += 16) {
+                    unsigned r[16];
+                    TmemLoad<16>::run(tmem_d + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int tok = c0 + j;
+                        if (tok < p.M) {
+                            const unsigned owner = (unsigned)(tok % S);
+                            const unsigned slot = (unsigned)(tok / S);
+                            st_async_f32(map_to_cta(red_addr + ((slot * S + split) * BP + row) * 4u, owner), __uint_as_float(r[j]),
+                                         map_to_cta(bar_addr, owner));
+                        }
+                    }
+                }
+            }
+            if (MODE == MODE_ROPE && n_owned > 0) {
+                // this thread's column of the packed row: which head, which lane of it; what it needs of the
+                // step's index data and of the rotation table is fetched while the sums arrive
+                const int col = slab * BP + row;
+                const int hd = p.head_dim;
+                const int head = col / hd, d = col - head * hd;
+                const bool live = col < p.N;
+                const bool rotated = head < p.n_heads + p.n_kv_heads;
+                constexpr int AHEAD = 4;
+                float2 cs_ahead[AHEAD];
+                int sm_ahead[AHEAD];
+#pragma unroll
+                for (int slot = 0; slot < AHEAD; ++slot) {
+                    cs_ahead[slot] = make_float2(1.f, 0.f);
+                    sm_ahead[slot] = 0;
+                    if (slot < n_owned) {
+                        const int tok = slot * S + rank;
+                        int pos = p.positions[tok];
+                        pos = pos < 0 ? 0 : (pos >= p.table_rows ? p.table_rows - 1 : pos);    // the host keeps positions inside the table
+                        if (live && rotated) cs_ahead[slot] = *reinterpret_cast<const float2*>(p.table + (size_t)pos * hd + (d & ~1));
+                        if (p.k_pages != nullptr) sm_ahead[slot] = p.slot_mapping[tok];
+                    }
+                }
+                RowScale rs = {p.in_ssq, p.in_parts, p.in_inv_dim, p.in_eps};
+                if (p.in_ssq != nullptr) grid_dependency_wait();
+                float sc_ahead[AHEAD];
+#pragma unroll
+                for (int slot = 0; slot < AHEAD; ++slot) sc_ahead[slot] = slot < n_owned ? warp_row_scale(rs, slot * S + rank) : 1.f;
+                bool got = mbar_wait(&red_bar, 0, aborted);
+                if (!got && lane == 0) {
+                    abort_flag = 1;
+                    atomicExch(p.status, ERR_REDUCE_WAIT);
+                }
+                got = __all_sync(0xffffffffu, got);
+                if (got) {
+#pragma unroll 1
+                    for (int slot = 0; slot < n_owned; ++slot) {
+                        const int tok = slot * S + rank;
+                        float acc = 0.f;
+                        for (int sp = 0; sp < S; ++sp) acc += red[(slot * S + sp) * BP + row];      // in the order of the splits
+                        float2 cs = make_float2(1.f, 0.f);
+                        float sc = 1.f;
+                        int sm = 0;
+#pragma unroll
+                        for (int a = 0; a < AHEAD; ++a) if (a == slot) { cs = cs_ahead[a]; sc = sc_ahead[a]; sm = sm_ahead[a]; }
+                        if (slot >= AHEAD) {
+                            int pos = p.positions[tok];
+                            pos = pos < 0 ? 0 : (pos >= p.table_rows ? p.table_rows - 1 : pos);
+                            if (live && rotated) cs = *reinterpret_cast<const float2*>(p.table + (size_t)pos * hd + (d & ~1));
+                            if (p.k_pages != nullptr) sm = p.slot_mapping[tok];
+                            sc = warp_row_scale(rs, tok);
+                        }
+                        // the projection as it is when it passes through memory in bfloat16 (prompt portions),
+                        // then the row's scale, then the rotation of the pair (this lane and its neighbour)
+                        const float x = __bfloat162float(__float2bfloat16_rn(acc)) * sc;
+                        const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+                        float y = x;
+                        if (rotated) y = (d & 1) ? x * cs.x + other * cs.y : x * cs.x - other * cs.y;
+                        if (!live) continue;
+                        if (head < p.n_heads) {
+                            p.q_out[((size_t)tok * p.n_heads + head) * hd + d] = __float2bfloat16_rn(y);
+                        } else if (p.k_pages != nullptr) {
+                            const bool is_k = rotated;
+                            const int kvh = is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
+                            const int page = sm / p.page_size, in_page = sm - page * p.page_size;
+                            __nv_bfloat16* base = is_k ? p.k_pages : p.v_pages;
+                            base[(((size_t)page * p.n_kv_heads + kvh) * p.page_size + in_page) * hd + d] = __float2bfloat16_rn(y);
+                        }
+                    }
+                }
+            }
+            if (MODE == MODE_RESID && n_owned > 0) {
+                // what this CTA's tokens get added to does not come from the product: fetched while the sums arrive
+                const int col = slab * BP + row;
+                const float nw = col < p.N ? p.norm_w[col] : 0.f;
+                constexpr int AHEAD = 8;
+                float h_ahead[AHEAD];
+                grid_dependency_wait();
+#pragma unroll
+                for (int slot = 0; slot < AHEAD; ++slot)
+                    h_ahead[slot] = (slot < n_owned && col < p.N) ? p.h[(size_t)(slot * S + rank) * p.N + col] : 0.f;
+                bool got = mbar_wait(&red_bar, 0, aborted);
+                if (!got && lane == 0) {
+                    abort_flag = 1;
+                    atomicExch(p.status, ERR_REDUCE_WAIT);
+                }
+                got = __all_sync(0xffffffffu, got);
+                if (got) {
+#pragma unroll 1
+                    for (int slot = 0; slot < n_owned; ++slot) {
+                        const int tok = slot * S + rank;
+                        float acc = 0.f;
+                        for (int sp = 0; sp < S; ++sp) acc += red[(slot * S + sp) * BP + row];      // in the order of the splits
+                        float hv = 0.f;
+                        float h_old = 0.f;
+#pragma unroll
+                        for (int a = 0; a < AHEAD; ++a) if (a == slot) h_old = h_ahead[a];
+                        if (slot >= AHEAD && col < p.N) h_old = p.h[(size_t)tok * p.N + col];
+                        if (col < p.N) {
+                            // the product enters the stream as it does when it passes through memory in
+                            // bfloat16 (prompt portions, whose products the library takes): one arithmetic
+                            // however a request is cut into steps
+                            hv = h_old + __bfloat162float(__float2bfloat16_rn(acc));
+                            p.h[(size_t)tok * p.N + col] = hv;
+                            p.xw[(size_t)tok * p.N + col] = __float2bfloat16_rn(hv * nw);
+                        }
+                        const float ss = warp_sum(hv * hv);
+                        if (lane == 0) p.ssq[(size_t)tok * (gridDim.x * 4) + slab * 4 + quarter] = ss;
+                    }
+                }
+            }
         } else if (ok) {
             const size_t plane = (size_t)p.M * p.N;
 #pragma unroll
@@ -367,71 +552,6 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
                             else reinterpret_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(v);
                         }
                     }
-                }
-            }
-        }
-        if (MODE == MODE_RESID) {
-            // Count this CTA off on its slab's counter; the CTA that arrives last finds every split's
-            // partial sums in memory (each wrote, fenced, then counted).  All four warps keep the two
-            // appointments at the barrier whether their waits held or not; a CTA that failed does not
-            // count itself off, so nobody adds up what is not there (the status word says so).
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (quarter == 0 && lane == 0) {
-                int last = 0;
-                if (!abort_flag) {
-                    last = atomicAdd(p.counters + slab, 1) == p.splits - 1 ? 1 : 0;
-                    if (last) p.counters[slab] = 0;          // ready for the next launch
-                }
-                last_flag = last;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (last_flag) {
-                __threadfence();
-                const size_t plane = (size_t)p.M * p.N;
-                const int col = slab * BP + 4 * lane;        // a lane takes four columns, a warp the slab's 128
-                const bool in_range = col < p.N;             // N is a multiple of 4: all four or none
-                float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (in_range) w = *reinterpret_cast<const float4*>(p.norm_w + col);
-                const float* parts = reinterpret_cast<const float*>(p.out);
-                for (int tok = quarter; tok < p.M; tok += 4) {
-                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                    float4 hv = acc;
-                    if (in_range) {
-                        const float* src = parts + (size_t)tok * p.N + col;
-                        hv = *reinterpret_cast<const float4*>(p.h + (size_t)tok * p.N + col);
-                        int sp = 0;
-                        for (; sp + 4 <= p.splits; sp += 4) {           // four loads in flight, added in order
-                            const float4 a = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * plane));
-                            const float4 b = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + 1) * plane));
-                            const float4 c = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + 2) * plane));
-                            const float4 d = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + 3) * plane));
-                            acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
-                            acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
-                            acc.x += c.x; acc.y += c.y; acc.z += c.z; acc.w += c.w;
-                            acc.x += d.x; acc.y += d.y; acc.z += d.z; acc.w += d.w;
-                        }
-                        for (; sp < p.splits; ++sp) {
-                            const float4 a = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * plane));
-                            acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
-                        }
-                        // the product enters the stream as it does when it passes through memory in
-                        // bfloat16 (prompt portions, whose products the library takes): one arithmetic
-                        // however a request is cut into steps
-                        hv.x += __bfloat162float(__float2bfloat16_rn(acc.x));
-                        hv.y += __bfloat162float(__float2bfloat16_rn(acc.y));
-                        hv.z += __bfloat162float(__float2bfloat16_rn(acc.z));
-                        hv.w += __bfloat162float(__float2bfloat16_rn(acc.w));
-                        *reinterpret_cast<float4*>(p.h + (size_t)tok * p.N + col) = hv;
-                        __nv_bfloat162 lo = __floats2bfloat162_rn(hv.x * w.x, hv.y * w.y);
-                        __nv_bfloat162 hi = __floats2bfloat162_rn(hv.z * w.z, hv.w * w.w);
-                        uint2 raw;
-                        raw.x = *reinterpret_cast<unsigned*>(&lo);
-                        raw.y = *reinterpret_cast<unsigned*>(&hi);
-                        *reinterpret_cast<uint2*>(p.xw + (size_t)tok * p.N + col) = raw;
-                    }
-                    const float ss = warp_sum(hv.x * hv.x + hv.y * hv.y + hv.z * hv.z + hv.w * hv.w);
-                    if (lane == 0) p.ssq[(size_t)tok * gridDim.x + slab] = ss;
                 }
             }
         }
@@ -477,31 +597,8 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, in
     return rc == CUDA_SUCCESS ? TL_OK : TL_BAD_SIZE;
 }
 
-template <int BQ, int STAGES, int MODE = MODE_PLAIN>
-int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, int slabs, int splits, cudaStream_t s) {
-    constexpr size_t smem = (size_t)STAGES * (BP * BK * 2 + BQ * BK * 2) + 1024;
-    static_assert(MODE != MODE_GATED || (size_t)64 * (BQ + 1) * 4 <= (size_t)STAGES * (BP * BK * 2 + BQ * BK * 2), "the ups pass through the stages' memory");
-    auto kern = gemm_tcgen05_kernel<BQ, STAGES, MODE>;
-    static bool raised = false;
-    if (!raised) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        raised = true;
-    }
-    return (int)tl_launch(kern, dim3(slabs, splits), dim3(NTHREADS), smem, s, mw, ma, p);
-}
 
-}  // namespace
-
-// Launches a kernel whose only wait can never be satisfied and gives up after limit_ns (at most a
-// second): the status word receives code 109, waited_ns (device memory) the time the wait took.
-extern "C" int tl_wait_selftest(int* status, unsigned long long limit_ns, unsigned long long* waited_ns, void* stream) {
-    if (status == nullptr || waited_ns == nullptr || limit_ns == 0 || limit_ns > 1000ull * 1000ull * 1000ull) return TL_BAD_SIZE;
-    return (int)tl_launch(wait_selftest_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, status, limit_ns, waited_ns);
-}
-
-// How many K splits the kernel uses for M rows against a [N, K] weight.
-extern "C" int tl_gemm_tcgen05_splits(int M, int N, int K) {
+int tl_gemm_tcgen05_splits_impl(int M, int N, int K) {
     // Two CTAs fit an SM; all CTAs of a launch should be resident at once (one wave), because a
     // second, partly filled wave streams at a fraction of the bandwidth.  So: as many splits as
     // keep slabs * splits within 2 * 148, each with at least four stages of work.  (Fewer splits
@@ -517,6 +614,61 @@ extern "C" int tl_gemm_tcgen05_splits(int M, int N, int K) {
     const int per = (k_blocks + splits - 1) / splits;
     return (k_blocks + per - 1) / per;                          // no empty split
 }
+
+template <int BQ, int STAGES, int MODE = MODE_PLAIN>
+int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, int slabs, int splits, cudaStream_t s) {
+    // the residual form keeps, behind the stages, the rows that the other CTAs of its cluster send it
+    constexpr size_t red_bytes = (MODE == MODE_RESID || MODE == MODE_ROPE) ? (size_t)(BQ + 8) * BP * 4 : 0;
+    constexpr size_t smem = (size_t)STAGES * (BP * BK * 2 + BQ * BK * 2) + red_bytes + 1024;
+    static_assert(MODE != MODE_GATED || (size_t)64 * (BQ + 1) * 4 <= (size_t)STAGES * (BP * BK * 2 + BQ * BK * 2), "the ups pass through the stages' memory");
+    auto kern = gemm_tcgen05_kernel<BQ, STAGES, MODE>;
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        raised = true;
+    }
+    if (MODE == MODE_RESID || MODE == MODE_ROPE) {
+        // the splits of a slab as one cluster (at most 8 CTAs, the portable size)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(slabs, splits);
+        cfg.blockDim = dim3(NTHREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 1;
+        attr[1].val.clusterDim.y = (unsigned)splits;
+        attr[1].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 2;
+        return (int)cudaLaunchKernelEx(&cfg, kern, mw, ma, p);
+    }
+    return (int)tl_launch(kern, dim3(slabs, splits), dim3(NTHREADS), smem, s, mw, ma, p);
+}
+
+// K splits of the residual form: as the plain form has them, but no more than a cluster holds
+int residual_splits(int M, int N, int K) {
+    int splits = tl_gemm_tcgen05_splits_impl(M, N, K);
+    if (splits > 8) splits = 8;
+    const int k_blocks = (K + BK - 1) / BK;
+    const int per = (k_blocks + splits - 1) / splits;
+    return (k_blocks + per - 1) / per;
+}
+
+}  // namespace
+
+// Launches a kernel whose only wait can never be satisfied and gives up after limit_ns (at most a
+// second): the status word receives code 109, waited_ns (device memory) the time the wait took.
+extern "C" int tl_wait_selftest(int* status, unsigned long long limit_ns, unsigned long long* waited_ns, void* stream) {
+    if (status == nullptr || waited_ns == nullptr || limit_ns == 0 || limit_ns > 1000ull * 1000ull * 1000ull) return TL_BAD_SIZE;
+    return (int)tl_launch(wait_selftest_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, status, limit_ns, waited_ns);
+}
+
+// How many K splits the kernel uses for M rows against a [N, K] weight.
+extern "C" int tl_gemm_tcgen05_splits(int M, int N, int K) { return tl_gemm_tcgen05_splits_impl(M, N, K); }
 
 // 1 if the kernel takes this problem: at most 64 rows, K a multiple of 8 (TMA wants 16-byte row
 // pitches), operands 16-byte aligned.
@@ -554,28 +706,23 @@ extern "C" int tl_gemm_tcgen05(const void* A, const void* W, void* out, int out_
     return launch<64, 4>(mw, ma, p, slabs, splits, s);
 }
 
-// How many 128-row slabs of W the kernels cut N into (the width of the residual form's `ssq` and `counters`).
-extern "C" int tl_gemm_tcgen05_slabs(int N) { return (N + BP - 1) / BP; }
+// 1 if the residual form takes this problem: what tl_gemm_tcgen05 takes.
+extern "C" int tl_gemm_tcgen05_residual_supports(int M, int N, int K) { return tl_gemm_tcgen05_supports(M, N, K); }
 
-// 1 if the residual form takes this problem: what tl_gemm_tcgen05 takes, and N a multiple of 4
-// (the CTA that finishes a slab reads and writes four columns at a time).
-extern "C" int tl_gemm_tcgen05_residual_supports(int M, int N, int K) {
-    return (tl_gemm_tcgen05_supports(M, N, K) && N % 4 == 0) ? 1 : 0;
-}
+// Width of `ssq` for a weight of N rows: one part per 32 columns of every 128-row slab.
+extern "C" int tl_gemm_tcgen05_residual_parts(int N) { return 4 * ((N + BP - 1) / BP); }
 
-// h[M, N] += A[M, K] . W[N, K]^T (float32, in place); xw[M, N] = bf16(h * norm_w);
-// ssq[M, slabs] = every slab's share of sum over the row of h^2.  partial: [splits, M, N] float32 scratch
-// with splits = tl_gemm_tcgen05_splits(M, N, K); counters: [slabs] ints, zero before the first launch
-// (every launch leaves them zero).  Launches that share `counters` must not overlap on the device.
-extern "C" int tl_gemm_tcgen05_residual(const void* A, const void* W, float* partial, int* counters, float* h,
-                                        const float* norm_w, void* xw, float* ssq, int M, int N, int K, int splits,
-                                        int* status, void* stream) {
+// h[M, N] += bf16(A[M, K] . W[N, K]^T) (float32, in place); xw[M, N] = bf16(h * norm_w);
+// ssq[M, tl_gemm_tcgen05_residual_parts(N)] = the parts of every row's sum of h^2 (all of them are
+// written, zeros beyond N).  No scratch memory: the K splits of a slab are one cluster and add up
+// through shared memory.
+extern "C" int tl_gemm_tcgen05_residual(const void* A, const void* W, float* h, const float* norm_w, void* xw, float* ssq,
+                                        int M, int N, int K, int* status, void* stream) {
     if (M <= 0 || N <= 0) return TL_OK;
     if (!tl_gemm_tcgen05_residual_supports(M, N, K)) return TL_BAD_SIZE;
-    if (!aligned16(A) || !aligned16(W) || !aligned16(partial) || !aligned16(h) || !aligned16(norm_w) || !aligned16(xw) ||
-        status == nullptr || counters == nullptr || ssq == nullptr)
+    if (!aligned16(A) || !aligned16(W) || !aligned16(h) || !aligned16(norm_w) || !aligned16(xw) || status == nullptr || ssq == nullptr)
         return TL_BAD_ALIGN;
-    if (splits != tl_gemm_tcgen05_splits(M, N, K)) return TL_BAD_SIZE;
+    const int splits = residual_splits(M, N, K);
     const int slabs = (N + BP - 1) / BP;
     const int k_blocks = (K + BK - 1) / BK;
     const int bq = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
@@ -585,15 +732,63 @@ extern "C" int tl_gemm_tcgen05_residual(const void* A, const void* W, float* par
     rc = make_map(&ma, A, M, K, bq);
     if (rc != TL_OK) return rc;
     GemmParams p = {};
-    p.out = partial; p.status = status; p.M = M; p.N = N; p.K = K;
+    p.status = status; p.M = M; p.N = N; p.K = K;
     p.k_blocks_per_split = (k_blocks + splits - 1) / splits;
     p.out_is_f32 = 1;
     p.splits = splits;
-    p.counters = counters; p.h = h; p.norm_w = norm_w; p.xw = (__nv_bfloat16*)xw; p.ssq = ssq;
+    p.h = h; p.norm_w = norm_w; p.xw = (__nv_bfloat16*)xw; p.ssq = ssq;
     cudaStream_t s = (cudaStream_t)stream;
-    if (bq == 16) return launch<16, 6, MODE_RESID>(mw, ma, p, slabs, splits, s);
-    if (bq == 32) return launch<32, 5, MODE_RESID>(mw, ma, p, slabs, splits, s);
-    return launch<64, 4, MODE_RESID>(mw, ma, p, slabs, splits, s);
+    // (a stage less than the plain form: the rows that the cluster sends need their room)
+    if (bq == 16) return launch<16, 5, MODE_RESID>(mw, ma, p, slabs, splits, s);
+    if (bq == 32) return launch<32, 4, MODE_RESID>(mw, ma, p, slabs, splits, s);
+    return launch<64, 3, MODE_RESID>(mw, ma, p, slabs, splits, s);
+}
+
+
+// 1 if the rotary form takes this problem: what tl_gemm_tcgen05 takes for the stacked q/k/v weight,
+// and an even head_dim (adjacent lanes make the pairs).
+extern "C" int tl_gemm_tcgen05_rope_supports(int M, int n_heads, int n_kv_heads, int head_dim, int K) {
+    if (n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || (head_dim & 1)) return 0;
+    return tl_gemm_tcgen05_supports(M, (n_heads + 2 * n_kv_heads) * head_dim, K);
+}
+
+// The stacked q/k/v projection of A[M, K] (W: [(n_heads + 2 n_kv_heads) * head_dim, K]), every row
+// multiplied by its deferred scale (in_ssq null: none), q and k rotated by adjacent lanes with
+// (cos, sin) from table[positions[t]]; q goes to q_out [M, n_heads, head_dim], k and v to
+// pages[slot_mapping[t] / page_size][kv head][slot_mapping[t] % page_size] (k_pages, v_pages null: q only).
+extern "C" int tl_gemm_tcgen05_rope(const void* A, const void* W, const float* in_ssq, int in_parts, float in_inv_dim,
+                                    float in_eps, const int* positions, const float* table, int table_rows,
+                                    const int* slot_mapping, void* q_out, void* k_pages, void* v_pages, int M,
+                                    int n_heads, int n_kv_heads, int head_dim, int page_size, int K, int* status,
+                                    void* stream) {
+    if (M <= 0) return TL_OK;
+    if (!tl_gemm_tcgen05_rope_supports(M, n_heads, n_kv_heads, head_dim, K) || page_size <= 0 || table_rows <= 0) return TL_BAD_SIZE;
+    if ((k_pages == nullptr) != (v_pages == nullptr) || (k_pages != nullptr && slot_mapping == nullptr)) return TL_BAD_SIZE;
+    if (in_ssq != nullptr && in_parts < 1) return TL_BAD_SIZE;
+    if (!aligned16(A) || !aligned16(W) || !aligned16(table) || status == nullptr || positions == nullptr || q_out == nullptr)
+        return TL_BAD_ALIGN;
+    const int N = (n_heads + 2 * n_kv_heads) * head_dim;
+    const int splits = residual_splits(M, N, K);
+    const int slabs = (N + BP - 1) / BP;
+    const int k_blocks = (K + BK - 1) / BK;
+    const int bq = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    CUtensorMap mw, ma;
+    int rc = make_map(&mw, W, N, K, BP);
+    if (rc != TL_OK) return rc;
+    rc = make_map(&ma, A, M, K, bq);
+    if (rc != TL_OK) return rc;
+    GemmParams p = {};
+    p.status = status; p.M = M; p.N = N; p.K = K;
+    p.k_blocks_per_split = (k_blocks + splits - 1) / splits;
+    p.splits = splits;
+    p.in_ssq = in_ssq; p.in_parts = in_parts; p.in_inv_dim = in_inv_dim; p.in_eps = in_eps;
+    p.positions = positions; p.table = table; p.table_rows = table_rows; p.slot_mapping = slot_mapping;
+    p.q_out = (__nv_bfloat16*)q_out; p.k_pages = (__nv_bfloat16*)k_pages; p.v_pages = (__nv_bfloat16*)v_pages;
+    p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.page_size = page_size;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (bq == 16) return launch<16, 5, MODE_ROPE>(mw, ma, p, slabs, splits, s);
+    if (bq == 32) return launch<32, 4, MODE_ROPE>(mw, ma, p, slabs, splits, s);
+    return launch<64, 3, MODE_ROPE>(mw, ma, p, slabs, splits, s);
 }
 
 // 1 if the gated form takes this problem (W is [2 * hidden, K]) and is the better choice: what

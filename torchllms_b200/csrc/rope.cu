@@ -13,18 +13,6 @@
 // (the norm of torchllms/models/networks.py:195-200, applied after the product instead of before it).
 #include "common.cuh"
 
-struct RowScale {
-    const float* ssq;
-    int parts;
-    float inv_dim, eps;
-};
-__device__ __forceinline__ float row_scale(const RowScale& rs, long long row) {
-    if (rs.ssq == nullptr) return 1.f;
-    float v = 0.f;
-    for (int q = 0; q < rs.parts; ++q) v += __ldcg(rs.ssq + row * rs.parts + q);
-    return rsqrtf(v * rs.inv_dim + rs.eps);
-}
-
 // qkv holds `splits` planes `plane` elements apart (partial sums of a split-K product), summed first
 template <typename TI, typename T>
 __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int splits, long long plane,
@@ -36,7 +24,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int splits, lon
     grid_launch_dependents();
     grid_dependency_wait();
     const int t = blockIdx.x;
-    const float sc = row_scale(rs, t);
+    const float sc = warp_row_scale(rs, t);        // (a CTA's threads all work on token t)
     const int half = head_dim >> 1;
     const int heads_per_cta = (n_heads + 2 * n_kv_heads + gridDim.y - 1) / gridDim.y;
     const int head_lo = blockIdx.y * heads_per_cta;
@@ -147,7 +135,7 @@ __global__ void rope_kv_write_vec_kernel(const TI* __restrict__ qkv, int splits,
     if (c_first < heads * per_head && c_first / per_head < n_heads + n_kv_heads)
         load8(cs + ((c_first - (c_first / per_head) * per_head) << 3), r_first);
     grid_dependency_wait();
-    const float sc = row_scale(rs, t);
+    const float sc = warp_row_scale(rs, t);        // (a CTA's threads all work on token t)
     for (int c = c_first; c < heads * per_head; c += gridDim.y * blockDim.x) {
         const int head = c / per_head;
         const int off = (c - head * per_head) << 3;

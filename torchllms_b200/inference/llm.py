@@ -134,6 +134,7 @@ class LLM:
         self.eos_ids = list(eos_ids)
         self.eos_set = set(self.eos_ids)
         self.last_stats = None
+        self.last_trace = None
 
     def warmup(self, batch_sizes: Optional[Sequence[int]] = None, context_lengths: Optional[Sequence[int]] = None) -> int:
         """Record the CUDA graphs of decode steps for these numbers of running requests (default:
@@ -231,6 +232,7 @@ class LLM:
                     self.engine.release(r.handle)
                     r.handle = None
         self.last_stats = scheduler.stats
+        self.last_trace = scheduler.trace          # per step: (request's place in the call, tokens it brought)
         tok = self._load_tokenizer(required=False)
         out = []
         for r in requests:

@@ -101,6 +101,9 @@ class NativeOps:
     """The kernels as methods.  Libraries are compiled and loaded on first use."""
 
     PREFILL_MIN_Q = 96      # portions at least this long go to the tcgen05 prefill attention kernel
+    FUSE_MAX_ROWS = 16      # steps of at most this many tokens let a product finish the work that follows it
+                            # (residual sum and norm preparation, rotary encoding and cache write) in its own
+                            # kernel; with more rows the separate kernels are as fast or faster (measured)
 
     name = "native-sm100a"
 
@@ -119,9 +122,10 @@ class NativeOps:
         self._status = torch.zeros(4, dtype=torch.int32).pin_memory()
         self._mm_out_dtype: Optional[bool] = None
         self._profile = None
-        # the product that adds itself to the residual stream counts its K splits off per column slab
-        self._counters: Dict[int, torch.Tensor] = {}
+        # the tcgen05 prefill attention multiplies probabilities as one bfloat16 (1) or as value + remainder (2)
+        self.prefill_probability_parts = int(os.environ.get("TORCHLLMS_B200_PREFILL_PARTS", "2"))
         self.use_fused_residual = os.environ.get("TORCHLLMS_B200_NO_FUSED_RESIDUAL", "") not in ("1", "true")
+        self.use_fused_rope = os.environ.get("TORCHLLMS_B200_NO_FUSED_ROPE", "") not in ("1", "true")
 
     def graph_capturable(self, dtype: torch.dtype) -> bool:
         """Whether this library's launches for ``dtype`` may be recorded into a CUDA graph."""
@@ -226,15 +230,16 @@ class NativeOps:
             return False
         M, K = x.shape
         N = w.shape[0]
-        return (h.shape == (M, N) and x.is_contiguous() and w.is_contiguous() and x.data_ptr() % 16 == 0
-                and w.data_ptr() % 16 == 0
-                and self._lib("gemm_tcgen05").tl_gemm_tcgen05_residual_supports(M, N, K) == 1)
+        if not (h.shape == (M, N) and x.is_contiguous() and w.is_contiguous() and x.data_ptr() % 16 == 0
+                and w.data_ptr() % 16 == 0 and M <= self.FUSE_MAX_ROWS):
+            return False
+        return self._lib("gemm_tcgen05").tl_gemm_tcgen05_residual_supports(M, N, K) == 1
 
     @_timed
     def linear_residual_norm(self, pending: PendingProduct, h: torch.Tensor, weight: torch.Tensor, eps: float) -> RowScaled:
         """``h += bf16(x @ w.T)`` in place (float32; the product rounded as one that passes through
-        memory is) and the rows ``bf16(h * weight)`` with the parts of their sums of squares: one kernel in which the product's K splits are added up by whichever
-        CTA of a column slab finishes last."""
+        memory is) and the rows ``bf16(h * weight)`` with the parts of their sums of squares: one kernel in which the K splits of a column slab are one cluster of
+        CTAs that add up through each other's shared memory."""
         x, w = pending.x, pending.w
         _cuda_contig(x, "linear input", torch.bfloat16)
         _cuda_contig(w, "linear weight", torch.bfloat16)
@@ -245,20 +250,11 @@ class NativeOps:
         _need(w.shape[1] == K and h.shape == (M, N) and weight.numel() == N, "linear_residual_norm: shapes disagree")
         lib = self._lib("gemm_tcgen05")
         _need(lib.tl_gemm_tcgen05_residual_supports(M, N, K) == 1,
-              "the fused form takes bfloat16, at most 64 rows, K % 8 == 0 and a width that is a multiple of 4")
-        splits = lib.tl_gemm_tcgen05_splits(M, N, K)
-        slabs = lib.tl_gemm_tcgen05_slabs(N)
-        dev = x.device.index or 0
-        counters = self._counters.get(dev)
-        if counters is None or counters.numel() < slabs:
-            if counters is not None:
-                self._retired.append(counters)     # a captured graph may still point at it
-            counters = self._counters[dev] = torch.zeros(max(slabs, 1024), dtype=torch.int32, device=x.device)
-        partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+              "the fused form takes bfloat16, at most 64 rows and K % 8 == 0")
         xw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
-        ssq = torch.empty((M, slabs), dtype=torch.float32, device=x.device)
-        rc = lib.tl_gemm_tcgen05_residual(_ptr(x), _ptr(w), _ptr(partial), _ptr(counters), _ptr(h), _ptr(weight), _ptr(xw),
-                                          _ptr(ssq), M, N, K, splits, ctypes.c_void_p(self._status.data_ptr()), _stream())
+        ssq = torch.empty((M, lib.tl_gemm_tcgen05_residual_parts(N)), dtype=torch.float32, device=x.device)
+        rc = lib.tl_gemm_tcgen05_residual(_ptr(x), _ptr(w), _ptr(h), _ptr(weight), _ptr(xw), _ptr(ssq), M, N, K,
+                                          ctypes.c_void_p(self._status.data_ptr()), _stream())
         _check(rc, "gemm_tcgen05_residual")
         self.launches += 1
         return RowScaled(xw, ssq, N, float(eps))
@@ -394,8 +390,6 @@ class NativeOps:
         code = int(self._status[0])
         if code != 0:
             self._status[0] = 0
-            for counters in self._counters.values():       # a kernel that gave up may have left a count behind
-                counters.zero_()
             raise KernelError(f"a kernel gave up waiting (code {code}); its output is not valid")
 
     def wait_selftest(self, limit_ms: float = 1.0) -> float:
@@ -433,6 +427,13 @@ class NativeOps:
         """``qkv`` is ``[tokens, row]``, or float32 partial sums ``[splits, tokens, row]`` (then
         ``out_dtype`` is the dtype of q and of the pages), or a :class:`RowScaled` of either (every
         row is multiplied by its scale before it is rotated and stored)."""
+        if isinstance(qkv, PendingProduct):
+            fused = self._rope_in_the_product(qkv, positions, table, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim,
+                                              interleaved=interleaved, k_pages=k_pages, v_pages=v_pages,
+                                              slot_mapping=slot_mapping, page_size=page_size, out_dtype=out_dtype)
+            if fused is not None:
+                return fused
+            qkv = self.linear(qkv.x, qkv.w, partials_ok=True)      # (a RowScaled input gives a RowScaled product)
         rs = qkv if isinstance(qkv, RowScaled) else None
         if rs is not None:
             qkv = rs.x
@@ -463,6 +464,42 @@ class NativeOps:
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _DT[out_dtype], T, n_heads, n_kv_heads, head_dim,
             page_size, table.shape[0], 1 if interleaved else 0, *_scale_args(rs, T), _stream())
         _check(rc, "rope_kv_write")
+        self.launches += 1
+        return q
+
+    def _rope_in_the_product(self, pending: PendingProduct, positions, table, *, n_heads, n_kv_heads, head_dim, interleaved,
+                             k_pages, v_pages, slot_mapping, page_size, out_dtype) -> Optional[torch.Tensor]:
+        """The q/k/v projection, the rows' deferred scale, the rotation and the cache write as one
+        kernel (few rows, bfloat16, adjacent-lane pairing); ``None`` when that kernel does not apply."""
+        x, w = pending.x, pending.w
+        rs = x if isinstance(x, RowScaled) else None
+        if rs is not None:
+            x = rs.x
+        if not (self.use_fused_rope and self.use_tcgen05 and interleaved and x.dim() == 2 and x.is_cuda
+                and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and (out_dtype or x.dtype) == torch.bfloat16
+                and x.shape[0] <= self.FUSE_MAX_ROWS and x.is_contiguous() and w.is_contiguous()
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.shape == ((n_heads + 2 * n_kv_heads) * head_dim, x.shape[1])):
+            return None
+        M, K = x.shape
+        lib = self._lib("gemm_tcgen05")
+        if lib.tl_gemm_tcgen05_rope_supports(M, n_heads, n_kv_heads, head_dim, K) != 1:
+            return None
+        _cuda_contig(positions, "positions", torch.int32)
+        _cuda_contig(table, "rotary table", torch.float32)
+        _need(table.dim() == 3 and table.shape[1] == head_dim // 2 and table.shape[2] == 2 and positions.numel() == M,
+              "rotary table must be [positions, head_dim / 2, 2], one position per token")
+        if k_pages is not None:
+            _cuda_contig(k_pages, "k_pages", torch.bfloat16)
+            _cuda_contig(v_pages, "v_pages", torch.bfloat16)
+            _cuda_contig(slot_mapping, "slot_mapping", torch.int32)
+            _need(k_pages.shape[1:] == (n_kv_heads, page_size, head_dim) and v_pages.shape == k_pages.shape
+                  and slot_mapping.numel() == M, "pages must be [pages, n_kv_heads, page_size, head_dim], one cache slot per token")
+        q = torch.empty((M, n_heads, head_dim), dtype=torch.bfloat16, device=x.device)
+        rc = lib.tl_gemm_tcgen05_rope(
+            _ptr(x), _ptr(w), *_scale_args(rs, M), _ptr(positions), _ptr(table), table.shape[0],
+            _ptr(slot_mapping if k_pages is not None else None), _ptr(q), _ptr(k_pages), _ptr(v_pages), M, n_heads, n_kv_heads,
+            head_dim, page_size, K, ctypes.c_void_p(self._status.data_ptr()), _stream())
+        _check(rc, "gemm_tcgen05_rope")
         self.launches += 1
         return q
 
@@ -542,7 +579,7 @@ class NativeOps:
                 _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
                 _ptr(q_start), _ptr(kv_len), ctypes.c_void_p(self._status.data_ptr()), ctypes.c_longlong(q.shape[0]),
                 T, n_seqs, n_heads, n_kv_heads, head_dim, page_size, ctypes.c_longlong(k_pages.shape[0]), max_q_len,
-                int(window or 0), ctypes.c_float(scale), _stream())
+                int(window or 0), ctypes.c_float(scale), self.prefill_probability_parts, _stream())
             _check(rc, "paged_attention_prefill")
             self.launches += 1
             return out
