@@ -269,42 +269,6 @@ def test_rope_applies_a_deferred_row_scale(ops, dtype, H, KV, hd, P, interleaved
         assert not torch.allclose(unscaled.float(), q1.float(), atol=a)
 
 
-@pytest.mark.parametrize("T", [1, 8, 13, 16])
-@pytest.mark.parametrize("H,KV,hd,P,K", [(32, 8, 128, 16, 4096), (4, 2, 64, 16, 128), (6, 2, 48, 4, 104), (3, 1, 32, 8, 96), (2, 2, 256, 32, 264)])
-@pytest.mark.parametrize("scaled", [False, True])
-def test_projection_rotation_and_cache_write_in_one_kernel(ops, T, H, KV, hd, P, K, scaled):
-    """The q/k/v projection whose own kernel applies the rows' deferred scale, rotates q and k and
-    writes k and v into their pages: against the twin (product, then rotation), against the two
-    kernels it replaces, twice in a row, and without pages (a run that reads another run's cache)."""
-    n_pages, max_pos = 12, 300
-    row = (H + 2 * KV) * hd
-    x, w = rand((T, K), torch.bfloat16, 80 + T), rand((row, K), torch.bfloat16, 81, K ** -0.5)
-    pos = torch.randint(0, max_pos, (T,), dtype=torch.int32).cuda()
-    ang = torch.arange(max_pos).float()[:, None] * (1.0 / 100 ** (torch.arange(hd // 2).float() / (hd // 2)))[None, :]
-    table = torch.stack([ang.cos(), ang.sin()], -1).contiguous().cuda()
-    slots = torch.randperm(n_pages * P)[:T].to(torch.int32).cuda()
-    ssq, dim, eps = random_row_scale(T, 32, K, 11)
-    inp = RowScaled(x, ssq, dim, eps) if scaled else x
-    kw = dict(n_heads=H, n_kv_heads=KV, head_dim=hd, interleaved=True, slot_mapping=slots, page_size=P, out_dtype=torch.bfloat16)
-    pages = [torch.full((n_pages, KV, P, hd), 7.0, dtype=torch.bfloat16).cuda() for _ in range(6)]
-    before = ops.launches
-    q1 = ops.rope_kv_write(PendingProduct(inp, w), pos, table, k_pages=pages[0], v_pages=pages[1], **kw)
-    ops.check_status()
-    assert ops.launches - before == 1                                   # one kernel
-    q2 = TWIN.rope_kv_write(PendingProduct(inp, w), pos, table, k_pages=pages[2], v_pages=pages[3], **kw)
-    q3 = ops.rope_kv_write(ops.linear(inp, w, partials_ok=True), pos, table, k_pages=pages[4], v_pages=pages[5], **kw)   # the two kernels
-    a = dict(atol=3e-2, rtol=3e-2)
-    for got, want in ((q1, q2), (q1, q3), (pages[0], pages[2]), (pages[1], pages[3]), (pages[0], pages[4]), (pages[1], pages[5])):
-        torch.testing.assert_close(got.float(), want.float(), **a)
-    assert (pages[0] == 7.0).any()                                      # untouched slots stay untouched
-    again = ops.rope_kv_write(PendingProduct(inp, w), pos, table, k_pages=None, v_pages=None, **kw)
-    assert torch.equal(again, q1)
-    # the half-split pairing, float32, or many rows: the product is taken and the rotary kernel follows
-    before = ops.launches
-    ops.rope_kv_write(PendingProduct(inp, w), pos, table, k_pages=None, v_pages=None, **dict(kw, interleaved=False))
-    assert ops.launches - before == 2
-
-
 @pytest.mark.parametrize("M,hidden,K", [(1, 64, 64), (8, 192, 264), (16, 14336, 128), (33, 128, 4096), (64, 1024, 520), (9, 83, 40), (200, 256, 128)])
 @pytest.mark.parametrize("parts", [1, 32])
 def test_swiglu_applies_a_deferred_row_scale(ops, M, hidden, K, parts):

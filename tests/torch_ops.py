@@ -123,8 +123,6 @@ class TorchOps:
 
     def rope_kv_write(self, qkv, positions, table, *, n_heads, n_kv_heads, head_dim, interleaved,
                       k_pages, v_pages, slot_mapping, page_size, out_dtype=None):
-        if isinstance(qkv, PendingProduct):
-            qkv = self.linear(qkv.x, qkv.w)          # (a RowScaled input gives a RowScaled product)
         scale = None
         if isinstance(qkv, RowScaled):
             scale, qkv = qkv.scale(), qkv.x

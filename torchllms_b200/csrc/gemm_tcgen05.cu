@@ -36,12 +36,6 @@
 //             the gated epilogue here) multiply by rsqrt(sum / dim + eps): a product is linear in
 //             its input, so the scale may follow it.  No partial sum passes through global memory
 //             and no norm kernel stands between two products.
-//   rotary    the same cluster sums, for the stacked q/k/v projection: the CTA that owns a token has
-//             128 whole columns of its packed row, i.e. whole rotary pairs (adjacent lanes, 2i and
-//             2i + 1: Attention.forward and RotaryPositionalEmbeddings.forward,
-//             torchllms/models/networks.py:513-553, :332-352), applies the row's deferred scale,
-//             rotates q and k and writes q to its tensor and k, v into their cache pages: no kernel
-//             of its own for the rotation and the cache write.
 #include "common.cuh"
 #include <cuda.h>
 
@@ -189,18 +183,9 @@ struct GemmParams {
     const float* norm_w;    // [N]
     __nv_bfloat16* xw;      // [M, N]: bf16(h * norm_w)
     float* ssq;             // [M, 4 * slabs]: the share of sum(h^2) of every 32 columns
-    // rotary form: the product is the packed row [q heads | k heads | v heads] of every token (W is the
-    // stacked q/k/v weight); q leaves rotated, k rotated and v as it is go into their cache pages
-    const int* positions;   // [M]
-    const float* table;     // [table_rows, head_dim / 2, 2] (cos, sin)
-    const int* slot_mapping;  // [M]: page * page_size + slot; unused without pages
-    __nv_bfloat16* q_out;   // [M, n_heads, head_dim]
-    __nv_bfloat16* k_pages; // [pages, n_kv_heads, page_size, head_dim] or null (a run that reads another run's cache)
-    __nv_bfloat16* v_pages;
-    int n_heads, n_kv_heads, head_dim, page_size, table_rows;
 };
 
-enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_RESID = 2, MODE_ROPE = 3 };
+enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_RESID = 2 };
 
 // GATED: the slab is 64 rows of the gate projection and the 64 matching rows of the up projection
 // (two TMA boxes per stage), and the epilogue writes silu(gate) * up in bfloat16: the SwiGLU costs
@@ -223,7 +208,7 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
     __shared__ __align__(8) unsigned long long red_bar;      // residual form: counts the bytes other CTAs send here
     __shared__ float rstd_s[BQ];
     constexpr bool GATED = MODE == MODE_GATED;
-    constexpr bool CLUSTERED = MODE == MODE_RESID || MODE == MODE_ROPE;     // the K splits of a slab are one cluster
+    constexpr bool CLUSTERED = MODE == MODE_RESID;     // the K splits of a slab are one cluster
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slab = blockIdx.x, split = blockIdx.y;
@@ -338,6 +323,19 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
                 for (int tok = quarter * 32 + lane; tok < BQ; tok += 128) rstd_s[tok] = 1.f;
             }
         }
+        // residual form: what this CTA's own tokens need besides the sums (their rows of the stream, the
+        // norm's weight) is fetched now, while the products run
+        constexpr int AHEAD = 4;
+        const int own_row = quarter * 32 + lane;
+        const int own_col = slab * BP + own_row;
+        float pre_h[AHEAD], pre_nw = 0.f;
+        if (CLUSTERED && n_owned > 0) {
+            grid_dependency_wait();
+            if (own_col < p.N) pre_nw = p.norm_w[own_col];
+#pragma unroll
+            for (int slot = 0; slot < AHEAD; ++slot)
+                pre_h[slot] = (slot < n_owned && own_col < p.N) ? p.h[(size_t)(slot * S + rank) * p.N + own_col] : 0.f;
+        }
         if (n_kb > 0) {
             ok = mbar_wait(&accum_bar, 0, aborted);
             if (!ok && lane == 0) {
@@ -418,87 +416,9 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
                     }
                 }
             }
-            if (MODE == MODE_ROPE && n_owned > 0) {
-                // this thread's column of the packed row: which head, which lane of it; what it needs of the
-                // step's index data and of the rotation table is fetched while the sums arrive
-                const int col = slab * BP + row;
-                const int hd = p.head_dim;
-                const int head = col / hd, d = col - head * hd;
-                const bool live = col < p.N;
-                const bool rotated = head < p.n_heads + p.n_kv_heads;
-                constexpr int AHEAD = 4;
-                float2 cs_ahead[AHEAD];
-                int sm_ahead[AHEAD];
-#pragma unroll
-                for (int slot = 0; slot < AHEAD; ++slot) {
-                    cs_ahead[slot] = make_float2(1.f, 0.f);
-                    sm_ahead[slot] = 0;
-                    if (slot < n_owned) {
-                        const int tok = slot * S + rank;
-                        int pos = p.positions[tok];
-                        pos = pos < 0 ? 0 : (pos >= p.table_rows ? p.table_rows - 1 : pos);    // the host keeps positions inside the table
-                        if (live && rotated) cs_ahead[slot] = *reinterpret_cast<const float2*>(p.table + (size_t)pos * hd + (d & ~1));
-                        if (p.k_pages != nullptr) sm_ahead[slot] = p.slot_mapping[tok];
-                    }
-                }
-                RowScale rs = {p.in_ssq, p.in_parts, p.in_inv_dim, p.in_eps};
-                if (p.in_ssq != nullptr) grid_dependency_wait();
-                float sc_ahead[AHEAD];
-#pragma unroll
-                for (int slot = 0; slot < AHEAD; ++slot) sc_ahead[slot] = slot < n_owned ? warp_row_scale(rs, slot * S + rank) : 1.f;
-                bool got = mbar_wait(&red_bar, 0, aborted);
-                if (!got && lane == 0) {
-                    abort_flag = 1;
-                    atomicExch(p.status, ERR_REDUCE_WAIT);
-                }
-                got = __all_sync(0xffffffffu, got);
-                if (got) {
-#pragma unroll 1
-                    for (int slot = 0; slot < n_owned; ++slot) {
-                        const int tok = slot * S + rank;
-                        float acc = 0.f;
-                        for (int sp = 0; sp < S; ++sp) acc += red[(slot * S + sp) * BP + row];      // in the order of the splits
-                        float2 cs = make_float2(1.f, 0.f);
-                        float sc = 1.f;
-                        int sm = 0;
-#pragma unroll
-                        for (int a = 0; a < AHEAD; ++a) if (a == slot) { cs = cs_ahead[a]; sc = sc_ahead[a]; sm = sm_ahead[a]; }
-                        if (slot >= AHEAD) {
-                            int pos = p.positions[tok];
-                            pos = pos < 0 ? 0 : (pos >= p.table_rows ? p.table_rows - 1 : pos);
-                            if (live && rotated) cs = *reinterpret_cast<const float2*>(p.table + (size_t)pos * hd + (d & ~1));
-                            if (p.k_pages != nullptr) sm = p.slot_mapping[tok];
-                            sc = warp_row_scale(rs, tok);
-                        }
-                        // the projection as it is when it passes through memory in bfloat16 (prompt portions),
-                        // then the row's scale, then the rotation of the pair (this lane and its neighbour)
-                        const float x = __bfloat162float(__float2bfloat16_rn(acc)) * sc;
-                        const float other = __shfl_xor_sync(0xffffffffu, x, 1);
-                        float y = x;
-                        if (rotated) y = (d & 1) ? x * cs.x + other * cs.y : x * cs.x - other * cs.y;
-                        if (!live) continue;
-                        if (head < p.n_heads) {
-                            p.q_out[((size_t)tok * p.n_heads + head) * hd + d] = __float2bfloat16_rn(y);
-                        } else if (p.k_pages != nullptr) {
-                            const bool is_k = rotated;
-                            const int kvh = is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
-                            const int page = sm / p.page_size, in_page = sm - page * p.page_size;
-                            __nv_bfloat16* base = is_k ? p.k_pages : p.v_pages;
-                            base[(((size_t)page * p.n_kv_heads + kvh) * p.page_size + in_page) * hd + d] = __float2bfloat16_rn(y);
-                        }
-                    }
-                }
-            }
             if (MODE == MODE_RESID && n_owned > 0) {
-                // what this CTA's tokens get added to does not come from the product: fetched while the sums arrive
-                const int col = slab * BP + row;
-                const float nw = col < p.N ? p.norm_w[col] : 0.f;
-                constexpr int AHEAD = 8;
-                float h_ahead[AHEAD];
-                grid_dependency_wait();
-#pragma unroll
-                for (int slot = 0; slot < AHEAD; ++slot)
-                    h_ahead[slot] = (slot < n_owned && col < p.N) ? p.h[(size_t)(slot * S + rank) * p.N + col] : 0.f;
+                const int col = own_col;
+                const float nw = pre_nw;
                 bool got = mbar_wait(&red_bar, 0, aborted);
                 if (!got && lane == 0) {
                     abort_flag = 1;
@@ -514,7 +434,7 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
                         float hv = 0.f;
                         float h_old = 0.f;
 #pragma unroll
-                        for (int a = 0; a < AHEAD; ++a) if (a == slot) h_old = h_ahead[a];
+                        for (int a = 0; a < AHEAD; ++a) if (a == slot) h_old = pre_h[a];
                         if (slot >= AHEAD && col < p.N) h_old = p.h[(size_t)tok * p.N + col];
                         if (col < p.N) {
                             // the product enters the stream as it does when it passes through memory in
@@ -618,7 +538,7 @@ int tl_gemm_tcgen05_splits_impl(int M, int N, int K) {
 template <int BQ, int STAGES, int MODE = MODE_PLAIN>
 int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, int slabs, int splits, cudaStream_t s) {
     // the residual form keeps, behind the stages, the rows that the other CTAs of its cluster send it
-    constexpr size_t red_bytes = (MODE == MODE_RESID || MODE == MODE_ROPE) ? (size_t)(BQ + 8) * BP * 4 : 0;
+    constexpr size_t red_bytes = MODE == MODE_RESID ? (size_t)(BQ + 8) * BP * 4 : 0;
     constexpr size_t smem = (size_t)STAGES * (BP * BK * 2 + BQ * BK * 2) + red_bytes + 1024;
     static_assert(MODE != MODE_GATED || (size_t)64 * (BQ + 1) * 4 <= (size_t)STAGES * (BP * BK * 2 + BQ * BK * 2), "the ups pass through the stages' memory");
     auto kern = gemm_tcgen05_kernel<BQ, STAGES, MODE>;
@@ -628,7 +548,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, in
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
-    if (MODE == MODE_RESID || MODE == MODE_ROPE) {
+    if (MODE == MODE_RESID) {
         // the splits of a slab as one cluster (at most 8 CTAs, the portable size)
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(slabs, splits);
@@ -649,13 +569,15 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, in
     return (int)tl_launch(kern, dim3(slabs, splits), dim3(NTHREADS), smem, s, mw, ma, p);
 }
 
-// K splits of the residual form: as the plain form has them, but no more than a cluster holds
-int residual_splits(int M, int N, int K) {
+// K splits of the residual form: as the plain form has them, but no more than a cluster holds.
+// (Measured at batch 8 on the 8B shape, a step with clusters of 8 / 7 / 6 / 4 CTAs: 3.25 / 3.25 /
+// 3.28 / 3.39 ms.)
+int clustered_splits(int M, int N, int K) {
     int splits = tl_gemm_tcgen05_splits_impl(M, N, K);
     if (splits > 8) splits = 8;
     const int k_blocks = (K + BK - 1) / BK;
     const int per = (k_blocks + splits - 1) / splits;
-    return (k_blocks + per - 1) / per;
+    return (k_blocks + per - 1) / per;            // no empty split
 }
 
 }  // namespace
@@ -722,10 +644,10 @@ extern "C" int tl_gemm_tcgen05_residual(const void* A, const void* W, float* h, 
     if (!tl_gemm_tcgen05_residual_supports(M, N, K)) return TL_BAD_SIZE;
     if (!aligned16(A) || !aligned16(W) || !aligned16(h) || !aligned16(norm_w) || !aligned16(xw) || status == nullptr || ssq == nullptr)
         return TL_BAD_ALIGN;
-    const int splits = residual_splits(M, N, K);
     const int slabs = (N + BP - 1) / BP;
     const int k_blocks = (K + BK - 1) / BK;
     const int bq = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    const int splits = clustered_splits(M, N, K);
     CUtensorMap mw, ma;
     int rc = make_map(&mw, W, N, K, BP);
     if (rc != TL_OK) return rc;
@@ -744,52 +666,6 @@ extern "C" int tl_gemm_tcgen05_residual(const void* A, const void* W, float* h, 
     return launch<64, 3, MODE_RESID>(mw, ma, p, slabs, splits, s);
 }
 
-
-// 1 if the rotary form takes this problem: what tl_gemm_tcgen05 takes for the stacked q/k/v weight,
-// and an even head_dim (adjacent lanes make the pairs).
-extern "C" int tl_gemm_tcgen05_rope_supports(int M, int n_heads, int n_kv_heads, int head_dim, int K) {
-    if (n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || (head_dim & 1)) return 0;
-    return tl_gemm_tcgen05_supports(M, (n_heads + 2 * n_kv_heads) * head_dim, K);
-}
-
-// The stacked q/k/v projection of A[M, K] (W: [(n_heads + 2 n_kv_heads) * head_dim, K]), every row
-// multiplied by its deferred scale (in_ssq null: none), q and k rotated by adjacent lanes with
-// (cos, sin) from table[positions[t]]; q goes to q_out [M, n_heads, head_dim], k and v to
-// pages[slot_mapping[t] / page_size][kv head][slot_mapping[t] % page_size] (k_pages, v_pages null: q only).
-extern "C" int tl_gemm_tcgen05_rope(const void* A, const void* W, const float* in_ssq, int in_parts, float in_inv_dim,
-                                    float in_eps, const int* positions, const float* table, int table_rows,
-                                    const int* slot_mapping, void* q_out, void* k_pages, void* v_pages, int M,
-                                    int n_heads, int n_kv_heads, int head_dim, int page_size, int K, int* status,
-                                    void* stream) {
-    if (M <= 0) return TL_OK;
-    if (!tl_gemm_tcgen05_rope_supports(M, n_heads, n_kv_heads, head_dim, K) || page_size <= 0 || table_rows <= 0) return TL_BAD_SIZE;
-    if ((k_pages == nullptr) != (v_pages == nullptr) || (k_pages != nullptr && slot_mapping == nullptr)) return TL_BAD_SIZE;
-    if (in_ssq != nullptr && in_parts < 1) return TL_BAD_SIZE;
-    if (!aligned16(A) || !aligned16(W) || !aligned16(table) || status == nullptr || positions == nullptr || q_out == nullptr)
-        return TL_BAD_ALIGN;
-    const int N = (n_heads + 2 * n_kv_heads) * head_dim;
-    const int splits = residual_splits(M, N, K);
-    const int slabs = (N + BP - 1) / BP;
-    const int k_blocks = (K + BK - 1) / BK;
-    const int bq = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-    CUtensorMap mw, ma;
-    int rc = make_map(&mw, W, N, K, BP);
-    if (rc != TL_OK) return rc;
-    rc = make_map(&ma, A, M, K, bq);
-    if (rc != TL_OK) return rc;
-    GemmParams p = {};
-    p.status = status; p.M = M; p.N = N; p.K = K;
-    p.k_blocks_per_split = (k_blocks + splits - 1) / splits;
-    p.splits = splits;
-    p.in_ssq = in_ssq; p.in_parts = in_parts; p.in_inv_dim = in_inv_dim; p.in_eps = in_eps;
-    p.positions = positions; p.table = table; p.table_rows = table_rows; p.slot_mapping = slot_mapping;
-    p.q_out = (__nv_bfloat16*)q_out; p.k_pages = (__nv_bfloat16*)k_pages; p.v_pages = (__nv_bfloat16*)v_pages;
-    p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.page_size = page_size;
-    cudaStream_t s = (cudaStream_t)stream;
-    if (bq == 16) return launch<16, 5, MODE_ROPE>(mw, ma, p, slabs, splits, s);
-    if (bq == 32) return launch<32, 4, MODE_ROPE>(mw, ma, p, slabs, splits, s);
-    return launch<64, 3, MODE_ROPE>(mw, ma, p, slabs, splits, s);
-}
 
 // 1 if the gated form takes this problem (W is [2 * hidden, K]) and is the better choice: what
 // tl_gemm_tcgen05 takes, hidden a multiple of 64, and a shape that the plain form would not split

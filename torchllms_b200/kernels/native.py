@@ -101,9 +101,9 @@ class NativeOps:
     """The kernels as methods.  Libraries are compiled and loaded on first use."""
 
     PREFILL_MIN_Q = 96      # portions at least this long go to the tcgen05 prefill attention kernel
-    FUSE_MAX_ROWS = 16      # steps of at most this many tokens let a product finish the work that follows it
-                            # (residual sum and norm preparation, rotary encoding and cache write) in its own
-                            # kernel; with more rows the separate kernels are as fast or faster (measured)
+    FUSE_MAX_ROWS = 16      # steps of at most this many tokens let a product add itself to the residual stream and
+                            # prepare the norm that follows in its own kernel; with more rows product + norm
+                            # kernel are as fast or faster (measured: 16 rows equal, 32 and 64 rows 2 to 7 % slower)
 
     name = "native-sm100a"
 
@@ -125,7 +125,6 @@ class NativeOps:
         # the tcgen05 prefill attention multiplies probabilities as one bfloat16 (1) or as value + remainder (2)
         self.prefill_probability_parts = int(os.environ.get("TORCHLLMS_B200_PREFILL_PARTS", "2"))
         self.use_fused_residual = os.environ.get("TORCHLLMS_B200_NO_FUSED_RESIDUAL", "") not in ("1", "true")
-        self.use_fused_rope = os.environ.get("TORCHLLMS_B200_NO_FUSED_ROPE", "") not in ("1", "true")
 
     def graph_capturable(self, dtype: torch.dtype) -> bool:
         """Whether this library's launches for ``dtype`` may be recorded into a CUDA graph."""
@@ -427,13 +426,6 @@ class NativeOps:
         """``qkv`` is ``[tokens, row]``, or float32 partial sums ``[splits, tokens, row]`` (then
         ``out_dtype`` is the dtype of q and of the pages), or a :class:`RowScaled` of either (every
         row is multiplied by its scale before it is rotated and stored)."""
-        if isinstance(qkv, PendingProduct):
-            fused = self._rope_in_the_product(qkv, positions, table, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim,
-                                              interleaved=interleaved, k_pages=k_pages, v_pages=v_pages,
-                                              slot_mapping=slot_mapping, page_size=page_size, out_dtype=out_dtype)
-            if fused is not None:
-                return fused
-            qkv = self.linear(qkv.x, qkv.w, partials_ok=True)      # (a RowScaled input gives a RowScaled product)
         rs = qkv if isinstance(qkv, RowScaled) else None
         if rs is not None:
             qkv = rs.x
@@ -464,42 +456,6 @@ class NativeOps:
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _DT[out_dtype], T, n_heads, n_kv_heads, head_dim,
             page_size, table.shape[0], 1 if interleaved else 0, *_scale_args(rs, T), _stream())
         _check(rc, "rope_kv_write")
-        self.launches += 1
-        return q
-
-    def _rope_in_the_product(self, pending: PendingProduct, positions, table, *, n_heads, n_kv_heads, head_dim, interleaved,
-                             k_pages, v_pages, slot_mapping, page_size, out_dtype) -> Optional[torch.Tensor]:
-        """The q/k/v projection, the rows' deferred scale, the rotation and the cache write as one
-        kernel (few rows, bfloat16, adjacent-lane pairing); ``None`` when that kernel does not apply."""
-        x, w = pending.x, pending.w
-        rs = x if isinstance(x, RowScaled) else None
-        if rs is not None:
-            x = rs.x
-        if not (self.use_fused_rope and self.use_tcgen05 and interleaved and x.dim() == 2 and x.is_cuda
-                and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and (out_dtype or x.dtype) == torch.bfloat16
-                and x.shape[0] <= self.FUSE_MAX_ROWS and x.is_contiguous() and w.is_contiguous()
-                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.shape == ((n_heads + 2 * n_kv_heads) * head_dim, x.shape[1])):
-            return None
-        M, K = x.shape
-        lib = self._lib("gemm_tcgen05")
-        if lib.tl_gemm_tcgen05_rope_supports(M, n_heads, n_kv_heads, head_dim, K) != 1:
-            return None
-        _cuda_contig(positions, "positions", torch.int32)
-        _cuda_contig(table, "rotary table", torch.float32)
-        _need(table.dim() == 3 and table.shape[1] == head_dim // 2 and table.shape[2] == 2 and positions.numel() == M,
-              "rotary table must be [positions, head_dim / 2, 2], one position per token")
-        if k_pages is not None:
-            _cuda_contig(k_pages, "k_pages", torch.bfloat16)
-            _cuda_contig(v_pages, "v_pages", torch.bfloat16)
-            _cuda_contig(slot_mapping, "slot_mapping", torch.int32)
-            _need(k_pages.shape[1:] == (n_kv_heads, page_size, head_dim) and v_pages.shape == k_pages.shape
-                  and slot_mapping.numel() == M, "pages must be [pages, n_kv_heads, page_size, head_dim], one cache slot per token")
-        q = torch.empty((M, n_heads, head_dim), dtype=torch.bfloat16, device=x.device)
-        rc = lib.tl_gemm_tcgen05_rope(
-            _ptr(x), _ptr(w), *_scale_args(rs, M), _ptr(positions), _ptr(table), table.shape[0],
-            _ptr(slot_mapping if k_pages is not None else None), _ptr(q), _ptr(k_pages), _ptr(v_pages), M, n_heads, n_kv_heads,
-            head_dim, page_size, K, ctypes.c_void_p(self._status.data_ptr()), _stream())
-        _check(rc, "gemm_tcgen05_rope")
         self.launches += 1
         return q
 

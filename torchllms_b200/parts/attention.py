@@ -66,10 +66,7 @@ class PagedAttention(Mixer):
 
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         ops = self.env.ops
-        if self.position.takes_pending_product:
-            qkv = PendingProduct(x, self.wqkv)             # the encoding's kernel may take the projection itself
-        else:
-            qkv = ops.linear(x, self.wqkv, partials_ok=True)   # the encoding adds up split-K partial sums
+        qkv = ops.linear(x, self.wqkv, partials_ok=True)   # the encoding adds up split-K partial sums
         q = self.position.encode_and_store(qkv, ctx, cache, self.n_heads, self.n_kv_heads, self.head_dim)
         common = dict(scale=self.scale, window=self.window, page_size=cache.page_size)
         nd, B = getattr(ctx, "n_decode", 0), ctx.n_seqs

@@ -124,8 +124,6 @@ class PositionEncoding(Part):
     encoding sets ``takes_row_scaled``, a :class:`~torchllms_b200.kernels.lazy.RowScaled`."""
 
     takes_row_scaled = False
-    takes_pending_product = False    # True: ``qkv`` may also be the q/k/v projection not yet taken (a PendingProduct,
-                                     # whose input may itself be a RowScaled): the encoding's kernel may take it itself
 
     def encode_and_store(self, qkv, ctx, cache, n_heads: int, n_kv_heads: int, head_dim: int):
         raise NotImplementedError

@@ -59,7 +59,6 @@ class RotaryEncoding(PositionEncoding):
 
     graph_safe = True
     takes_row_scaled = True      # the kernel scales every row before it rotates and stores it
-    takes_pending_product = True  # and, for the few rows of a decode step, takes the projection itself
 
     def __init__(self, env: BuildEnv, *, head_dim: int, theta: float,
                  scaling: Optional[Mapping[str, Any]] = None, pairing: str = "interleaved"):
