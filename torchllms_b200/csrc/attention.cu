@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(NT) paged_attention_kernel(const AttnParams p)
             const int kpos = k0 + j;
             float* kd = Ks + j * qpitch + v * VEC;
             float* vd = Vs + j * hd + v * VEC;
-            if (kpos < k_hi) {
+            if (kpos < k_hi && tl_check_page(table[kpos / p.page_size])) {     // (debug builds: a bad page reads as zeros)
                 const int page = table[kpos / p.page_size];
                 const size_t off = (((size_t)page * p.n_kv_heads + kvh) * p.page_size + kpos % p.page_size) * hd + v * VEC;
                 Vec16<T> kv, vv;

@@ -192,7 +192,8 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 3 : 2) attention_decode_ke
             int row = p.total_rows;
             if (kpos < k_hi) {
                 const int page = table[kpos >> p.page_shift];
-                row = (page * p.n_kv_heads + kvh) * p.page_size + (kpos & (p.page_size - 1));
+                if (tl_check_page(page))                           // (debug builds: a bad page reads as the zero fill)
+                    row = (page * p.n_kv_heads + kvh) * p.page_size + (kpos & (p.page_size - 1));
             }
 #pragma unroll
             for (int h = 0; h < HALVES; ++h) {

@@ -175,8 +175,8 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
                     blk = kpos / p.page_size;
                     slot = kpos - blk * p.page_size;
                 }
-                const size_t off = (size_t)table[blk] * page_stride + head_off + (size_t)slot * HD;
-                cp_async16(kd + j * PITCH, p.k_pages + off);
+                const size_t off = (size_t)(tl_check_page(table[blk]) ? table[blk] : 0) * page_stride + head_off + (size_t)slot * HD;
+                cp_async16(kd + j * PITCH, p.k_pages + off);      // (debug builds: a bad page is reported, page 0 read in its place)
                 cp_async16(vd + j * PITCH, p.v_pages + off);
             } else {
                 *reinterpret_cast<uint4*>(kd + j * PITCH) = make_uint4(0u, 0u, 0u, 0u);

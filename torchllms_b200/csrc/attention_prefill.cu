@@ -339,7 +339,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
                         int row = p.total_rows;
                         if (kpos < k_hi && kpos + p.box_rows > k_lo) {
                             const int page = table[kpos >> p.page_shift];
-                            row = (page * p.n_kv_heads + kvh) * p.page_size + (kpos & (p.page_size - 1));
+                            if (tl_check_page(page))               // (debug builds: a bad page reads as the zero fill)
+                                row = (page * p.n_kv_heads + kvh) * p.page_size + (kpos & (p.page_size - 1));
                         }
 #pragma unroll
                         for (int h = 0; h < HALVES; ++h) {

@@ -69,6 +69,46 @@ __device__ __forceinline__ float warp_max(float x) {
     return x;
 }
 
+// ---- debug builds (-DTL_DEBUG): every index that a kernel takes from the step's index data is
+// range-checked before it is used.  A bad one is not followed (the access is skipped or reads
+// zeros) and its kind is left in the library's debug word, which the host reads with
+// tl_debug_take(); nothing traps.  The limits that a kernel's arguments do not carry (pages of the
+// page tensor in use, rows of the stream) are set by the host before the launch, in stream order.
+// Release builds compile the checks away.
+enum : int { TL_DBG_TOKEN_ID = 901, TL_DBG_POSITION = 902, TL_DBG_SLOT = 903, TL_DBG_PAGE = 904, TL_DBG_ROW = 905 };
+#ifdef TL_DEBUG
+__device__ int tl_debug_word = 0;
+__device__ long long tl_debug_limits[2] = {0, 0};      // pages of the page tensor, rows of the stream (0: unknown)
+__device__ __forceinline__ bool tl_debug_ok(bool cond, int code) {
+    if (!cond) atomicCAS(&tl_debug_word, 0, code);
+    return cond;
+}
+__device__ __forceinline__ bool tl_check_page(long long page) {
+    return tl_debug_ok(page >= 0 && (tl_debug_limits[0] == 0 || page < tl_debug_limits[0]), TL_DBG_PAGE);
+}
+__device__ __forceinline__ bool tl_check_row(long long row) {
+    return tl_debug_ok(row >= 0 && (tl_debug_limits[1] == 0 || row < tl_debug_limits[1]), TL_DBG_ROW);
+}
+#define TL_CHECK(cond, code) tl_debug_ok((cond), (code))
+// which limit (0: pages, 1: rows), its value; ordered with the launches on `stream`
+extern "C" int tl_debug_set_limit(int which, long long value, void* stream) {
+    if (which < 0 || which > 1) return TL_BAD_SIZE;
+    return (int)cudaMemcpyToSymbolAsync(tl_debug_limits, &value, sizeof(value), which * sizeof(long long),
+                                        cudaMemcpyHostToDevice, (cudaStream_t)stream);
+}
+// the code of the first bad index since the last call (0: none); waits for the device
+extern "C" int tl_debug_take() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, tl_debug_word, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(tl_debug_word, &zero, sizeof(int));
+    return v;
+}
+#else
+__device__ __forceinline__ bool tl_check_page(long long) { return true; }
+__device__ __forceinline__ bool tl_check_row(long long) { return true; }
+#define TL_CHECK(cond, code) true
+#endif
+
 // ---- rows whose RMS normalisation was deferred: the kernel that produced them left the weighted rows
 // and, beside them, the parts of every row's sum of squares (one part per strip of columns that a
 // CTA of the producer owned).  Whoever ends the chain of products multiplies by

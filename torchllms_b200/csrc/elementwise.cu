@@ -19,6 +19,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
     grid_dependency_wait();
     const int t = blockIdx.x;
     int id = ids[t];
+    (void)TL_CHECK(id >= 0 && id < vocab, TL_DBG_TOKEN_ID);
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // the host rejects such ids; stay in bounds anyway
     const T* src = table + (size_t)id * dim;
     float* dst = out + (size_t)t * dim;
@@ -32,6 +33,7 @@ __global__ void embed_bf16x8_kernel(const int* __restrict__ ids, const __nv_bflo
     grid_dependency_wait();
     const int t = blockIdx.x;
     int id = ids[t];
+    (void)TL_CHECK(id >= 0 && id < vocab, TL_DBG_TOKEN_ID);
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
     const __nv_bfloat16* src = table + (size_t)id * dim;
     float* dst = out + (size_t)t * dim;
@@ -75,7 +77,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
     grid_launch_dependents();
     // the row index and the norm's weight do not come from the kernel before this one
     const int o = blockIdx.x;
-    const int r = rows ? rows[o] : o;
+    int r = rows ? rows[o] : o;
+    if (!tl_check_row(r)) r = 0;                     // (debug builds: a bad row is reported, row 0 read in its place)
     float4 w_first = make_float4(0.f, 0.f, 0.f, 0.f);
     if (VEC == 4 && threadIdx.x * 4 < dim) w_first = load4(weight + threadIdx.x * 4);
     grid_dependency_wait();

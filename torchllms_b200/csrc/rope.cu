@@ -30,6 +30,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int splits, lon
     const int head_lo = blockIdx.y * heads_per_cta;
     const int head_hi = min(n_heads + 2 * n_kv_heads, head_lo + heads_per_cta);
     int pos = positions[t];
+    (void)TL_CHECK(pos >= 0 && pos < table_rows, TL_DBG_POSITION);
     pos = pos < 0 ? 0 : (pos >= table_rows ? table_rows - 1 : pos);  // the host keeps positions inside the table
     const float* cs = table + (size_t)pos * head_dim;                 // [half][2]
     const int row = (n_heads + 2 * n_kv_heads) * head_dim;
@@ -37,11 +38,12 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int splits, lon
     const int n_rot_pairs = (n_heads + n_kv_heads) * half;
     const int n_pairs = head_hi * half;
     int page = 0, slot = 0;
-    const bool write = k_pages != nullptr;
+    bool write = k_pages != nullptr;
     if (write) {
         const int sm = slot_mapping[t];
         page = sm / page_size;
         slot = sm - page * page_size;
+        if (!(TL_CHECK(sm >= 0, TL_DBG_SLOT) && tl_check_page(page))) write = false;    // (debug builds: nothing is written there)
     }
     for (int p = head_lo * half + threadIdx.x; p < n_pairs; p += blockDim.x) {
         const int head = p / half;       // 0 .. H + 2 KV - 1 over the packed row
@@ -120,15 +122,17 @@ __global__ void rope_kv_write_vec_kernel(const TI* __restrict__ qkv, int splits,
     const int heads = n_heads + 2 * n_kv_heads;
     const int per_head = head_dim >> 3;
     int pos = positions[t];
+    (void)TL_CHECK(pos >= 0 && pos < table_rows, TL_DBG_POSITION);
     pos = pos < 0 ? 0 : (pos >= table_rows ? table_rows - 1 : pos);
     const float* cs = table + (size_t)pos * head_dim;
     const TI* src = qkv + (size_t)t * heads * head_dim;
-    const bool write = k_pages != nullptr;
+    bool write = k_pages != nullptr;
     int page = 0, slot = 0;
     if (write) {
         const int sm = slot_mapping[t];
         page = sm / page_size;
         slot = sm - page * page_size;
+        if (!(TL_CHECK(sm >= 0, TL_DBG_SLOT) && tl_check_page(page))) write = false;    // (debug builds: nothing is written there)
     }
     const int c_first = blockIdx.y * blockDim.x + threadIdx.x;
     float r_first[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};

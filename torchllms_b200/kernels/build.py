@@ -30,6 +30,14 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-lineinfo", "-std=c++17", "--shared", "-Xcompiler", "-fPIC",
 ]
+# TORCHLLMS_B200_DEBUG=1 builds every kernel with -DTL_DEBUG: indices that come from the step's
+# index data (cache slots, pages of a block table, rows to gather) are range-checked on the device
+# before they are used; a bad one is skipped and reported through the library's debug word (see
+# common.cuh), never trapped on.  TORCHLLMS_B200_NVCC_FLAGS adds flags of the caller's own.  Either
+# changes the name of the built library, so builds of different kinds live side by side.
+if os.environ.get("TORCHLLMS_B200_DEBUG", "") not in ("", "0"):
+    NVCC_FLAGS.append("-DTL_DEBUG")
+NVCC_FLAGS += os.environ.get("TORCHLLMS_B200_NVCC_FLAGS", "").split()
 # libraries that need more than the CUDA runtime
 EXTRA_LINK: Dict[str, List[str]] = {}
 

@@ -122,13 +122,22 @@ class NativeOps:
         self._status = torch.zeros(4, dtype=torch.int32).pin_memory()
         self._mm_out_dtype: Optional[bool] = None
         self._profile = None
+        # TORCHLLMS_B200_DEBUG=1: the libraries are built with -DTL_DEBUG (see kernels/build.py); kernels
+        # range-check the indices they are given and report through a word that check_status() reads
+        self.debug = os.environ.get("TORCHLLMS_B200_DEBUG", "") not in ("", "0")
         # the tcgen05 prefill attention multiplies probabilities as one bfloat16 (1) or as value + remainder (2)
         self.prefill_probability_parts = int(os.environ.get("TORCHLLMS_B200_PREFILL_PARTS", "2"))
         self.use_fused_residual = os.environ.get("TORCHLLMS_B200_NO_FUSED_RESIDUAL", "") not in ("1", "true")
 
     def graph_capturable(self, dtype: torch.dtype) -> bool:
-        """Whether this library's launches for ``dtype`` may be recorded into a CUDA graph."""
-        return True
+        """Whether this library's launches for ``dtype`` may be recorded into a CUDA graph (not in
+        debug mode: the limits its checks compare with are copied in from the host before launches)."""
+        return not self.debug
+
+    def _debug_limit(self, lib_name: str, which: int, value: int) -> None:
+        """Debug builds: tell a library how many pages (0) or rows (1) the tensors of the next launch have."""
+        if self.debug:
+            _check(self._lib(lib_name).tl_debug_set_limit(which, ctypes.c_longlong(int(value)), _stream()), "debug limit")
 
     # ------------------------------------------------------------ libraries
     def prepare(self, dtype: torch.dtype, sampling: bool = True) -> None:
@@ -212,6 +221,7 @@ class NativeOps:
         out = torch.empty((n_out, dim), dtype=out_dtype, device=h.device)
         ssq = torch.empty((n_out, 1), dtype=torch.float32, device=h.device) if deferred else None
         write_back = 1 if (delta is not None and rows is None) else 0
+        self._debug_limit("elementwise", 1, h.shape[0])
         rc = self._lib("elementwise").tl_rmsnorm(
             _ptr(h), _ptr(delta), _DT[delta.dtype] if delta is not None else 0, splits, ctypes.c_longlong(plane),
             _ptr(weight), _ptr(out), _DT[out_dtype], _ptr(rows), n_out, dim, ctypes.c_float(eps), write_back,
@@ -390,6 +400,15 @@ class NativeOps:
         if code != 0:
             self._status[0] = 0
             raise KernelError(f"a kernel gave up waiting (code {code}); its output is not valid")
+        if self.debug:
+            from .build import loaded_libraries
+            kinds = {901: "a token id outside the vocabulary", 902: "a position outside the rotary table",
+                     903: "a negative cache slot", 904: "a page outside the page tensor", 905: "a row outside the stream"}
+            for name in loaded_libraries():
+                code = self._lib(name).tl_debug_take()
+                if code != 0:
+                    raise KernelError(f"debug build: a kernel of {name} was given {kinds.get(code, 'a bad index')} "
+                                      f"(code {code}); it skipped the access")
 
     def wait_selftest(self, limit_ms: float = 1.0) -> float:
         """Run a kernel whose only mbarrier wait nothing will ever satisfy, with a limit of
@@ -450,6 +469,8 @@ class NativeOps:
                   "pages must be [pages, n_kv_heads, page_size, head_dim]")
             _need(slot_mapping.numel() == T, "one cache slot per token")
         q = torch.empty((T, n_heads, head_dim), dtype=out_dtype, device=qkv.device)
+        if k_pages is not None:
+            self._debug_limit("rope", 0, k_pages.shape[0])
         rc = self._lib("rope").tl_rope_kv_write(
             _ptr(qkv), _DT[qkv.dtype], splits, _ptr(positions), _ptr(table),
             _ptr(slot_mapping if k_pages is not None else None),
@@ -531,6 +552,7 @@ class NativeOps:
               "and a power-of-two page size")
         if prefill_ok:
             lib = self._lib("attention_prefill")
+            self._debug_limit("attention_prefill", 0, k_pages.shape[0])
             rc = lib.tl_paged_attention_prefill(
                 _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
                 _ptr(q_start), _ptr(kv_len), ctypes.c_void_p(self._status.data_ptr()), ctypes.c_longlong(q.shape[0]),
@@ -545,6 +567,7 @@ class NativeOps:
                                               int(allow_split), ctypes.byref(n_splits), ctypes.byref(floats))
             _check(rc, "attention_decode_plan")
             ws = self._scratch(q.device, floats.value)
+            self._debug_limit("attention_decode", 0, k_pages.shape[0])
             rc = lib.tl_paged_attention_decode(
                 _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
                 _ptr(q_start), _ptr(kv_len), _ptr(ws), ctypes.c_void_p(self._status.data_ptr()), T, n_seqs,
@@ -557,6 +580,7 @@ class NativeOps:
                                            1 if allow_split else 0, ctypes.byref(n_splits), ctypes.byref(floats))
             _check(rc, "attention_mma_plan")
             ws = self._scratch(q.device, floats.value)
+            self._debug_limit("attention_mma", 0, k_pages.shape[0])
             rc = lib.tl_paged_attention_mma(
                 _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
                 _ptr(q_start), _ptr(kv_len), _ptr(ws), T, n_seqs, n_heads, n_kv_heads, head_dim,
@@ -569,6 +593,7 @@ class NativeOps:
                                        1 if allow_split else 0, ctypes.byref(n_splits), ctypes.byref(floats))
             _check(rc, "attention_plan")
             ws = self._scratch(q.device, floats.value)
+            self._debug_limit("attention", 0, k_pages.shape[0])
             rc = lib.tl_paged_attention(
                 _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
                 _ptr(q_start), _ptr(kv_len), _ptr(ws), _DT[q.dtype], T, n_seqs, n_heads, n_kv_heads, head_dim,
