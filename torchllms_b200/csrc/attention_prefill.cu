@@ -54,8 +54,10 @@ namespace {
 constexpr int BM = 128;                 // rows of a query tile (tokens of one head)
 constexpr int QT = 2;                   // query tiles per CTA: they share every K and V tile that is loaded
 constexpr int BN = 128;                 // keys per tile
-constexpr int W_COPY = 4 * QT, W_ISSUE = 4 * QT + 1;   // warps 0 .. 4 QT - 1 are the softmax (four to a query tile), then one copies, two issue
-constexpr int NTHREADS = (4 * QT + 3) * 32;
+constexpr int RT = 2;                   // threads that share a query row in the softmax (warps w, w + 4, ..: same TMEM lanes);
+                                        // 4 measured the same speed: the softmax is bound by instruction issue, not by latency
+constexpr int W_COPY = 4 * RT, W_ISSUE = 4 * RT + 1;   // warps 0 .. 4 RT - 1 are the softmax, then one copies, two issue
+constexpr int NTHREADS = (4 * RT + 3) * 32;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LAG = 8.f;              // how far (in powers of two) the maximum in use may lag
 constexpr unsigned long long WAIT_NS = 2000ull * 1000ull * 1000ull;
@@ -204,6 +206,7 @@ struct Tail {                   // what lies behind the tiles in shared memory
     unsigned long long s_full[QT], p_full[QT], pv_done[QT];
     unsigned tmem_base_slot;
     int failed_flag;
+    float swap[2][RT][BM];      // [parity of the softmax's step][part of the row][row]
 };
 
 // What a query tile has to do with the CTA's key tiles: it works on tiles first .. last - 1.
@@ -211,7 +214,9 @@ struct TileRange {
     int rows, first, last;
 };
 
-template <int HD, int STAGES>
+// PARTS: 2 = probabilities as value + remainder (two products, 16 bits of every probability kept);
+// 1 = probabilities rounded to bfloat16 once (one product).
+template <int HD, int STAGES, int PARTS>
 __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                        const __grid_constant__ CUtensorMap map_v,
                                                                        const PrefillParams p) {
@@ -235,11 +240,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
     unsigned long long (&pv_done)[QT] = tail.pv_done;
     unsigned& tmem_base_slot = tail.tmem_base_slot;
     int& failed_flag = tail.failed_flag;
+    float (&swap_max)[2][RT][BM] = tail.swap;                // the threads of a row tell each other their maximum
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
         failed_flag = 0;
-        mbar_init(&q_full, 4 * QT);
+        mbar_init(&q_full, 4 * RT);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&k_empty[s], QT);       // every query tile's issuer lets go of a stage
@@ -248,7 +254,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
         }
         for (int t = 0; t < QT; ++t) {
             mbar_init(&s_full[t], 1);
-            mbar_init(&p_full[t], 4);             // the four warps of the tile's softmax
+            mbar_init(&p_full[t], 4 * RT);
             mbar_init(&pv_done[t], 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -395,8 +401,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
                     const unsigned long long vd0 = desc_mn_major(smem_u32(tiles + (STAGES + s) * KV_BYTES), HALF_BYTES);
                     const unsigned acc = j > first ? 1u : 0u;
 #pragma unroll
-                    for (int kk = 0; kk < BN / 16; ++kk)             // 16 keys on: 2048 bytes of V, 8 columns of P
-                        umma_ts(d_o, d_s + kk * 8, vd0 + kk * (2048 >> 4), id_o, kk > 0 ? 1u : acc);
+                    for (int part = 0; part < PARTS; ++part)         // value, then remainder
+#pragma unroll
+                        for (int kk = 0; kk < BN / 16; ++kk)         // 16 keys on: 2048 bytes of V, 8 columns of P
+                            umma_ts(d_o, d_s + part * (BN / 2) + kk * 8, vd0 + kk * (2048 >> 4), id_o,
+                                    (part > 0 || kk > 0) ? 1u : acc);
                     umma_commit(&pv_done[t]);        // the accumulator is up to date
                     umma_commit(&v_empty[s]);        // and this tile is done with the V stage
                 } else {
@@ -409,25 +418,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
             }
         }
     } else if (active) {
-        // ---- softmax: warps 0-3 serve query tile 0, warps 4-7 query tile 1; row r = TMEM lane r
-        // belongs to one thread, which walks the 128 scores of a key tile twice, in pieces of 32
-        // columns: once for the row's maximum, once to turn them into probabilities that go back
-        // where the scores were, two bfloat16 to a column (a piece of probabilities lands on
-        // columns whose scores were read before).  The two tiles' warps never wait for each other.
-        constexpr int PIECE = 32;                            // score columns per tcgen05.ld
-        const int t = warp >> 2;                             // the query tile this warp serves
+        // ---- softmax: row r = TMEM lane r of either query tile; this thread has the keys
+        // HN half .. HN half + HN - 1 of every key tile (half: which of the row's RT threads this is)
+        constexpr int HN = BN / RT;                          // keys per thread and tile
+        constexpr int HO = HD / RT;                          // accumulator columns per thread
+        const int half = warp >> 2;
         const int r = (warp & 3) * 32 + lane;
         const unsigned lane_addr = tmem + ((unsigned)((warp & 3) * 32) << 16);
-        const int rows = range[t].rows, first = range[t].first, last = range[t].last;
-        const unsigned col_s = COL_S + t * BN, col_o = COL_O + t * BN;
-        // this thread's query row goes into shared memory in the layout of a K tile: rows of
-        // 128 bytes (64 elements), 16-byte chunks swizzled with the row
-        {
-            const bool valid = r < rows;
-            const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + tok0 + t * BM + r) * p.n_heads + head) * HD);
+        const int pair_barrier = 1 + (warp & 3);             // named barrier of the RT warps that share 32 rows
+        // this thread's half of its query rows goes into shared memory in the layout of a K tile:
+        // rows of 128 bytes (64 elements), 16-byte chunks swizzled with the row
 #pragma unroll
-            for (int chunk = 0; chunk < HD / 8; ++chunk) {
-                const uint4 v = valid ? src[chunk] : make_uint4(0u, 0u, 0u, 0u);
+        for (int t = 0; t < QT; ++t) {
+            const bool valid = r < range[t].rows;
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + tok0 + t * BM + r) * p.n_heads + head) * HD + half * HO);
+#pragma unroll
+            for (int i = 0; i < HO / 8; ++i) {
+                const uint4 v = valid ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+                const int chunk = (half * HO) / 8 + i;              // of the row: block chunk / 8, chunk % 8 within it
                 *reinterpret_cast<uint4*>(Qs + t * KV_BYTES + (chunk >> 3) * HALF_BYTES + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) = v;
             }
         }
@@ -435,127 +443,171 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
         __syncwarp();
         if (lane == 0) mbar_arrive(&q_full);
 
-        float m_used = -INFINITY, l_sum = 0.f;
-        const int t0 = qpos_base + tok0 + t * BM;            // position of the tile's first row
-        const int qpos = t0 + (r < rows ? r : rows - 1);     // idle rows follow the last real one
-        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+        // The state of the two query tiles lives in scalars picked by hand, and the loop over the
+        // tiles is not unrolled: one copy of the body, no indexed arrays, fewer registers.
+        static_assert(QT == 2, "the softmax keeps the state of two query tiles");
+        float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+        const int rows_a = range[0].rows, rows_b = range[1].rows;
+        const int first_a = range[0].first, first_b = range[1].first, last_a = range[0].last, last_b = range[1].last;
         bool ok = true;
-        for (int j = first; j < last && ok; ++j) {
+        int step = 0;                                        // counts the (key tile, query tile) pairs done: slot of the swap
+        // Once a wait has failed (ok = false) the loop only keeps its appointments at the pair's
+        // barrier: both warps of a pair pass it once per step whatever happens, so neither can be
+        // left waiting there.
+        for (int j = 0; j < n_tiles; ++j) {
             const int k0 = k_start + j * BN;
-            const int it = j - first;                        // how many key tiles this query tile has done
-            // (a wait's outcome is taken by the whole warp: the loads below need all of its lanes)
-            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], it & 1, failed));
-            if (!ok) break;
-            tc_fence_after();
-            // the whole key tile is visible to every row of this query tile?
-            const bool clear = k0 + BN - 1 <= t0 && (p.window <= 0 || k0 > t0 + rows - 1 - p.window);
-            // ---- first walk: the row's maximum
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll 1
+            for (int t = 0; t < QT; ++t) {
+                const int first = t ? first_b : first_a, last = t ? last_b : last_a, rows = t ? rows_b : rows_a;
+                if (j < first || j >= last) continue;
+                const int it = j - first;                    // how many tiles this query tile has done
+                const int slot = step & 1;
+                ++step;
+                float m_used = t ? m_b : m_a;
+                const int t0 = qpos_base + tok0 + t * BM;    // position of the tile's first row
+                const int qpos = t0 + (r < rows ? r : rows - 1);         // idle rows follow the last real one
+                const unsigned col_s = COL_S + t * BN, col_o = COL_O + t * BN;
+                // (a wait's outcome is taken by the whole warp: the loads below need all of its lanes)
+                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], it & 1, failed));
+                if (!ok) failed_flag = 1;
+                unsigned raw[HN];                            // the scores
+                float mine = -INFINITY;
+                if (ok) {
+                    tc_fence_after();
+                    tmem_ld<HN>(lane_addr + col_s + half * HN, raw);
+                    tmem_wait_ld();
+                    // the whole key tile is visible to every row of this query tile?
+                    const bool clear = k0 + BN - 1 <= t0 && (p.window <= 0 || k0 > t0 + rows - 1 - p.window);
+                    if (!clear) {
 #pragma unroll
-            for (int c = 0; c < BN / PIECE; ++c) {
-                unsigned raw[PIECE];
-                tmem_ld<PIECE>(lane_addr + col_s + c * PIECE, raw);
-                tmem_wait_ld();
-                if (!clear) {
-#pragma unroll
-                    for (int i = 0; i < PIECE; ++i) {
-                        const int kpos = k0 + c * PIECE + i;
-                        const bool vis = kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
-                        if (!vis) raw[i] = 0xff800000u;      // -inf
+                        for (int i = 0; i < HN; ++i) {
+                            const int kpos = k0 + half * HN + i;
+                            const bool vis = kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
+                            if (!vis) raw[i] = 0xff800000u;  // -inf
+                        }
                     }
-                }
+                    float mx0 = __uint_as_float(raw[0]), mx1 = __uint_as_float(raw[1]);
+                    float mx2 = __uint_as_float(raw[2]), mx3 = __uint_as_float(raw[3]);
 #pragma unroll
-                for (int i = 0; i < PIECE; i += 4) {
-                    mx0 = fmaxf(mx0, __uint_as_float(raw[i])); mx1 = fmaxf(mx1, __uint_as_float(raw[i + 1]));
-                    mx2 = fmaxf(mx2, __uint_as_float(raw[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(raw[i + 3]));
-                }
-            }
-            const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
-            const bool grow = m_new > m_used + LAG;          // also true for the first keys a row sees
-            const bool rescale = it > 0 && __any_sync(0xffffffffu, grow);
-            const float alpha = grow ? ex2(m_used - m_new) : 1.f;        // 0 for a row that had seen nothing
-            if (grow) m_used = m_new;
-            const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;   // nothing seen yet: keep exponents finite
-            const float2 nm2 = make_float2(-m_safe, -m_safe);
-            // ---- second walk: probabilities, a piece at a time
-            // (arithmetic two floats at a time, fma.f32x2 and add.f32x2 of this architecture)
-            float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
-#pragma unroll
-            for (int c = 0; c < BN / PIECE; ++c) {
-                unsigned raw[PIECE];
-                tmem_ld<PIECE>(lane_addr + col_s + c * PIECE, raw);
-                tmem_wait_ld();
-                if (!clear) {
-#pragma unroll
-                    for (int i = 0; i < PIECE; ++i) {
-                        const int kpos = k0 + c * PIECE + i;
-                        const bool vis = kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
-                        if (!vis) raw[i] = 0xff800000u;
+                    for (int i = 4; i < HN; i += 4) {
+                        mx0 = fmaxf(mx0, __uint_as_float(raw[i])); mx1 = fmaxf(mx1, __uint_as_float(raw[i + 1]));
+                        mx2 = fmaxf(mx2, __uint_as_float(raw[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(raw[i + 3]));
                     }
+                    mine = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
                 }
-                unsigned packed[PIECE / 2];
+                // The partner can be one step ahead at most (it stops at the next barrier until this
+                // thread gets there), so two slots, used in turn, are never overwritten unread.  Past the
+                // barrier both have their scores in registers: the probabilities may go where they were.
+                swap_max[slot][half][r] = mine;
+                asm volatile("bar.sync %0, %1;" ::"r"(pair_barrier), "n"(32 * RT) : "memory");
+                if (!ok) continue;
+                float both = mine;
 #pragma unroll
-                for (int i = 0; i < PIECE; i += 4) {
+                for (int o = 1; o < RT; ++o) both = fmaxf(both, swap_max[slot][(half + o) % RT][r]);
+                const float m_new = fmaxf(m_used, both * p.scale_log2);
+                const bool grow = m_new > m_used + LAG;      // also true for the first keys a row sees
+                const bool rescale = it > 0 && __any_sync(0xffffffffu, grow);
+                const float alpha = grow ? ex2(m_used - m_new) : 1.f;        // 0 for a row that had seen nothing
+                if (grow) m_used = m_new;
+                const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;   // nothing seen yet: keep exponents finite
+                // probabilities as value + remainder, two bfloat16 to a column: columns 32 half .. of the
+                // tile's buffer hold the values of this thread's keys, columns 64 + 32 half .. the remainders
+                unsigned hi[HN / 2], lo[HN / 2];
+                // (arithmetic two floats at a time, fma.f32x2 and add.f32x2 of this architecture: the softmax
+                // is bound by how many instructions it issues)
+                float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
+                const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_safe, -m_safe);
+                const float2 neg1 = make_float2(-1.f, -1.f);
+#pragma unroll
+                for (int i = 0; i < HN; i += 4) {
                     const float2 xa = __ffma2_rn(make_float2(__uint_as_float(raw[i]), __uint_as_float(raw[i + 1])), sc2, nm2);
                     const float2 xb = __ffma2_rn(make_float2(__uint_as_float(raw[i + 2]), __uint_as_float(raw[i + 3])), sc2, nm2);
                     const float2 ea = make_float2(ex2(xa.x), ex2(xa.y)), eb = make_float2(ex2(xb.x), ex2(xb.y));
                     la = __fadd2_rn(la, ea);
                     lb = __fadd2_rn(lb, eb);
-                    packed[i / 2] = pack_bf16(ea.x, ea.y);
-                    packed[i / 2 + 1] = pack_bf16(eb.x, eb.y);
+                    const __nv_bfloat162 ha = __floats2bfloat162_rn(ea.x, ea.y), hb = __floats2bfloat162_rn(eb.x, eb.y);
+                    hi[i / 2] = *reinterpret_cast<const unsigned*>(&ha);
+                    hi[i / 2 + 1] = *reinterpret_cast<const unsigned*>(&hb);
+                    if (PARTS == 2) {
+                        const float2 ra = __ffma2_rn(__bfloat1622float2(ha), neg1, ea);      // what the rounding left, exactly
+                        const float2 rb = __ffma2_rn(__bfloat1622float2(hb), neg1, eb);
+                        lo[i / 2] = pack_bf16(ra.x, ra.y);
+                        lo[i / 2 + 1] = pack_bf16(rb.x, rb.y);
+                    }
                 }
-                // columns c * 16 .. + 15 of the tile's buffer: their scores (keys 16 c .. 16 c + 15) were read in piece c / 2
-                tmem_st<PIECE / 2>(lane_addr + col_s + c * (PIECE / 2), packed);
-            }
-            if (rescale) {
-                // the product that last wrote the accumulator must be over
-                ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[t], (it - 1) & 1, failed));
-                if (!ok) break;
-                tc_fence_after();
-                l_sum *= alpha;
-#pragma unroll
-                for (int c = 0; c < HD / PIECE; ++c) {
-                    unsigned v[PIECE];
-                    tmem_ld<PIECE>(lane_addr + col_o + c * PIECE, v);
+                const float l0 = la.x, l1 = la.y, l2 = lb.x, l3 = lb.y;
+                float l_sum = (t ? l_b : l_a);
+                if (rescale) {
+                    // the product that last wrote the accumulator must be over
+                    ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[t], (it - 1) & 1, failed));
+                    if (!ok) {
+                        failed_flag = 1;
+                        continue;
+                    }
+                    tc_fence_after();
+                    l_sum *= alpha;
+                    unsigned v[HO];
+                    tmem_ld<HO>(lane_addr + col_o + half * HO, v);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < PIECE; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                    tmem_st<PIECE>(lane_addr + col_o + c * PIECE, v);
+                    for (int i = 0; i < HO; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    tmem_st<HO>(lane_addr + col_o + half * HO, v);
                 }
+                l_sum += (l0 + l1) + (l2 + l3);
+                if (t) { m_b = m_used; l_b = l_sum; } else { m_a = m_used; l_a = l_sum; }
+                tmem_st<HN / 2>(lane_addr + col_s + half * (HN / 2), hi);
+                if (PARTS == 2) tmem_st<HN / 2>(lane_addr + col_s + BN / 2 + half * (HN / 2), lo);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[t]);
             }
-            l_sum += (la.x + la.y) + (lb.x + lb.y);
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[t]);
         }
-        // ---- the end: wait for the last product, divide, store
-        if (ok && last > first) ok = mbar_wait(&pv_done[t], (last - first - 1) & 1, failed);
+        float l[QT] = {l_a, l_b};
+        // ---- the end: wait for the last products, add the two halves' sums, divide, store
+#pragma unroll
+        for (int t = 0; t < QT; ++t) {
+            const int n = range[t].last - range[t].first;
+            if (ok && n > 0) ok = mbar_wait(&pv_done[t], (n - 1) & 1, failed);
+        }
         ok = __all_sync(0xffffffffu, ok);
+        // (both warps of a pair come here, failed or not; the slot is the one the last step did not
+        // use: the partner has read that one before it came to the last step's barrier)
+        float (&swap_sum)[RT][BM] = swap_max[step & 1];
+        float (&swap_sum2)[RT][BM] = swap_max[(step & 1) ^ 1];
+        swap_sum[half][r] = l[0];
+        asm volatile("bar.sync %0, %1;" ::"r"(pair_barrier), "n"(32 * RT) : "memory");
+#pragma unroll
+        for (int o = 1; o < RT; ++o) l[0] += swap_sum[(half + o) % RT][r];
+        swap_sum2[half][r] = l[1];
+        asm volatile("bar.sync %0, %1;" ::"r"(pair_barrier), "n"(32 * RT) : "memory");
+#pragma unroll
+        for (int o = 1; o < RT; ++o) l[1] += swap_sum2[(half + o) % RT][r];
         if (!ok) {
             if (lane == 0) {
                 failed_flag = 1;
                 atomicExch(p.status, ERR_SOFTMAX_WAIT);
             }
-        } else if (rows > 0) {
+        } else {
             tc_fence_after();
-            const bool valid = r < rows;
-            const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-            __nv_bfloat16* orow = p.out + ((size_t)(qs + tok0 + t * BM + r) * p.n_heads + head) * HD;
 #pragma unroll
-            for (int c = 0; c < HD / PIECE; ++c) {
-                unsigned v[PIECE];
-                tmem_ld<PIECE>(lane_addr + col_o + c * PIECE, v);      // every lane takes part in the load
+            for (int t = 0; t < QT; ++t) {
+                if (range[t].rows == 0) continue;
+                const bool valid = r < range[t].rows;
+                const float inv = l[t] > 0.f ? 1.f / l[t] : 0.f;
+                __nv_bfloat16* orow = p.out + ((size_t)(qs + tok0 + t * BM + r) * p.n_heads + head) * HD + half * HO;
+                unsigned v[HO];
+                tmem_ld<HO>(lane_addr + COL_O + t * BN + half * HO, v);     // every lane takes part in the load
                 tmem_wait_ld();
                 if (valid) {
 #pragma unroll
-                    for (int i = 0; i < PIECE / 8; ++i) {
+                    for (int i = 0; i < HO / 8; ++i) {
                         uint4 w;
                         w.x = pack_bf16(__uint_as_float(v[8 * i]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
                         w.y = pack_bf16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
                         w.z = pack_bf16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
                         w.w = pack_bf16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + c * PIECE + i * 8) = w;
+                        *reinterpret_cast<uint4*>(orow + i * 8) = w;
                     }
                 }
             }
@@ -632,10 +684,10 @@ bool takes(int n_heads, int n_kv_heads, int head_dim, int page_size) {
 
 bool p_blocks_too_many(int max_q_len) { return (max_q_len + QT * BM - 1) / (QT * BM) > 65535; }
 
-template <int HD>
+template <int HD, int PARTS>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, dim3 grid, cudaStream_t s) {
     constexpr size_t smem = smem_for<HD>();
-    auto kern = attention_prefill_kernel<HD, stages_for<HD>()>;
+    auto kern = attention_prefill_kernel<HD, stages_for<HD>(), PARTS>;
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -654,13 +706,15 @@ extern "C" int tl_attention_prefill_supports(int n_heads, int n_kv_heads, int he
 
 // q, out: [q_rows, n_heads, head_dim] bfloat16 (q_rows: all rows of the buffer, n_tokens of them in
 // use by the n_seqs requests given); pages: [n_pages, n_kv_heads, page_size, head_dim].
+// parts: 2 multiplies every probability as bfloat16 value + bfloat16 remainder, 1 as one bfloat16.
 extern "C" int tl_paged_attention_prefill(const void* q, const void* k_pages, const void* v_pages, void* out,
                                           const int* block_table, int table_stride, const int* q_start,
                                           const int* kv_len, int* status, long long q_rows, int n_tokens, int n_seqs,
                                           int n_heads, int n_kv_heads, int head_dim, int page_size, long long n_pages,
-                                          int max_q_len, int window, float scale, void* stream) {
+                                          int max_q_len, int window, float scale, int parts, void* stream) {
     if (n_tokens <= 0 || n_seqs <= 0) return TL_OK;
     if (!takes(n_heads, n_kv_heads, head_dim, page_size) || max_q_len <= 0 || n_pages <= 0 || q_rows < n_tokens) return TL_BAD_SIZE;
+    if (parts != 1 && parts != 2) return TL_BAD_SIZE;
     if (n_pages * n_kv_heads * page_size >= (1LL << 31)) return TL_BAD_SIZE;
     if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(out) || status == nullptr) return TL_BAD_ALIGN;
     if (n_seqs > 65535 || p_blocks_too_many(max_q_len)) return TL_BAD_SIZE;
@@ -688,5 +742,6 @@ extern "C" int tl_paged_attention_prefill(const void* q, const void* k_pages, co
 
     dim3 grid(n_heads, p.n_q_blocks, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;
-    return head_dim == 128 ? launch<128>(mk, mv, p, grid, s) : launch<64>(mk, mv, p, grid, s);
+    if (parts == 2) return head_dim == 128 ? launch<128, 2>(mk, mv, p, grid, s) : launch<64, 2>(mk, mv, p, grid, s);
+    return head_dim == 128 ? launch<128, 1>(mk, mv, p, grid, s) : launch<64, 1>(mk, mv, p, grid, s);
 }

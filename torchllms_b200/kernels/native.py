@@ -125,6 +125,8 @@ class NativeOps:
         # TORCHLLMS_B200_DEBUG=1: the libraries are built with -DTL_DEBUG (see kernels/build.py); kernels
         # range-check the indices they are given and report through a word that check_status() reads
         self.debug = os.environ.get("TORCHLLMS_B200_DEBUG", "") not in ("", "0")
+        # the tcgen05 prefill attention multiplies probabilities as one bfloat16 (1) or as value + remainder (2)
+        self.prefill_probability_parts = int(os.environ.get("TORCHLLMS_B200_PREFILL_PARTS", "2"))
         self.use_fused_residual = os.environ.get("TORCHLLMS_B200_NO_FUSED_RESIDUAL", "") not in ("1", "true")
 
     def graph_capturable(self, dtype: torch.dtype) -> bool:
@@ -555,7 +557,7 @@ class NativeOps:
                 _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
                 _ptr(q_start), _ptr(kv_len), ctypes.c_void_p(self._status.data_ptr()), ctypes.c_longlong(q.shape[0]),
                 T, n_seqs, n_heads, n_kv_heads, head_dim, page_size, ctypes.c_longlong(k_pages.shape[0]), max_q_len,
-                int(window or 0), ctypes.c_float(scale), _stream())
+                int(window or 0), ctypes.c_float(scale), self.prefill_probability_parts, _stream())
             _check(rc, "paged_attention_prefill")
             self.launches += 1
             return out
