@@ -458,10 +458,11 @@ def main():
     # the timed run launches each decode step before it has read the tokens of the step before: the
     # step-by-step way must give the same greedy tokens
     llm.look_ahead = False
-    check = llm.generate(prompt_token_ids=e2e_prompts, max_new_tokens=8, disable_tqdm=True)
+    n_check = min(8, n_new)
+    check = llm.generate(prompt_token_ids=e2e_prompts, max_new_tokens=n_check, disable_tqdm=True)
     llm.look_ahead = True
-    if [r.token_ids[:8] for r in e2e_out] != [r.token_ids for r in check] or any(r.error for r in e2e_out):
-        raise RuntimeError("end to end: launching ahead and the step-by-step way disagree on the first 8 greedy tokens")
+    if [r.token_ids[:n_check] for r in e2e_out] != [r.token_ids for r in check] or any(r.error for r in e2e_out):
+        raise RuntimeError(f"end to end: launching ahead and the step-by-step way disagree on the first {n_check} greedy tokens")
     e2e_tok_s = st.decode_step_tokens / st.decode_seconds if st.decode_seconds > 0 else None
     h2d = engine._buf.uploaded_bytes                 # the last decode step's one upload (positions, slots, block tables)
     e2e = {"value": round(e2e_tok_s, 1) if e2e_tok_s else None, "unit": "tokens/s",
