@@ -3,8 +3,13 @@
 //
 // Same contract as the kernels in attention_mma.cu (causal, optional sliding window, grouped
 // heads, float32 scores / running maximum / sum / accumulator), other machinery: both products
-// are tcgen05.mma with accumulators in tensor memory, K and V arrive by TMA, and a query row
-// belongs to two threads that exchange one number per key tile.
+// are tcgen05.mma with accumulators in tensor memory, K and V arrive by TMA.
+//
+// Two kernels.  The one that is used by default is the second in this file: one bfloat16 per
+// probability, a thread to a query row, 512 threads.  The first, described next, multiplies every
+// probability as value + remainder (half the rounding error, a third slower); it has two threads
+// to a query row that exchange one number per key tile.  Both share the tiling, the producer and
+// the issuers' order of work.
 //
 // A CTA serves 256 consecutive tokens of one request and one query head as two query tiles of
 // 128 rows (M = 128 each), walking the visible keys in tiles of 128.  Every K and V tile that is
@@ -23,14 +28,16 @@
 //   warp 8         : TMA producer: per key tile one box per page (or per 128 rows of a larger
 //                    page) and 64-element column block of K and of V into 128-byte-swizzled
 //                    shared memory, each in a ring of its own; no multicast.
-//   warps 9 and 10 : one lane each issues the products of one query tile: S_j = Q K_j^T, then,
-//                    once the probabilities are in place, O += P_j V_j with the probabilities
-//                    read from tensor memory.  While the softmax works on one query tile the
-//                    tensor core works for the other.  (One thread polling for both tiles left
-//                    the tensor core idle between its turns.)
+//   warps 9 and 10 : each issues the products of one query tile (the whole warp in step, one
+//                    elected lane issuing): S_j = Q K_j^T, then, once the probabilities are in
+//                    place, O += P_j V_j with the probabilities read from tensor memory, and the
+//                    scores of the next key tile right behind it.  While the softmax works on one
+//                    query tile the tensor core works for the other.  (One thread polling for both
+//                    tiles left the tensor core idle between its turns.)
 // Q and K are K-major operands (rows of 128 bytes, swizzled); V is used as stored, keys x
-// columns, as an MN-major operand.  Probabilities are multiplied as value + remainder, both
-// bfloat16 (two products), so that the product keeps 16 bits of them, as in the other kernels.
+// columns, as an MN-major operand.  In this kernel probabilities are multiplied as value +
+// remainder, both bfloat16 (two products), so that the product keeps 16 bits of them, as in the
+// mma.sync kernels.
 // (A float16 left operand against a bfloat16 right operand in one tcgen05.mma.kind::f16 raised
 // "illegal instruction" on a B200: the two formats have to be the same.)
 //
@@ -145,23 +152,28 @@ __device__ __forceinline__ unsigned long long desc_mn_major(unsigned addr, unsig
 __host__ __device__ constexpr unsigned idesc(int n, unsigned a_fmt, unsigned b_fmt, unsigned b_mn_major) {
     return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (b_mn_major << 16) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
 }
+// The three tensor-core instructions below are for a whole warp in step: one elected lane issues.  So
+// the descriptors stay warp-uniform values (uniform registers); a lone lane inside a divergent branch
+// cannot have those, and its instructions issued a fifth slower.
 // D[tmem] (+)= A[shared] . B[shared]
-__device__ __forceinline__ void umma_ss(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
-                                        unsigned id, unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+__device__ __forceinline__ void umma_ss_elect(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
+                                              unsigned id, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(id), "r"(accumulate) : "memory");
 }
 // D[tmem] (+)= A[tmem] . B[shared]: the left operand lies in tensor memory, row = lane, two 16-bit
 // elements of K to a column
-__device__ __forceinline__ void umma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long b_desc,
-                                        unsigned id, unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+__device__ __forceinline__ void umma_ts_elect(unsigned tmem_d, unsigned tmem_a, unsigned long long b_desc,
+                                              unsigned id, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(id), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+// the barrier gets an arrival when everything this lane has issued so far is done
+__device__ __forceinline__ void umma_commit_elect(unsigned long long* bar) {
+    asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+                 "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned (&r)[16]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -215,7 +227,7 @@ struct TileRange {
 };
 
 // PARTS: 2 = probabilities as value + remainder (two products, 16 bits of every probability kept);
-// 1 = probabilities rounded to bfloat16 once (one product).
+// 1 = probabilities rounded to bfloat16 once (one product; the kernel further down does that faster).
 template <int HD, int STAGES, int PARTS>
 __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                        const __grid_constant__ CUtensorMap map_v,
@@ -358,27 +370,28 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
             }
         }
     } else if (warp >= W_ISSUE) {
-        if (lane == 0 && active) {
-            // ---- issuers, one per query tile (warp W_ISSUE + t).  For every key tile its query tile
-            // takes part in: scores S_j = Q K_j^T, then, once the softmax has put the probabilities
-            // where the scores were, the product O += P_j V_j with the probabilities read from tensor
-            // memory.  The two tiles' chains do not depend on each other: while one issuer waits for its
-            // softmax, the other keeps the tensor core busy.  A stage of K or V is released by both.
+        if (active) {
+            // ---- issuers, one per query tile (warp W_ISSUE + t); the whole warp runs in step and one
+            // elected lane issues.  For every key tile its query tile takes part in: scores
+            // S_j = Q K_j^T, then, once the softmax has put the probabilities where the scores were, the
+            // product O += P_j V_j with the probabilities read from tensor memory, and right behind it
+            // the scores of the next key tile (the tensor core takes its instructions in order, so they
+            // overwrite the probabilities only after the product has read them).  What is not on the
+            // softmax's path (K, V) is waited for before the probabilities are.  The two tiles' chains
+            // do not depend on each other: while one issuer waits for its softmax, the other keeps the
+            // tensor core busy.  A stage of K or V is released by both.
             constexpr unsigned id_s = idesc(BN, 1u, 1u, 0u);     // bf16 x bf16, K as stored (K-major)
             constexpr unsigned id_o = idesc(HD, 1u, 1u, 1u);     // bf16 probabilities x bf16 values as stored (MN-major)
             const int t = warp - W_ISSUE;
             const int first = t ? range[1].first : range[0].first, last = t ? range[1].last : range[0].last;
-            bool ok = mbar_wait(&q_full, 0, failed);
+            bool ok = __all_sync(0xffffffffu, mbar_wait(&q_full, 0, failed));
             tc_fence_after();
             const unsigned long long qd0 = desc_k_major(smem_u32(Qs + t * KV_BYTES));
             const unsigned d_s = tmem + COL_S + t * BN, d_o = tmem + COL_O + t * BN;
-            for (int j = 0; j < n_tiles && ok; ++j) {
+            // scores of key tile j (its K stage has arrived), or this tile's leave to reuse the stage
+            auto scores = [&](int j) {
                 const int s = j % STAGES;
-                const unsigned ring = (j / STAGES) & 1;
-                const bool mine = j >= first && j < last;
-                ok = mbar_wait(&k_full[s], ring, failed);
-                if (!ok) break;
-                if (mine) {
+                if (j >= first && j < last) {
                     tc_fence_after();
                     // (the address is the low field of a descriptor, in units of 16 bytes: moving
                     // along K is an addition to the descriptor as a whole)
@@ -386,17 +399,28 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
 #pragma unroll
                     for (int kd = 0; kd < HD / 16; ++kd) {
                         const unsigned off = ((kd / 4) * HALF_BYTES + (kd % 4) * 32) >> 4;
-                        umma_ss(d_s, qd0 + off, kd0 + off, id_s, kd > 0 ? 1u : 0u);
+                        umma_ss_elect(d_s, qd0 + off, kd0 + off, id_s, kd > 0 ? 1u : 0u);
                     }
-                    umma_commit(&s_full[t]);
-                    umma_commit(&k_empty[s]);        // this tile is done with the K stage once its scores are computed
-                } else {
-                    mbar_arrive(&k_empty[s]);        // not this tile's keys: nothing to wait for
+                    umma_commit_elect(&s_full[t]);
+                    umma_commit_elect(&k_empty[s]);        // this tile is done with the K stage once its scores are computed
+                } else if (lane == 0) {
+                    mbar_arrive(&k_empty[s]);              // not this tile's keys: nothing to wait for
                 }
-                if (mine) ok = mbar_wait(&p_full[t], (j - first) & 1, failed);
-                ok = ok && mbar_wait(&v_full[s], ring, failed);
+            };
+            if (ok && n_tiles > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(&k_full[0], 0, failed));
+                if (ok) scores(0);
+            }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % STAGES;
+                const unsigned ring = (j / STAGES) & 1;
+                const bool mine = j >= first && j < last;
+                ok = __all_sync(0xffffffffu, mbar_wait(&v_full[s], ring, failed));
+                if (ok && j + 1 < n_tiles) ok = __all_sync(0xffffffffu, mbar_wait(&k_full[(j + 1) % STAGES], ((j + 1) / STAGES) & 1, failed));
                 if (!ok) break;
                 if (mine) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&p_full[t], (j - first) & 1, failed));
+                    if (!ok) break;
                     tc_fence_after();
                     const unsigned long long vd0 = desc_mn_major(smem_u32(tiles + (STAGES + s) * KV_BYTES), HALF_BYTES);
                     const unsigned acc = j > first ? 1u : 0u;
@@ -404,15 +428,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
                     for (int part = 0; part < PARTS; ++part)         // value, then remainder
 #pragma unroll
                         for (int kk = 0; kk < BN / 16; ++kk)         // 16 keys on: 2048 bytes of V, 8 columns of P
-                            umma_ts(d_o, d_s + part * (BN / 2) + kk * 8, vd0 + kk * (2048 >> 4), id_o,
-                                    (part > 0 || kk > 0) ? 1u : acc);
-                    umma_commit(&pv_done[t]);        // the accumulator is up to date
-                    umma_commit(&v_empty[s]);        // and this tile is done with the V stage
-                } else {
+                            umma_ts_elect(d_o, d_s + part * (BN / 2) + kk * 8, vd0 + kk * (2048 >> 4), id_o,
+                                          (part > 0 || kk > 0) ? 1u : acc);
+                    umma_commit_elect(&pv_done[t]);        // the accumulator is up to date
+                    umma_commit_elect(&v_empty[s]);        // and this tile is done with the V stage
+                } else if (lane == 0) {
                     mbar_arrive(&v_empty[s]);
                 }
+                if (j + 1 < n_tiles) scores(j + 1);
             }
-            if (!ok) {
+            if (!ok && lane == 0) {
                 failed_flag = 1;
                 atomicExch(p.status, ERR_ISSUER_WAIT);
             }
@@ -622,6 +647,448 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
     }
 }
 
+
+// ================================================================================================
+// The same work with one bfloat16 per probability and the roles spread over four warp groups (512
+// threads), so that a query row's softmax is one thread's business and waits for no neighbour:
+//   warps 0-3, 4-7 : softmax of query tile 0, of query tile 1.  Row r = TMEM lane r belongs to one
+//                    thread, which reads the 128 scores of a key tile into registers once (192
+//                    registers a thread: the warp groups trade registers at the start with
+//                    setmaxnreg), takes their maximum, tells the correction warps by how much the
+//                    row's accumulator has to shrink, and writes the probabilities where the scores were.
+//   warps 8-11     : correction.  When a row's maximum in use has grown they rescale its accumulator
+//                    (a round trip through registers) off the softmax's path; at the end they divide
+//                    by the row's sum and store it.
+//   warp 12        : TMA producer;  warps 13, 14 : the issuers of the two query tiles (the whole warp
+//                    runs in step and one elected lane issues: a lone lane inside a divergent branch
+//                    cannot keep the descriptors in uniform registers, and issued a fifth slower);
+//                    warp 15 is there to complete the warp group.
+// Barriers beside those of the kernel above: alpha_ready (softmax -> correction: factors are in
+// shared memory), o_ready (correction -> issuer: the accumulator may take the next product),
+// l_ready (softmax -> correction: the row sums are in shared memory), turn (softmax -> the other
+// tile's softmax: the exponential unit is yours).
+constexpr int NTHREADS_ROWS = 512;
+// Registers a thread after the trade: softmax / correction / the rest.  A warp group can only be given
+// what another has handed back, so the sum stays within what the launch allots (128 a thread).
+constexpr int REGS_SOFTMAX = 192, REGS_CORRECTION = 72, REGS_REST = 40;
+static_assert(QT * REGS_SOFTMAX + REGS_CORRECTION + REGS_REST <= 4 * 128, "registers are traded, not made");
+constexpr int WR_CORR = 4 * QT, WR_COPY = 4 * QT + 4, WR_ISSUE = 4 * QT + 5;
+
+template <int STAGES>
+struct TailRows {
+    unsigned long long q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+    unsigned long long s_full[QT], p_full[QT], pv_done[QT], alpha_ready[QT], o_ready[QT], l_ready[QT], turn[QT];
+    unsigned tmem_base_slot;
+    int failed_flag;
+    int grow_any[QT][2][4];     // [tile][parity of the tile's step][warp of the tile]: did a row of the warp grow
+    float alpha[QT][2][BM];     // [tile][parity of the tile's step][row]: what the row's accumulator shrinks by
+    float l_final[QT][BM];
+};
+
+template <int N> __device__ __forceinline__ void regs_up() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void regs_down() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
+template <int HD, int STAGES>
+__global__ void __launch_bounds__(NTHREADS_ROWS, 1) attention_prefill_rows_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                                 const __grid_constant__ CUtensorMap map_v,
+                                                                                 const PrefillParams p) {
+    constexpr int HALVES = HD / 64;
+    constexpr unsigned HALF_BYTES = BN * 128;
+    constexpr unsigned KV_BYTES = HALVES * HALF_BYTES;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* Qs = smem_raw;
+    unsigned char* tiles = Qs + QT * KV_BYTES;
+    TailRows<STAGES>& tail = *reinterpret_cast<TailRows<STAGES>*>(tiles + 2 * STAGES * KV_BYTES);
+    unsigned long long& q_full = tail.q_full;
+    unsigned long long (&k_full)[STAGES] = tail.k_full;
+    unsigned long long (&k_empty)[STAGES] = tail.k_empty;
+    unsigned long long (&v_full)[STAGES] = tail.v_full;
+    unsigned long long (&v_empty)[STAGES] = tail.v_empty;
+    unsigned long long (&s_full)[QT] = tail.s_full;
+    unsigned long long (&p_full)[QT] = tail.p_full;
+    unsigned long long (&pv_done)[QT] = tail.pv_done;
+    unsigned long long (&alpha_ready)[QT] = tail.alpha_ready;
+    unsigned long long (&o_ready)[QT] = tail.o_ready;
+    unsigned long long (&l_ready)[QT] = tail.l_ready;
+    unsigned long long (&turn)[QT] = tail.turn;
+    unsigned& tmem_base_slot = tail.tmem_base_slot;
+    int& failed_flag = tail.failed_flag;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        failed_flag = 0;
+        mbar_init(&q_full, 4 * QT);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], QT);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], QT);
+        }
+        for (int t = 0; t < QT; ++t) {
+            mbar_init(&s_full[t], 1);
+            mbar_init(&p_full[t], 4);
+            mbar_init(&pv_done[t], 1);
+            mbar_init(&alpha_ready[t], 4);
+            mbar_init(&o_ready[t], 4);
+            mbar_init(&l_ready[t], 4);
+            mbar_init(&turn[t], 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == WR_ISSUE) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = tmem_base_slot;
+    volatile int* failed = &failed_flag;
+    grid_launch_dependents();
+    grid_dependency_wait();
+
+    const int b = blockIdx.z;
+    const int head = blockIdx.x;
+    const int kvh = head / (p.n_heads / p.n_kv_heads);
+    const int qs = p.q_start[b];
+    const int ql = p.q_start[b + 1] - qs;
+    const int kl = p.kv_len[b];
+    const int tok0 = (p.n_q_blocks - 1 - (int)blockIdx.y) * (QT * BM);
+    const bool active = tok0 < ql;
+    const int qpos_base = kl - ql;
+    const int k_lo = p.window > 0 ? max(0, qpos_base + tok0 - p.window + 1) : 0;
+    const int k_start = k_lo & ~(BN - 1);
+    TileRange range[QT];
+    int n_tiles = 0;
+#pragma unroll
+    for (int t = 0; t < QT; ++t) {
+        const int t0 = tok0 + t * BM;
+        const int rows = active ? max(0, min(BM, ql - t0)) : 0;
+        const int lo = p.window > 0 ? max(0, qpos_base + t0 - p.window + 1) : 0;
+        range[t].rows = rows;
+        range[t].first = rows > 0 ? ((lo & ~(BN - 1)) - k_start) / BN : 0;
+        range[t].last = rows > 0 ? (qpos_base + t0 + rows - k_start + BN - 1) / BN : 0;
+        n_tiles = max(n_tiles, range[t].last);
+    }
+    const int k_hi = qpos_base + min(ql, tok0 + QT * BM);
+
+    if (warp >= WR_COPY) {
+        regs_down<REGS_REST>();
+        if (warp == WR_COPY) {
+            if (active) {
+                // ---- producer: as in the kernel above
+                bool sound = (smem_u32(Qs) & 1023u) == 0u;
+                if (!sound && lane == 0) {
+                    failed_flag = 1;
+                    atomicExch(p.status, ERR_BAD_COPY);
+                }
+                const int* table = p.block_table + (size_t)b * p.table_stride;
+                const int n_boxes = BN / p.box_rows;
+                for (int j = 0; j < n_tiles && sound; ++j) {
+                    const int s = j % STAGES;
+                    const int k0 = k_start + j * BN;
+                    for (int which = 0; which < 2 && sound; ++which) {
+                        unsigned long long* full = which == 0 ? &k_full[s] : &v_full[s];
+                        unsigned long long* empty = which == 0 ? &k_empty[s] : &v_empty[s];
+                        if (j >= STAGES && !__all_sync(0xffffffffu, mbar_wait(empty, ((j / STAGES) - 1) & 1, failed))) {
+                            if (lane == 0) {
+                                failed_flag = 1;
+                                atomicExch(p.status, ERR_PRODUCER_WAIT);
+                            }
+                            sound = false;
+                            break;
+                        }
+                        if (lane == 0) mbar_expect_tx(full, KV_BYTES);
+                        __syncwarp();
+                        unsigned char* dst0 = tiles + (which * STAGES + s) * KV_BYTES;
+                        const CUtensorMap* map = which == 0 ? &map_k : &map_v;
+                        for (int c = lane; c < n_boxes; c += 32) {
+                            const int kpos = k0 + c * p.box_rows;
+                            int row = p.total_rows;
+                            if (kpos < k_hi && kpos + p.box_rows > k_lo) {
+                                const int page = table[kpos >> p.page_shift];
+                                if (tl_check_page(page))
+                                    row = (page * p.n_kv_heads + kvh) * p.page_size + (kpos & (p.page_size - 1));
+                            }
+#pragma unroll
+                            for (int h = 0; h < HALVES; ++h) {
+                                unsigned char* dst = dst0 + h * HALF_BYTES + c * p.box_rows * 128;
+                                if (!copy_is_sound(dst, h * 64, row)) {
+                                    failed_flag = 1;
+                                    atomicExch(p.status, ERR_BAD_COPY);
+                                    continue;
+                                }
+                                tma_load_2d(dst, map, full, h * 64, row);
+                            }
+                        }
+                        __syncwarp();
+                    }
+                }
+            }
+        } else if (warp < WR_ISSUE + QT) {
+            if (active) {
+                // ---- issuers, one per query tile; the whole warp runs in step and one elected lane issues.
+                // As in the kernel above, with two differences.  The product into the accumulator also waits
+                // for the correction warps' word that the accumulator is ready for it.  And the scores of the
+                // next key tile are queued right behind that product (the tensor core takes its instructions
+                // in order, so the scores overwrite the probabilities only after the product has read them):
+                // everything else the two wait for (K, V) is waited for before the probabilities are, so
+                // that nothing but the products themselves stands between one softmax and the next.
+                constexpr unsigned id_s = idesc(BN, 1u, 1u, 0u);
+                constexpr unsigned id_o = idesc(HD, 1u, 1u, 1u);
+                const int t = warp - WR_ISSUE;
+                const int first = t ? range[1].first : range[0].first, last = t ? range[1].last : range[0].last;
+                bool ok = __all_sync(0xffffffffu, mbar_wait(&q_full, 0, failed));
+                tc_fence_after();
+                const unsigned long long qd0 = desc_k_major(smem_u32(Qs + t * KV_BYTES));
+                const unsigned d_s = tmem + COL_S + t * BN, d_o = tmem + COL_O + t * BN;
+                // scores of key tile j (its K stage has arrived), or this tile's leave to reuse the stage
+                auto scores = [&](int j) {
+                    const int s = j % STAGES;
+                    if (j >= first && j < last) {
+                        tc_fence_after();
+                        const unsigned long long kd0 = desc_k_major(smem_u32(tiles + s * KV_BYTES));
+#pragma unroll
+                        for (int kd = 0; kd < HD / 16; ++kd) {
+                            const unsigned off = ((kd / 4) * HALF_BYTES + (kd % 4) * 32) >> 4;
+                            umma_ss_elect(d_s, qd0 + off, kd0 + off, id_s, kd > 0 ? 1u : 0u);
+                        }
+                        umma_commit_elect(&s_full[t]);
+                        umma_commit_elect(&k_empty[s]);
+                    } else if (lane == 0) {
+                        mbar_arrive(&k_empty[s]);
+                    }
+                };
+                if (ok && n_tiles > 0) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&k_full[0], 0, failed));
+                    if (ok) scores(0);
+                }
+                for (int j = 0; j < n_tiles && ok; ++j) {
+                    const int s = j % STAGES;
+                    const unsigned ring = (j / STAGES) & 1;
+                    const bool mine = j >= first && j < last;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&v_full[s], ring, failed));
+                    if (ok && j + 1 < n_tiles) ok = __all_sync(0xffffffffu, mbar_wait(&k_full[(j + 1) % STAGES], ((j + 1) / STAGES) & 1, failed));
+                    if (!ok) break;
+                    if (mine) {
+                        ok = __all_sync(0xffffffffu, mbar_wait(&p_full[t], (j - first) & 1, failed) && mbar_wait(&o_ready[t], (j - first) & 1, failed));
+                        if (!ok) break;
+                        tc_fence_after();
+                        const unsigned long long vd0 = desc_mn_major(smem_u32(tiles + (STAGES + s) * KV_BYTES), HALF_BYTES);
+                        const unsigned acc = j > first ? 1u : 0u;
+#pragma unroll
+                        for (int kk = 0; kk < BN / 16; ++kk)
+                            umma_ts_elect(d_o, d_s + kk * 8, vd0 + kk * (2048 >> 4), id_o, kk > 0 ? 1u : acc);
+                        umma_commit_elect(&pv_done[t]);
+                        umma_commit_elect(&v_empty[s]);
+                    } else if (lane == 0) {
+                        mbar_arrive(&v_empty[s]);
+                    }
+                    if (j + 1 < n_tiles) scores(j + 1);
+                }
+                if (!ok && lane == 0) {
+                    failed_flag = 1;
+                    atomicExch(p.status, ERR_ISSUER_WAIT);
+                }
+            }
+        }
+    } else if (warp >= WR_CORR) {
+        regs_down<REGS_CORRECTION>();
+        if (active) {
+            // ---- correction: row r of either query tile
+            constexpr int PIECE = 32;
+            const int cw = warp & 3;
+            const int r = cw * 32 + lane;
+            const unsigned lane_addr = tmem + ((unsigned)(cw * 32) << 16);
+            bool ok = true;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+#pragma unroll 1
+                for (int t = 0; t < QT && ok; ++t) {
+                    const int first = t ? range[1].first : range[0].first, last = t ? range[1].last : range[0].last;
+                    if (j < first || j >= last) continue;
+                    const int it = j - first, par = it & 1;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&alpha_ready[t], par, failed));
+                    if (!ok) break;
+                    if (it > 0 && tail.grow_any[t][par][cw]) {
+                        ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[t], (it - 1) & 1, failed));     // the product that last wrote the accumulator
+                        if (!ok) break;
+                        tc_fence_after();
+                        const float a = tail.alpha[t][par][r];
+#pragma unroll
+                        for (int c = 0; c < HD / PIECE; ++c) {
+                            unsigned v[PIECE];
+                            tmem_ld<PIECE>(lane_addr + COL_O + t * BN + c * PIECE, v);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < PIECE; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * a);
+                            tmem_st<PIECE>(lane_addr + COL_O + t * BN + c * PIECE, v);
+                        }
+                        tmem_wait_st();
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&o_ready[t]);
+                }
+            }
+            // ---- the end: the rows' sums, the last products, divide, store
+#pragma unroll 1
+            for (int t = 0; t < QT && ok; ++t) {
+                const int rows = t ? range[1].rows : range[0].rows;
+                const int n = (t ? range[1].last : range[0].last) - (t ? range[1].first : range[0].first);
+                if (rows == 0 || n <= 0) continue;
+                ok = __all_sync(0xffffffffu, mbar_wait(&l_ready[t], 0, failed) && mbar_wait(&pv_done[t], (n - 1) & 1, failed));
+                if (!ok) break;
+                tc_fence_after();
+                const bool valid = r < rows;
+                const float l = tail.l_final[t][r];
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                __nv_bfloat16* orow = p.out + ((size_t)(qs + tok0 + t * BM + r) * p.n_heads + head) * HD;
+#pragma unroll
+                for (int c = 0; c < HD / PIECE; ++c) {
+                    unsigned v[PIECE];
+                    tmem_ld<PIECE>(lane_addr + COL_O + t * BN + c * PIECE, v);
+                    tmem_wait_ld();
+                    if (valid) {
+#pragma unroll
+                        for (int i = 0; i < PIECE / 8; ++i) {
+                            uint4 w;
+                            w.x = pack_bf16(__uint_as_float(v[8 * i]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
+                            w.y = pack_bf16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
+                            w.z = pack_bf16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
+                            w.w = pack_bf16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+                            *reinterpret_cast<uint4*>(orow + c * PIECE + i * 8) = w;
+                        }
+                    }
+                }
+            }
+            if (!ok && lane == 0) {
+                failed_flag = 1;
+                atomicExch(p.status, ERR_SOFTMAX_WAIT);
+            }
+        }
+    } else {
+        regs_up<REGS_SOFTMAX>();
+        if (active) {
+            // ---- softmax of query tile t: one thread to a row
+            const int t = warp >> 2;
+            const int sw = warp & 3;
+            const int r = sw * 32 + lane;
+            const unsigned lane_addr = tmem + ((unsigned)(sw * 32) << 16);
+            const int rows = t ? range[1].rows : range[0].rows;
+            const int first = t ? range[1].first : range[0].first, last = t ? range[1].last : range[0].last;
+            const unsigned col_s = COL_S + t * BN;
+            {
+                const bool valid = r < rows;
+                const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + tok0 + t * BM + r) * p.n_heads + head) * HD);
+#pragma unroll
+                for (int chunk = 0; chunk < HD / 8; ++chunk) {
+                    const uint4 v = valid ? src[chunk] : make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(Qs + t * KV_BYTES + (chunk >> 3) * HALF_BYTES + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) = v;
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&q_full);
+
+            float m_used = -INFINITY, l_sum = 0.f;
+            const int t0 = qpos_base + tok0 + t * BM;
+            const int qpos = t0 + (r < rows ? r : rows - 1);
+            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+            bool ok = true;
+            // The exponentials of the two query tiles take turns (turn[t]: tile t may go), so that one tile's
+            // softmax has the exponential unit to itself while the tensor core works for the other tile;
+            // side by side they would both wait for the unit and then both for the tensor core.
+            if (t == 1 && lane == 0) mbar_arrive(&turn[0]);
+            for (int j = 0; j < n_tiles; ++j) {
+                if (j < first || j >= last) {      // not this tile's keys: pass the turn on
+                    ok = __all_sync(0xffffffffu, mbar_wait(&turn[t], j & 1, failed));
+                    if (!ok) break;
+                    if (lane == 0) mbar_arrive(&turn[t ^ 1]);
+                    continue;
+                }
+                const int k0 = k_start + j * BN;
+                const int it = j - first, par = it & 1;
+                ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], par, failed));
+                if (!ok) break;
+                tc_fence_after();
+                unsigned raw[BN];
+                tmem_ld<BN>(lane_addr + col_s, raw);
+                tmem_wait_ld();
+                const bool clear = k0 + BN - 1 <= t0 && (p.window <= 0 || k0 > t0 + rows - 1 - p.window);
+                if (!clear) {
+#pragma unroll
+                    for (int i = 0; i < BN; ++i) {
+                        const int kpos = k0 + i;
+                        const bool vis = kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
+                        if (!vis) raw[i] = 0xff800000u;      // -inf
+                    }
+                }
+                float mx0 = __uint_as_float(raw[0]), mx1 = __uint_as_float(raw[1]);
+                float mx2 = __uint_as_float(raw[2]), mx3 = __uint_as_float(raw[3]);
+#pragma unroll
+                for (int i = 4; i < BN; i += 4) {
+                    mx0 = fmaxf(mx0, __uint_as_float(raw[i])); mx1 = fmaxf(mx1, __uint_as_float(raw[i + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(raw[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(raw[i + 3]));
+                }
+                const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
+                const bool grow = m_new > m_used + LAG;      // also true for the first keys a row sees
+                const float alpha = grow ? ex2(m_used - m_new) : 1.f;
+                if (grow) m_used = m_new;
+                // the correction warps learn what this row's accumulator shrinks by, and whether any row of the warp does
+                const bool any = __any_sync(0xffffffffu, grow);
+                tail.alpha[t][par][r] = alpha;
+                if (lane == 0) tail.grow_any[t][par][sw] = any ? 1 : 0;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&alpha_ready[t]);
+                ok = __all_sync(0xffffffffu, mbar_wait(&turn[t], j & 1, failed));
+                if (!ok) break;
+                l_sum *= alpha;
+                const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+                const float2 nm2 = make_float2(-m_safe, -m_safe);
+                float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int c = 0; c < BN / 32; ++c) {
+                    unsigned packed[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        const int k = c * 32 + i;
+                        const float2 xa = __ffma2_rn(make_float2(__uint_as_float(raw[k]), __uint_as_float(raw[k + 1])), sc2, nm2);
+                        const float2 xb = __ffma2_rn(make_float2(__uint_as_float(raw[k + 2]), __uint_as_float(raw[k + 3])), sc2, nm2);
+                        const float2 ea = make_float2(ex2(xa.x), ex2(xa.y)), eb = make_float2(ex2(xb.x), ex2(xb.y));
+                        la = __fadd2_rn(la, ea);
+                        lb = __fadd2_rn(lb, eb);
+                        packed[i / 2] = pack_bf16(ea.x, ea.y);
+                        packed[i / 2 + 1] = pack_bf16(eb.x, eb.y);
+                    }
+                    tmem_st<16>(lane_addr + col_s + c * 16, packed);      // (all scores are in registers: nothing is overwritten unread)
+                }
+                l_sum += (la.x + la.y) + (lb.x + lb.y);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&turn[t ^ 1]);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[t]);
+            }
+            if (ok) {
+                tail.l_final[t][r] = l_sum;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&l_ready[t]);
+            } else if (lane == 0) {
+                failed_flag = 1;
+                atomicExch(p.status, ERR_SOFTMAX_WAIT);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == WR_ISSUE) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -684,6 +1151,24 @@ bool takes(int n_heads, int n_kv_heads, int head_dim, int page_size) {
 
 bool p_blocks_too_many(int max_q_len) { return (max_q_len + QT * BM - 1) / (QT * BM) > 65535; }
 
+template <int HD> constexpr size_t smem_rows_for() {
+    return (size_t)(QT + 2 * stages_for<HD>()) * (HD / 64) * BN * 128 + sizeof(TailRows<stages_for<HD>()>);
+}
+static_assert(smem_rows_for<128>() <= 227 * 1024 && smem_rows_for<64>() <= 227 * 1024, "a CTA has 227 KB of shared memory");
+
+template <int HD>
+int launch_rows(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, dim3 grid, cudaStream_t s) {
+    constexpr size_t smem = smem_rows_for<HD>();
+    auto kern = attention_prefill_rows_kernel<HD, stages_for<HD>()>;
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        raised = true;
+    }
+    return (int)tl_launch(kern, grid, dim3(NTHREADS_ROWS), smem, s, mk, mv, p);
+}
+
 template <int HD, int PARTS>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, dim3 grid, cudaStream_t s) {
     constexpr size_t smem = smem_for<HD>();
@@ -706,7 +1191,8 @@ extern "C" int tl_attention_prefill_supports(int n_heads, int n_kv_heads, int he
 
 // q, out: [q_rows, n_heads, head_dim] bfloat16 (q_rows: all rows of the buffer, n_tokens of them in
 // use by the n_seqs requests given); pages: [n_pages, n_kv_heads, page_size, head_dim].
-// parts: 2 multiplies every probability as bfloat16 value + bfloat16 remainder, 1 as one bfloat16.
+// parts: 1 multiplies every probability as one bfloat16 (the kernel of 512 threads), 2 as bfloat16 value +
+// bfloat16 remainder (the kernel of 352 threads: a third slower, half the rounding error).
 extern "C" int tl_paged_attention_prefill(const void* q, const void* k_pages, const void* v_pages, void* out,
                                           const int* block_table, int table_stride, const int* q_start,
                                           const int* kv_len, int* status, long long q_rows, int n_tokens, int n_seqs,
@@ -743,5 +1229,5 @@ extern "C" int tl_paged_attention_prefill(const void* q, const void* k_pages, co
     dim3 grid(n_heads, p.n_q_blocks, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;
     if (parts == 2) return head_dim == 128 ? launch<128, 2>(mk, mv, p, grid, s) : launch<64, 2>(mk, mv, p, grid, s);
-    return head_dim == 128 ? launch<128, 1>(mk, mv, p, grid, s) : launch<64, 1>(mk, mv, p, grid, s);
+    return head_dim == 128 ? launch_rows<128>(mk, mv, p, grid, s) : launch_rows<64>(mk, mv, p, grid, s);
 }

@@ -125,8 +125,9 @@ class NativeOps:
         # TORCHLLMS_B200_DEBUG=1: the libraries are built with -DTL_DEBUG (see kernels/build.py); kernels
         # range-check the indices they are given and report through a word that check_status() reads
         self.debug = os.environ.get("TORCHLLMS_B200_DEBUG", "") not in ("", "0")
-        # the tcgen05 prefill attention multiplies probabilities as one bfloat16 (1) or as value + remainder (2)
-        self.prefill_probability_parts = int(os.environ.get("TORCHLLMS_B200_PREFILL_PARTS", "2"))
+        # the tcgen05 prefill attention multiplies probabilities as one bfloat16 (1: the faster kernel) or as
+        # bfloat16 value + bfloat16 remainder (2: a third slower, half the rounding error)
+        self.prefill_probability_parts = int(os.environ.get("TORCHLLMS_B200_PREFILL_PARTS", "1"))
         self.use_fused_residual = os.environ.get("TORCHLLMS_B200_NO_FUSED_RESIDUAL", "") not in ("1", "true")
 
     def graph_capturable(self, dtype: torch.dtype) -> bool:
