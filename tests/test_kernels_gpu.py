@@ -389,7 +389,7 @@ ATTN_CASES = [
 
 
 IMPLS = [(torch.float32, "general"), (torch.bfloat16, "general"), (torch.bfloat16, "mma"), (torch.bfloat16, "decode"),
-         (torch.bfloat16, "prefill")]
+         (torch.bfloat16, "prefill"), (torch.bfloat16, "prefill2")]
 
 
 def mma_takes(hd):
@@ -413,7 +413,7 @@ def test_paged_attention_matches_twin(ops, dtype, impl, case):
         pytest.skip("the tensor-core kernel does not take this head size")
     if impl == "decode" and not decode_takes(q_lens, H, KV, hd, P):
         pytest.skip("the decode kernel does not take this step")
-    if impl == "prefill" and not prefill_takes(hd, P):
+    if impl in ("prefill", "prefill2") and not prefill_takes(hd, P):
         pytest.skip("the tcgen05 prefill kernel does not take this head size or page size")
     a = build_paged(seq_lens, q_lens, H, KV, hd, P, dtype, seed=len(seq_lens) * 100 + hd)
     scale = hd ** -0.5
@@ -464,7 +464,7 @@ def test_decode_attention_with_a_given_number_of_splits(ops, case, n_splits):
 def test_attention_finds_one_far_key_among_hundreds(ops, dtype, impl, key_pos):
     """Random scores hide a dropped key; here one key takes nearly all the weight, so the output
     must equal that key's value."""
-    L, H, KV, hd, P = 700, 4, 2, (64 if impl in ("decode", "prefill") else 32), 16
+    L, H, KV, hd, P = 700, 4, 2, (64 if impl in ("decode", "prefill", "prefill2") else 32), 16
     a = build_paged([L, 40], [1, 1], H, KV, hd, P, dtype, seed=key_pos, peak=(0, key_pos, 10.0))
     got = ops.paged_attention(**a, scale=hd ** -0.5, window=None, impl=impl).float()
     page, slot = a["block_table"][0, key_pos // P].item(), key_pos % P
@@ -503,7 +503,7 @@ def test_a_long_portion_finds_one_far_key(ops, dtype, impl, key_pos):
     that can see the key must return its value, every row before it must not."""
     if impl == "decode":
         pytest.skip("the decode kernel takes no long portions")
-    L, Q, H, KV, hd, P = 700, 600, 4, 2, (64 if impl == "prefill" else 32), 16
+    L, Q, H, KV, hd, P = 700, 600, 4, 2, (64 if impl in ("prefill", "prefill2") else 32), 16
     a = build_paged([L, 40], [Q, 1], H, KV, hd, P, dtype, seed=key_pos + 1, peak=(0, key_pos, 10.0))
     got = ops.paged_attention(**a, scale=hd ** -0.5, window=None, impl=impl).float()
     page, slot = a["block_table"][0, key_pos // P].item(), key_pos % P
@@ -524,7 +524,7 @@ def test_a_long_portion_finds_one_far_key(ops, dtype, impl, key_pos):
 def test_window_edge_is_exact(ops, dtype, impl):
     """The key just outside the window gets a huge score: if the edge were off by one it would
     take over the output."""
-    L, H, KV, hd, P, w = 100, 2, 1, (64 if impl in ("decode", "prefill") else 16), 8, 24
+    L, H, KV, hd, P, w = 100, 2, 1, (64 if impl in ("decode", "prefill", "prefill2") else 16), 8, 24
     for edge_inside in (False, True):
         key_pos = (L - 1) - w + (1 if edge_inside else 0)   # last query sits at L - 1
         a = build_paged([L], [1], H, KV, hd, P, dtype, seed=3, peak=(0, key_pos, 12.0))

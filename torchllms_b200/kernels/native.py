@@ -505,7 +505,8 @@ class NativeOps:
         cores, bfloat16, head_dim 16/32/64/128), ``"decode"`` (tensor cores fed by TMA, bfloat16,
         head_dim 64/128, steps whose requests bring one token or very few), ``"prefill"``
         (tcgen05 tensor cores with accumulators in tensor memory, bfloat16, head_dim 64/128, made
-        for long portions) or ``"auto"`` (the most specialised kernel that applies).
+        for long portions; ``"prefill2"`` is its variant that multiplies probabilities as value +
+        remainder) or ``"auto"`` (the most specialised kernel that applies).
 
         ``block_table``, ``q_start`` and ``kv_len`` may be slices that cover only some requests of
         the step (``q_start`` keeps counting tokens from the start of ``q``); ``n_tokens`` then
@@ -533,7 +534,11 @@ class NativeOps:
         _need(block_table.shape[0] >= n_seqs and q_start.numel() >= n_seqs + 1 and kv_len.numel() >= n_seqs,
               "block_table, q_start and kv_len must cover every request of the step")
         _need(block_table.shape[1] * page_size >= max_kv_len, "block_table is too narrow for max_kv_len")
-        _need(impl in ("auto", "general", "mma", "decode", "prefill"), f"unknown attention implementation {impl!r}")
+        _need(impl in ("auto", "general", "mma", "decode", "prefill", "prefill2"), f"unknown attention implementation {impl!r}")
+        # "prefill2": the tcgen05 prefill kernel that multiplies probabilities as value + remainder
+        parts = 2 if impl == "prefill2" else self.prefill_probability_parts
+        if impl == "prefill2":
+            impl = "prefill"
         mma_ok = q.dtype == torch.bfloat16 and head_dim in (16, 32, 64, 128)
         _need(impl != "mma" or mma_ok, "the tensor-core attention kernel takes bfloat16 and head_dim 16, 32, 64 or 128")
         use_mma = mma_ok and impl in ("auto", "mma")
@@ -558,7 +563,7 @@ class NativeOps:
                 _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
                 _ptr(q_start), _ptr(kv_len), ctypes.c_void_p(self._status.data_ptr()), ctypes.c_longlong(q.shape[0]),
                 T, n_seqs, n_heads, n_kv_heads, head_dim, page_size, ctypes.c_longlong(k_pages.shape[0]), max_q_len,
-                int(window or 0), ctypes.c_float(scale), self.prefill_probability_parts, _stream())
+                int(window or 0), ctypes.c_float(scale), parts, _stream())
             _check(rc, "paged_attention_prefill")
             self.launches += 1
             return out
