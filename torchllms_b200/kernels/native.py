@@ -89,10 +89,14 @@ def _timed(fn):
         if prof is None:
             return fn(self, *args, **kwargs)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        depth, self._profile_depth = self._profile_depth, self._profile_depth + 1
         a.record()
-        out = fn(self, *args, **kwargs)
+        try:
+            out = fn(self, *args, **kwargs)
+        finally:
+            self._profile_depth = depth
         b.record()
-        prof.append((name, a, b))
+        prof.append((name, a, b, depth))      # depth: a call made inside another is taken off the outer one's time
         return out
     return wrapper
 
@@ -122,6 +126,7 @@ class NativeOps:
         self._status = torch.zeros(4, dtype=torch.int32).pin_memory()
         self._mm_out_dtype: Optional[bool] = None
         self._profile = None
+        self._profile_depth = 0
         # TORCHLLMS_B200_DEBUG=1: the libraries are built with -DTL_DEBUG (see kernels/build.py); kernels
         # range-check the indices they are given and report through a word that check_status() reads
         self.debug = os.environ.get("TORCHLLMS_B200_DEBUG", "") not in ("", "0")
@@ -164,10 +169,13 @@ class NativeOps:
         finally:
             records, self._profile = self._profile, None
             torch.cuda.synchronize()
-            for name, a, b in records:
+            inner: Dict[int, float] = {}            # time of finished calls by depth, not yet taken off their caller
+            for name, a, b, depth in records:       # (a call made inside another finishes, and is listed, first)
+                ms = a.elapsed_time(b)
                 entry = result.setdefault(name, [0, 0.0])
                 entry[0] += 1
-                entry[1] += a.elapsed_time(b)
+                entry[1] += ms - inner.pop(depth + 1, 0.0)
+                inner[depth] = inner.get(depth, 0.0) + ms
 
     # ------------------------------------------------------------- checks
     def check_attention_sizes(self, n_heads: int, n_kv_heads: int, head_dim: int, dtype: torch.dtype) -> None:
