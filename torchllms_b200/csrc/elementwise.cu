@@ -85,6 +85,36 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
     float* hr = h + (size_t)r * dim;
     const TD* dr = delta ? delta + (size_t)r * dim : nullptr;
     float ss = 0.f;
+    if (VEC == 4 && ssq_out != nullptr) {
+        // deferred form: what is written does not depend on the row's sum, so one walk does it all and
+        // nothing waits for the sum (no staging in shared memory, no second pass)
+        TO* orow = out + (size_t)o * dim;
+        for (int d = threadIdx.x * 4; d < dim; d += blockDim.x * 4) {
+            float4 x = load4(hr + d);
+            if (dr) {
+                float4 y = load4(dr + d);
+                for (int sp = 1; sp < splits; ++sp) {
+                    const float4 z = load4(dr + sp * plane + d);
+                    y.x += z.x; y.y += z.y; y.z += z.z; y.w += z.w;
+                }
+                x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+            }
+            const float4 w = d == (int)threadIdx.x * 4 ? w_first : load4(weight + d);
+            if (write_back) store4(hr + d, x);
+            store4(orow + d, make_float4(x.x * w.x, x.y * w.y, x.z * w.z, x.w * w.w));
+            ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+        }
+        ss = warp_sum(ss);
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+        if (lane == 0) warp_part[warp] = ss;
+        __syncthreads();
+        if (warp == 0) {
+            float v = lane < n_warps ? warp_part[lane] : 0.f;
+            v = warp_sum(v);
+            if (lane == 0) ssq_out[o] = v;
+        }
+        return;
+    }
     if (VEC == 4) {
         for (int d = threadIdx.x * 4; d < dim; d += blockDim.x * 4) {
             float4 x = load4(hr + d);
@@ -202,10 +232,10 @@ extern "C" int tl_embed(const int* ids, const void* table, int table_dtype, floa
 template <typename TD, typename TO>
 static int launch_rmsnorm(float* h, const void* delta, int splits, long long plane, const float* w, void* out,
                           const int* rows, int n_out, int dim, float eps, int write_back, float* ssq_out, cudaStream_t s) {
-    const size_t smem = (size_t)dim * sizeof(float);
-    if (smem > 200 * 1024) return TL_TOO_LARGE;
     const bool vec = dim % 4 == 0 && plane % 4 == 0 && aligned16(h) && aligned16(w) && aligned16(out) &&
                      (delta == nullptr || aligned16(delta));
+    const size_t smem = (vec && ssq_out != nullptr) ? 0 : (size_t)dim * sizeof(float);    // (the deferred form stages nothing)
+    if (smem > 200 * 1024) return TL_TOO_LARGE;
     auto kern = vec ? rmsnorm_kernel<TD, TO, 4> : rmsnorm_kernel<TD, TO, 1>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

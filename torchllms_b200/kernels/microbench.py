@@ -131,6 +131,8 @@ def elementwise(args) -> None:
     w = torch.ones(WIDTH, device="cuda")
     us = _time(_graphed([(lambda i=i: ops.rmsnorm(hs[i], ds[i], w, 1e-5, torch.bfloat16)) for i in range(copies)]), 5) / copies
     print(f"rmsnorm T {T}: {us:7.1f} us  {T * WIDTH * 12 / us / 1e6:5.2f} TB/s")
+    us = _time(_graphed([(lambda i=i: ops.rmsnorm(hs[i], ds[i], w, 1e-5, torch.bfloat16, deferred=True)) for i in range(copies)]), 5) / copies
+    print(f"rmsnorm T {T}, scale deferred: {us:7.1f} us  {T * WIDTH * 12 / us / 1e6:5.2f} TB/s")
     gus = [torch.randn(T, 2 * HIDDEN, device="cuda", dtype=torch.bfloat16) for _ in range(copies)]
     us = _time(_graphed([(lambda i=i: ops.swiglu(gus[i])) for i in range(copies)]), 5) / copies
     print(f"swiglu  T {T}: {us:7.1f} us  {T * HIDDEN * 6 / us / 1e6:5.2f} TB/s")
