@@ -133,6 +133,18 @@ def elementwise(args) -> None:
     print(f"rmsnorm T {T}: {us:7.1f} us  {T * WIDTH * 12 / us / 1e6:5.2f} TB/s")
     us = _time(_graphed([(lambda i=i: ops.rmsnorm(hs[i], ds[i], w, 1e-5, torch.bfloat16, deferred=True)) for i in range(copies)]), 5) / copies
     print(f"rmsnorm T {T}, scale deferred: {us:7.1f} us  {T * WIDTH * 12 / us / 1e6:5.2f} TB/s")
+    # rotation of q and k and the write of k and v into pages, as a prompt portion of T tokens needs it
+    row, page = (HEADS + 2 * KV_HEADS) * HEAD_DIM, 16
+    qkvs = [torch.randn(T, row, device="cuda", dtype=torch.bfloat16) for _ in range(copies)]
+    table = torch.randn(T, HEAD_DIM // 2, 2, device="cuda")
+    positions = torch.arange(T, dtype=torch.int32, device="cuda")
+    slots = torch.randperm(T, device="cuda").int()
+    kp = torch.empty(-(-T // page), KV_HEADS, page, HEAD_DIM, device="cuda", dtype=torch.bfloat16)
+    vp = torch.empty_like(kp)
+    us = _time(_graphed([(lambda i=i: ops.rope_kv_write(qkvs[i], positions, table, n_heads=HEADS, n_kv_heads=KV_HEADS,
+                                                        head_dim=HEAD_DIM, interleaved=True, k_pages=kp, v_pages=vp,
+                                                        slot_mapping=slots, page_size=page)) for i in range(copies)]), 5) / copies
+    print(f"rope + cache write T {T}: {us:7.1f} us  {T * row * 4 / us / 1e6:5.2f} TB/s")
     gus = [torch.randn(T, 2 * HIDDEN, device="cuda", dtype=torch.bfloat16) for _ in range(copies)]
     us = _time(_graphed([(lambda i=i: ops.swiglu(gus[i])) for i in range(copies)]), 5) / copies
     print(f"swiglu  T {T}: {us:7.1f} us  {T * HIDDEN * 6 / us / 1e6:5.2f} TB/s")
