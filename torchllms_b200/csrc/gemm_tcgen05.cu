@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
     __shared__ unsigned tmem_base_slot;
     __shared__ int abort_flag;
     __shared__ __align__(8) unsigned long long red_bar;      // residual form: counts the bytes other CTAs send here
-    __shared__ float rstd_s[BQ];
+    __shared__ __align__(16) float rstd_s[BQ];
     constexpr bool GATED = MODE == MODE_GATED;
     constexpr bool CLUSTERED = MODE == MODE_RESID;     // the K splits of a slab are one cluster
 
@@ -367,8 +367,16 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
 #pragma unroll
                 for (int c0 = 0; c0 < BQ; c0 += 16) {
                     unsigned r[16];
+                    if (n_kb > 0) TmemLoad<16>::run(tmem_d + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, r);
+                    // the sixteen tokens' scales in four loads, under way while the accumulator is fetched (one
+                    // load per element behind the wait cost 2 us with 64 tokens)
+                    float scales[16];
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const float4 v = *reinterpret_cast<const float4*>(&rstd_s[c0 + 4 * q4]);
+                        scales[4 * q4] = v.x; scales[4 * q4 + 1] = v.y; scales[4 * q4 + 2] = v.z; scales[4 * q4 + 3] = v.w;
+                    }
                     if (n_kb > 0) {
-                        TmemLoad<16>::run(tmem_d + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, r);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     } else {
 #pragma unroll
@@ -381,7 +389,7 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
                             if (tok < p.M) {
                                 // (rounded to bfloat16 first, as they are when they pass through memory:
                                 // this form and the two-kernel form give the same numbers)
-                                const float sc = rstd_s[tok];
+                                const float sc = scales[j];
                                 const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j]))) * sc;
                                 const float u = __bfloat162float(__float2bfloat16_rn(n_kb > 0 ? xch[row * (BQ + 1) + tok] : 0.f)) * sc;
                                 reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)tok * p.hidden + f] =
