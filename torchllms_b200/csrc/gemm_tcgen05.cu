@@ -150,10 +150,9 @@ __device__ __forceinline__ void st_async_f32(unsigned remote_addr, float v, unsi
     asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
                  ::"r"(remote_addr), "r"(__float_as_uint(v)), "r"(remote_bar) : "memory");
 }
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
+// The cluster's barrier in two halves: every thread arrives once and waits once, possibly much later.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 template <int N> struct TmemLoad;
 template <> struct TmemLoad<16> {
@@ -242,8 +241,12 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
     const int n_owned = (CLUSTERED && p.M > rank) ? (p.M - rank - 1) / S + 1 : 0;
     float* red = reinterpret_cast<float*>(tiles + STAGES * STAGE_BYTES);     // [owned token][split][row of the slab]
     if (CLUSTERED) {
+        // Every CTA's barrier must be set up before anybody sends to it.  The threads only say here that
+        // theirs is; each waits for the others where it needs them (the epilogue before it sends, the two
+        // other roles when they are done), so that the weights start to stream before the whole cluster
+        // is on the machine.
         if (threadIdx.x == 0) mbar_expect_tx(&red_bar, (unsigned)(n_owned * S * BP * 4));
-        cluster_sync_all();          // every CTA's barrier is set up before anybody sends to it
+        cluster_arrive();
     }
     grid_launch_dependents();
 
@@ -280,6 +283,8 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
                 tma_load_2d(wt + W_BYTES, &map_a, &full_bar[s], (kb0 + i) * BK, 0);
             }
         }
+        __syncwarp();
+        if (CLUSTERED) cluster_wait();
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- tensor-core issuer
@@ -303,6 +308,8 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
             }
             if (ok) umma_commit(&accum_bar);     // everything issued so far has landed in TMEM
         }
+        __syncwarp();
+        if (CLUSTERED) cluster_wait();
     } else {
         // ---- epilogue: warp w owns TMEM lanes 32 * (w % 4) .. + 31, i.e. rows of W of this slab
         const int quarter = warp & 3;
@@ -405,6 +412,7 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
             // has landed.  A CTA whose waits did not hold sends nothing: its owners' waits run out in
             // turn and say so.
             const int row = quarter * 32 + lane;
+            cluster_wait();          // the owners' barriers are set up
             if (ok) {
                 const unsigned red_addr = smem_u32(red), bar_addr = smem_u32(&red_bar);
 #pragma unroll
