@@ -385,6 +385,9 @@ ATTN_CASES = [
     ([3000, 700], [400, 700], 8, 2, 128, 16, None),       # a portion late in a long context beside a whole prompt
     ([1000], [1000], 4, 2, 64, 32, 300),                  # a window that spans several key tiles
     ([600, 130], [600, 129], 4, 4, 128, 256, None),       # pages larger than a key tile of any kernel
+    ([1200], [1200], 8, 2, 128, 16, 200),                 # head_dim 128 behind a window that starts inside a key tile
+    ([700, 300, 1025], [700, 300, 1025], 8, 2, 128, 16, None),   # ragged whole prompts: a last query block of one row
+    ([2500, 520], [257, 384], 4, 1, 64, 64, 1000),        # portions late in their contexts, windowed, pages of 64
 ]
 
 
