@@ -281,7 +281,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
     const unsigned tmem = tmem_base_slot;
     volatile int* failed = &failed_flag;
     grid_launch_dependents();
-    grid_dependency_wait();
+    // (what is read down to the dependency wait does not come from the kernels just before this one: the
+    // step's index data were uploaded before its first kernel; so this runs while the predecessor still works)
 
     // CTAs start in the order x, then y, then z: the heads run along x, so that all heads of the
     // query block with most keys start first and the short blocks fill the gaps at the end
@@ -311,6 +312,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
         n_tiles = max(n_tiles, range[t].last);
     }
     const int k_hi = qpos_base + min(ql, tok0 + QT * BM);    // one past the last key anybody here sees
+    grid_dependency_wait();
 
     if (warp == W_COPY) {
         if (active) {
@@ -745,7 +747,8 @@ __global__ void __launch_bounds__(NTHREADS_ROWS, 1) attention_prefill_rows_kerne
     const unsigned tmem = tmem_base_slot;
     volatile int* failed = &failed_flag;
     grid_launch_dependents();
-    grid_dependency_wait();
+    // (what is read down to the dependency wait does not come from the kernels just before this one: the
+    // step's index data were uploaded before its first kernel; so this runs while the predecessor still works)
 
     const int b = blockIdx.z;
     const int head = blockIdx.x;
@@ -771,6 +774,7 @@ __global__ void __launch_bounds__(NTHREADS_ROWS, 1) attention_prefill_rows_kerne
         n_tiles = max(n_tiles, range[t].last);
     }
     const int k_hi = qpos_base + min(ql, tok0 + QT * BM);
+    grid_dependency_wait();
 
     if (warp >= WR_COPY) {
         regs_down<REGS_REST>();
