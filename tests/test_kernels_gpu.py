@@ -540,6 +540,28 @@ def test_window_edge_is_exact(ops, dtype, impl):
         torch.testing.assert_close(got, want, atol=tol(dtype, 2e-5, 2e-2), rtol=tol(dtype, 2e-5, 2e-2))
 
 
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_prefill_attention_on_random_shapes(ops, seed):
+    """Both tcgen05 prefill kernels on shapes nobody picked: heads and groups, page sizes from 4 to 256, up to
+    four requests whose portions start anywhere in their contexts, windows of any length."""
+    import random
+    rng = random.Random(seed)
+    for _ in range(40):
+        hd = rng.choice([64, 128])
+        KV = rng.choice([1, 2, 4, 8])
+        H = KV * rng.choice([1, 2, 4, 8])
+        P = rng.choice([4, 8, 16, 32, 64, 128, 256])
+        q_lens = [rng.choice([rng.randint(96, 300), rng.randint(1, 700), rng.randint(200, 1100)]) for _ in range(rng.randint(1, 4))]
+        seq_lens = [q + rng.choice([0, 0, rng.randint(1, 1500)]) for q in q_lens]
+        window = rng.choice([None, None, rng.randint(1, 900)])
+        a = build_paged(seq_lens, q_lens, H, KV, hd, P, torch.bfloat16, seed=rng.randrange(1 << 30))
+        want = TWIN.paged_attention(**a, scale=hd ** -0.5, window=window).float()
+        for impl in ("prefill", "prefill2"):
+            got = ops.paged_attention(**a, scale=hd ** -0.5, window=window, impl=impl).float()
+            ops.check_status()
+            torch.testing.assert_close(got, want, atol=2e-2, rtol=2e-2, msg=lambda m: f"{impl} {seq_lens} {q_lens} H{H} KV{KV} hd{hd} P{P} w{window}: {m}")
+
+
 def test_attention_refuses_sizes_it_cannot_do(ops):
     from torchllms_b200.kernels.native import KernelError
     with pytest.raises(KernelError):
