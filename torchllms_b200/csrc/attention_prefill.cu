@@ -943,26 +943,36 @@ __global__ void __launch_bounds__(NTHREADS_ROWS, 1) attention_prefill_rows_kerne
                 ok = __all_sync(0xffffffffu, mbar_wait(&l_ready[t], 0, failed) && mbar_wait(&pv_done[t], (n - 1) & 1, failed));
                 if (!ok) break;
                 tc_fence_after();
-                const bool valid = r < rows;
                 const float l = tail.l_final[t][r];
                 const float inv = l > 0.f ? 1.f / l : 0.f;
-                __nv_bfloat16* orow = p.out + ((size_t)(qs + tok0 + t * BM + r) * p.n_heads + head) * HD;
+                // The rows leave through shared memory (the query tile's place: its last product is over), in
+                // the swizzled layout the queries had, so that they are written to global memory a row
+                // at a time; a thread writing 16 bytes of its own row, 8 KB from its neighbour's, took 6 us.
+                unsigned char* stage = Qs + t * KV_BYTES;
 #pragma unroll
                 for (int c = 0; c < HD / PIECE; ++c) {
                     unsigned v[PIECE];
                     tmem_ld<PIECE>(lane_addr + COL_O + t * BN + c * PIECE, v);
                     tmem_wait_ld();
-                    if (valid) {
 #pragma unroll
-                        for (int i = 0; i < PIECE / 8; ++i) {
-                            uint4 w;
-                            w.x = pack_bf16(__uint_as_float(v[8 * i]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
-                            w.y = pack_bf16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
-                            w.z = pack_bf16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
-                            w.w = pack_bf16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
-                            *reinterpret_cast<uint4*>(orow + c * PIECE + i * 8) = w;
-                        }
+                    for (int i = 0; i < PIECE / 8; ++i) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(v[8 * i]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+                        const int chunk = c * (PIECE / 8) + i;
+                        *reinterpret_cast<uint4*>(stage + (chunk >> 3) * HALF_BYTES + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) = w;
                     }
+                }
+                __syncwarp();                                // (a warp writes out the 32 rows it staged itself)
+                constexpr int CH = HD / 8;
+#pragma unroll
+                for (int i = 0; i < CH; ++i) {
+                    const int row = cw * 32 + i * (32 / CH) + lane / CH, chunk = lane % CH;
+                    const uint4 w = *reinterpret_cast<const uint4*>(stage + (chunk >> 3) * HALF_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+                    if (row < rows)
+                        *reinterpret_cast<uint4*>(p.out + ((size_t)(qs + tok0 + t * BM + row) * p.n_heads + head) * HD + chunk * 8) = w;
                 }
             }
             if (!ok && lane == 0) {
@@ -982,12 +992,17 @@ __global__ void __launch_bounds__(NTHREADS_ROWS, 1) attention_prefill_rows_kerne
             const int first = t ? range[1].first : range[0].first, last = t ? range[1].last : range[0].last;
             const unsigned col_s = COL_S + t * BN;
             {
-                const bool valid = r < rows;
-                const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + tok0 + t * BM + r) * p.n_heads + head) * HD);
+                // this warp's 32 query rows go into shared memory in the layout of a K tile (rows of 128 bytes,
+                // 16-byte chunks swizzled with the row); neighbouring lanes take neighbouring chunks of a
+                // row, so that a row is read in one piece
+                constexpr int CH = HD / 8;                   // 16-byte chunks of a row
 #pragma unroll
-                for (int chunk = 0; chunk < HD / 8; ++chunk) {
-                    const uint4 v = valid ? src[chunk] : make_uint4(0u, 0u, 0u, 0u);
-                    *reinterpret_cast<uint4*>(Qs + t * KV_BYTES + (chunk >> 3) * HALF_BYTES + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) = v;
+                for (int i = 0; i < CH; ++i) {
+                    const int row = sw * 32 + i * (32 / CH) + lane / CH, chunk = lane % CH;
+                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                    if (row < rows)
+                        v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + tok0 + t * BM + row) * p.n_heads + head) * HD + chunk * 8);
+                    *reinterpret_cast<uint4*>(Qs + t * KV_BYTES + (chunk >> 3) * HALF_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4)) = v;
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
