@@ -122,6 +122,10 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
 __device__ __forceinline__ bool copy_is_sound(const void* dst, int x, int y) {
     return (x & 7) == 0 && x >= 0 && y >= 0 && (smem_u32(dst) & 127u) == 0u;
 }
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
@@ -661,7 +665,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
 //   warps 8-11     : correction.  When a row's maximum in use has grown they rescale its accumulator
 //                    (a round trip through registers) off the softmax's path; at the end they divide
 //                    by the row's sum and store it.
-//   warp 12        : TMA producer;  warps 13, 14 : the issuers of the two query tiles (the whole warp
+//   warp 12        : TMA producer (the two query tiles through a three-dimensional map of q, then K and V);
+//                    warps 13, 14 : the issuers of the two query tiles (the whole warp
 //                    runs in step and one elected lane issues: a lone lane inside a divergent branch
 //                    cannot keep the descriptors in uniform registers, and issued a fifth slower);
 //                    warp 15 is there to complete the warp group.
@@ -693,6 +698,7 @@ template <int N> __device__ __forceinline__ void regs_down() { asm volatile("set
 template <int HD, int STAGES>
 __global__ void __launch_bounds__(NTHREADS_ROWS, 1) attention_prefill_rows_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                                  const __grid_constant__ CUtensorMap map_v,
+                                                                                 const __grid_constant__ CUtensorMap map_q,
                                                                                  const PrefillParams p) {
     constexpr int HALVES = HD / 64;
     constexpr unsigned HALF_BYTES = BN * 128;
@@ -719,7 +725,7 @@ __global__ void __launch_bounds__(NTHREADS_ROWS, 1) attention_prefill_rows_kerne
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
         failed_flag = 0;
-        mbar_init(&q_full, 4 * QT);
+        mbar_init(&q_full, 1);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&k_empty[s], QT);
@@ -786,6 +792,19 @@ __global__ void __launch_bounds__(NTHREADS_ROWS, 1) attention_prefill_rows_kerne
                     failed_flag = 1;
                     atomicExch(p.status, ERR_BAD_COPY);
                 }
+                // the queries of both tiles: [128 tokens x 64 elements] boxes of this head, which land in the
+                // layout of a K tile (rows past the request's own are another request's or the zero fill:
+                // their results are never stored)
+                if (sound && lane == 0) {
+                    int tiles_q = 0;
+                    for (int t = 0; t < QT; ++t) tiles_q += (t ? range[1].rows : range[0].rows) > 0 ? 1 : 0;
+                    mbar_expect_tx(&q_full, tiles_q * KV_BYTES);
+                    for (int t = 0; t < QT; ++t)
+                        if ((t ? range[1].rows : range[0].rows) > 0)
+                            for (int h = 0; h < HALVES; ++h)
+                                tma_load_3d(Qs + t * KV_BYTES + h * HALF_BYTES, &map_q, &q_full, h * 64, head, qs + tok0 + t * BM);
+                }
+                __syncwarp();
                 const int* table = p.block_table + (size_t)b * p.table_stride;
                 const int n_boxes = BN / p.box_rows;
                 for (int j = 0; j < n_tiles && sound; ++j) {
@@ -991,24 +1010,6 @@ __global__ void __launch_bounds__(NTHREADS_ROWS, 1) attention_prefill_rows_kerne
             const int rows = t ? range[1].rows : range[0].rows;
             const int first = t ? range[1].first : range[0].first, last = t ? range[1].last : range[0].last;
             const unsigned col_s = COL_S + t * BN;
-            {
-                // this warp's 32 query rows go into shared memory in the layout of a K tile (rows of 128 bytes,
-                // 16-byte chunks swizzled with the row); neighbouring lanes take neighbouring chunks of a
-                // row, so that a row is read in one piece
-                constexpr int CH = HD / 8;                   // 16-byte chunks of a row
-#pragma unroll
-                for (int i = 0; i < CH; ++i) {
-                    const int row = sw * 32 + i * (32 / CH) + lane / CH, chunk = lane % CH;
-                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                    if (row < rows)
-                        v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + tok0 + t * BM + row) * p.n_heads + head) * HD + chunk * 8);
-                    *reinterpret_cast<uint4*>(Qs + t * KV_BYTES + (chunk >> 3) * HALF_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4)) = v;
-                }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&q_full);
-
             float m_used = -INFINITY, l_sum = 0.f;
             const int t0 = qpos_base + tok0 + t * BM;
             const int qpos = t0 + (r < rows ? r : rows - 1);
@@ -1155,6 +1156,35 @@ int tiled_map(CUtensorMap* out, const void* base, long long rows, long long cols
     return TL_OK;
 }
 
+// the queries [rows, n_heads, head_dim] bfloat16 as a three-dimensional tensor; box = 128 tokens of one head
+// x 64 elements, 128-byte swizzle, zero fill outside
+int query_map(CUtensorMap* out, const void* base, long long rows, int n_heads, int head_dim) {
+    static std::map<std::tuple<const void*, long long, int, int>, CUtensorMap> cache;
+    static std::mutex lock;
+    std::lock_guard<std::mutex> guard(lock);
+    auto key = std::make_tuple(base, rows, n_heads, head_dim);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return TL_OK;
+    }
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr) return TL_BAD_SIZE;
+    cuuint64_t dims[3] = {(cuuint64_t)head_dim, (cuuint64_t)n_heads, (cuuint64_t)rows};
+    cuuint64_t strides[2] = {(cuuint64_t)head_dim * 2, (cuuint64_t)n_heads * head_dim * 2};
+    cuuint32_t box[3] = {64u, 1u, (cuuint32_t)BM};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUtensorMap m;
+    CUresult rc = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return TL_BAD_SIZE;
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = m;
+    *out = m;
+    return TL_OK;
+}
+
 template <int HD> constexpr int stages_for() { return HD == 128 ? 2 : 4; }
 template <int HD> constexpr size_t smem_for() {
     return (size_t)(QT + 2 * stages_for<HD>()) * (HD / 64) * BN * 128 + sizeof(Tail<stages_for<HD>()>);
@@ -1176,7 +1206,7 @@ template <int HD> constexpr size_t smem_rows_for() {
 static_assert(smem_rows_for<128>() <= 227 * 1024 && smem_rows_for<64>() <= 227 * 1024, "a CTA has 227 KB of shared memory");
 
 template <int HD>
-int launch_rows(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, dim3 grid, cudaStream_t s) {
+int launch_rows(const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mq, const PrefillParams& p, dim3 grid, cudaStream_t s) {
     constexpr size_t smem = smem_rows_for<HD>();
     auto kern = attention_prefill_rows_kernel<HD, stages_for<HD>()>;
     static bool raised = false;
@@ -1185,7 +1215,7 @@ int launch_rows(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParam
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
-    return (int)tl_launch(kern, grid, dim3(NTHREADS_ROWS), smem, s, mk, mv, p);
+    return (int)tl_launch(kern, grid, dim3(NTHREADS_ROWS), smem, s, mk, mv, mq, p);
 }
 
 template <int HD, int PARTS>
@@ -1248,5 +1278,8 @@ extern "C" int tl_paged_attention_prefill(const void* q, const void* k_pages, co
     dim3 grid(n_heads, p.n_q_blocks, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;
     if (parts == 2) return head_dim == 128 ? launch<128, 2>(mk, mv, p, grid, s) : launch<64, 2>(mk, mv, p, grid, s);
-    return head_dim == 128 ? launch_rows<128>(mk, mv, p, grid, s) : launch_rows<64>(mk, mv, p, grid, s);
+    CUtensorMap mq;
+    rc = query_map(&mq, q, q_rows, n_heads, head_dim);
+    if (rc != TL_OK) return rc;
+    return head_dim == 128 ? launch_rows<128>(mk, mv, mq, p, grid, s) : launch_rows<64>(mk, mv, mq, p, grid, s);
 }
