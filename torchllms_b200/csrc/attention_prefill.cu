@@ -684,7 +684,7 @@ constexpr int WR_CORR = 4 * QT, WR_COPY = 4 * QT + 4, WR_ISSUE = 4 * QT + 5;
 template <int STAGES>
 struct TailRows {
     unsigned long long q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-    unsigned long long s_full[QT], p_full[QT], pv_done[QT], alpha_ready[QT], o_ready[QT], l_ready[QT], turn[QT];
+    unsigned long long s_full[QT], p_half[QT], p_full[QT], pv_done[QT], alpha_ready[QT], o_ready[QT], l_ready[QT], turn[QT];
     unsigned tmem_base_slot;
     int failed_flag;
     int grow_any[QT][2][4];     // [tile][parity of the tile's step][warp of the tile]: did a row of the warp grow
@@ -714,6 +714,7 @@ __global__ void __launch_bounds__(NTHREADS_ROWS, 1) attention_prefill_rows_kerne
     unsigned long long (&v_empty)[STAGES] = tail.v_empty;
     unsigned long long (&s_full)[QT] = tail.s_full;
     unsigned long long (&p_full)[QT] = tail.p_full;
+    unsigned long long (&p_half)[QT] = tail.p_half;
     unsigned long long (&pv_done)[QT] = tail.pv_done;
     unsigned long long (&alpha_ready)[QT] = tail.alpha_ready;
     unsigned long long (&o_ready)[QT] = tail.o_ready;
@@ -735,6 +736,7 @@ __global__ void __launch_bounds__(NTHREADS_ROWS, 1) attention_prefill_rows_kerne
         for (int t = 0; t < QT; ++t) {
             mbar_init(&s_full[t], 1);
             mbar_init(&p_full[t], 4);
+            mbar_init(&p_half[t], 4);
             mbar_init(&pv_done[t], 1);
             mbar_init(&alpha_ready[t], 4);
             mbar_init(&o_ready[t], 4);
@@ -894,14 +896,21 @@ __global__ void __launch_bounds__(NTHREADS_ROWS, 1) attention_prefill_rows_kerne
                     if (ok && j + 1 < n_tiles) ok = __all_sync(0xffffffffu, mbar_wait(&k_full[(j + 1) % STAGES], ((j + 1) / STAGES) & 1, failed));
                     if (!ok) break;
                     if (mine) {
-                        ok = __all_sync(0xffffffffu, mbar_wait(&p_full[t], (j - first) & 1, failed) && mbar_wait(&o_ready[t], (j - first) & 1, failed));
+                        // the product starts on the first half of the probabilities while the second is still being taken
+                        ok = __all_sync(0xffffffffu, mbar_wait(&p_half[t], (j - first) & 1, failed) && mbar_wait(&o_ready[t], (j - first) & 1, failed));
                         if (!ok) break;
                         tc_fence_after();
                         const unsigned long long vd0 = desc_mn_major(smem_u32(tiles + (STAGES + s) * KV_BYTES), HALF_BYTES);
                         const unsigned acc = j > first ? 1u : 0u;
 #pragma unroll
-                        for (int kk = 0; kk < BN / 16; ++kk)
+                        for (int kk = 0; kk < BN / 32; ++kk)
                             umma_ts_elect(d_o, d_s + kk * 8, vd0 + kk * (2048 >> 4), id_o, kk > 0 ? 1u : acc);
+                        ok = __all_sync(0xffffffffu, mbar_wait(&p_full[t], (j - first) & 1, failed));
+                        if (!ok) break;
+                        tc_fence_after();
+#pragma unroll
+                        for (int kk = BN / 32; kk < BN / 16; ++kk)
+                            umma_ts_elect(d_o, d_s + kk * 8, vd0 + kk * (2048 >> 4), id_o, 1u);
                         umma_commit_elect(&pv_done[t]);
                         umma_commit_elect(&v_empty[s]);
                     } else if (lane == 0) {
@@ -1043,14 +1052,14 @@ __global__ void __launch_bounds__(NTHREADS_ROWS, 1) attention_prefill_rows_kerne
                         if (!vis) raw[i] = 0xff800000u;      // -inf
                     }
                 }
-                float mx0 = __uint_as_float(raw[0]), mx1 = __uint_as_float(raw[1]);
-                float mx2 = __uint_as_float(raw[2]), mx3 = __uint_as_float(raw[3]);
+                float mx[8];
 #pragma unroll
-                for (int i = 4; i < BN; i += 4) {
-                    mx0 = fmaxf(mx0, __uint_as_float(raw[i])); mx1 = fmaxf(mx1, __uint_as_float(raw[i + 1]));
-                    mx2 = fmaxf(mx2, __uint_as_float(raw[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(raw[i + 3]));
-                }
-                const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
+                for (int i = 0; i < 8; ++i) mx[i] = __uint_as_float(raw[i]);
+#pragma unroll
+                for (int i = 8; i < BN; i += 8)
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) mx[k] = fmaxf(mx[k], __uint_as_float(raw[i + k]));
+                const float m_new = fmaxf(m_used, fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))) * p.scale_log2);
                 const bool grow = m_new > m_used + LAG;      // also true for the first keys a row sees
                 const float alpha = grow ? ex2(m_used - m_new) : 1.f;
                 if (grow) m_used = m_new;
@@ -1081,6 +1090,12 @@ __global__ void __launch_bounds__(NTHREADS_ROWS, 1) attention_prefill_rows_kerne
                         packed[i / 2 + 1] = pack_bf16(eb.x, eb.y);
                     }
                     tmem_st<16>(lane_addr + col_s + c * 16, packed);      // (all scores are in registers: nothing is overwritten unread)
+                    if (c == BN / 64 - 1) {          // half of the keys' probabilities are in place
+                        tmem_wait_st();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&p_half[t]);
+                    }
                 }
                 l_sum += (la.x + la.y) + (lb.x + lb.y);
                 __syncwarp();
