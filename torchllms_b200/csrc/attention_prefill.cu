@@ -672,8 +672,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) attention_prefill_kernel(const __
 //                    warp 15 is there to complete the warp group.
 // Barriers beside those of the kernel above: alpha_ready (softmax -> correction: factors are in
 // shared memory), o_ready (correction -> issuer: the accumulator may take the next product),
-// l_ready (softmax -> correction: the row sums are in shared memory), turn (softmax -> the other
-// tile's softmax: the exponential unit is yours).
+// p_half (softmax -> issuer: the probabilities of the tile's first 64 keys are in place, the product may
+// start on them), l_ready (softmax -> correction: the row sums are in shared memory), turn (softmax ->
+// the other tile's softmax: the exponential unit is yours).
 constexpr int NTHREADS_ROWS = 512;
 // Registers a thread after the trade: softmax / correction / the rest.  A warp group can only be given
 // what another has handed back, so the sum stays within what the launch allots (128 a thread).
