@@ -124,14 +124,17 @@ __host__ __device__ constexpr unsigned umma_idesc(int n) {
          | ((unsigned)(BP >> 4) << 24);
 }
 
+// Both for a whole warp in step, of which one elected lane issues: the descriptors then stay warp-uniform
+// values (a lone lane inside a divergent branch cannot have those).
 __device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
                                           unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+    asm volatile("{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+    asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+                 "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
 }
 
 // ---- distributed shared memory: addresses of the same variable in another CTA of the cluster, and
@@ -286,15 +289,17 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
         __syncwarp();
         if (CLUSTERED) cluster_wait();
     } else if (warp == 1) {
-        if (lane == 0) {
-            // ---- tensor-core issuer
+        {
+            // ---- tensor-core issuer: the whole warp in step, one elected lane issuing
             constexpr unsigned idesc = umma_idesc(BQ);
             bool ok = true;
             for (int i = 0; i < n_kb && ok; ++i) {
                 const int s = i % STAGES;
-                if (!mbar_wait(&full_bar[s], (i / STAGES) & 1, aborted)) {
-                    abort_flag = 1;
-                    atomicExch(p.status, ERR_MMA_WAIT);
+                if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], (i / STAGES) & 1, aborted))) {
+                    if (lane == 0) {
+                        abort_flag = 1;
+                        atomicExch(p.status, ERR_MMA_WAIT);
+                    }
                     ok = false;
                     break;
                 }
