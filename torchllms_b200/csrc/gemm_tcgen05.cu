@@ -98,9 +98,15 @@ __global__ void wait_selftest_kernel(int* status, unsigned long long limit_ns, u
     }
 }
 
+// The producer's two instructions are for a whole warp in step, of which one elected lane issues.
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+    asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+                 "@e cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_elect(unsigned long long* bar, unsigned bytes) {
+    asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+                 "@e mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 
 // shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart
@@ -254,9 +260,10 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
     grid_launch_dependents();
 
     if (warp == 0) {
-        if (lane == 0) {
-            // ---- producer.  The weights depend on no earlier kernel: their first tiles are fetched
-            // before the dependency on the predecessor is resolved, the activations after it.
+        {
+            // ---- producer (the whole warp in step, one elected lane issuing).  The weights depend on no
+            // earlier kernel: their first tiles are fetched before the dependency on the predecessor is
+            // resolved, the activations after it.
             const int pre = n_kb < STAGES ? n_kb : STAGES;
             auto load_w = [&](unsigned char* dst, unsigned long long* bar, int kb) {
                 if (GATED) {
@@ -267,7 +274,7 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
                 }
             };
             for (int i = 0; i < pre; ++i) {
-                mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+                mbar_expect_tx_elect(&full_bar[i], STAGE_BYTES);
                 load_w(tiles + i * STAGE_BYTES, &full_bar[i], kb0 + i);
             }
             grid_dependency_wait();
@@ -275,13 +282,15 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
                 tma_load_2d(tiles + i * STAGE_BYTES + W_BYTES, &map_a, &full_bar[i], (kb0 + i) * BK, 0);
             for (int i = pre; i < n_kb; ++i) {
                 const int s = i % STAGES;
-                if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, aborted)) {
-                    abort_flag = 1;
-                    atomicExch(p.status, ERR_TMA_WAIT);
+                if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, aborted))) {
+                    if (lane == 0) {
+                        abort_flag = 1;
+                        atomicExch(p.status, ERR_TMA_WAIT);
+                    }
                     break;
                 }
                 unsigned char* wt = tiles + s * STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                mbar_expect_tx_elect(&full_bar[s], STAGE_BYTES);
                 load_w(wt, &full_bar[s], kb0 + i);
                 tma_load_2d(wt + W_BYTES, &map_a, &full_bar[s], (kb0 + i) * BK, 0);
             }
