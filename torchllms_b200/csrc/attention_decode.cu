@@ -179,13 +179,15 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 3 : 2) attention_decode_ke
     const int n_tiles = k_hi > k_start ? (k_hi - k_start + BN - 1) / BN : 0;
     const int* table = p.block_table + (size_t)b * p.table_stride;
 
-    // one tile: a box per page (or per 64 rows of a larger page) and 64-element column block, K and V
+    // one tile: a box per page (or per 64 rows of a larger page) and 64-element column block, K and V.
+    // The whole producer warp issues it, a lane to a box: the page lookups go side by side.
     auto issue_tile = [&](int it) {
         const int s = it % STAGES;
         const int k0 = k_start + it * BN;
-        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        if (lane == 0) mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        __syncwarp();
         unsigned char* kt = tiles + s * STAGE_BYTES;
-        for (int c = 0; c < BN / p.box_rows; ++c) {
+        for (int c = lane; c < BN / p.box_rows; c += 32) {
             const int kpos = k0 + c * p.box_rows;
             // boxes past the last key start outside the tensor: the copy writes the zero fill, so
             // that what is multiplied by probability 0 there is finite
@@ -202,17 +204,21 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 3 : 2) attention_decode_ke
                 tma_load_2d(dst + KV_BYTES, &map_v, &full_bar[s], h * 64, row);
             }
         }
+        __syncwarp();
     };
 
-    if (tid == NCW * 32) {
-        // the producer lane sets the barriers up and sends the first tiles on their way while the
+    if (warp == NCW) {
+        // the producer warp sets the barriers up and sends the first tiles on their way while the
         // other warps are still fetching the queries
-        failed_flag = 0;
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], NCW);
+        if (lane == 0) {
+            failed_flag = 0;
+            for (int s = 0; s < STAGES; ++s) {
+                mbar_init(&full_bar[s], 1);
+                mbar_init(&empty_bar[s], NCW);
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        __syncwarp();
         // tiles that end before the step's first new position can go now; a tile that may hold a key
         // written by the predecessor (only the last tile of the last split can) waits for it
         int it = 0;
@@ -250,15 +256,15 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 3 : 2) attention_decode_ke
 
     if (warp == NCW) {
         // ---- producer: the first tiles are on their way; keep the ring full
-        if (lane == 0) {
-            for (int it = STAGES; it < n_tiles; ++it) {
-                if (!mbar_wait(&empty_bar[it % STAGES], ((it / STAGES) - 1) & 1, failed)) {
+        for (int it = STAGES; it < n_tiles; ++it) {
+            if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[it % STAGES], ((it / STAGES) - 1) & 1, failed))) {
+                if (lane == 0) {
                     failed_flag = 1;
                     atomicExch(p.status, ERR_PRODUCER_WAIT);
-                    break;
                 }
-                issue_tile(it);
+                break;
             }
+            issue_tile(it);
         }
     } else {
         // ---- consumers: the same rows, 16 keys of every tile each
