@@ -388,6 +388,7 @@ ATTN_CASES = [
     ([1200], [1200], 8, 2, 128, 16, 200),                 # head_dim 128 behind a window that starts inside a key tile
     ([700, 300, 1025], [700, 300, 1025], 8, 2, 128, 16, None),   # ragged whole prompts: a last query block of one row
     ([2500, 520], [257, 384], 4, 1, 64, 64, 1000),        # portions late in their contexts, windowed, pages of 64
+    ([1500 + 7 * i for i in range(64)], [1] * 64, 8, 2, 128, 16, None),   # decoding over more keys and values than L2 holds (their copies are marked to leave it first)
 ]
 
 
